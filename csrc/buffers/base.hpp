@@ -1,0 +1,48 @@
+// Lifecycle shared by all buffers (reference: `csrc/buffers/base.hpp:11-63`).
+#pragma once
+
+#include <cstdio>
+#include <memory>
+
+#include "../comm/context.hpp"
+
+namespace deep_ep {
+
+class BufferBase {
+protected:
+    bool explicitly_destroy;
+    bool destroyed = false;
+
+    // Called from the destructor of the concrete buffer.
+    void destroy_on_destruction(const char* name) {
+        if (destroyed) return;
+        if (explicitly_destroy) {
+            std::fprintf(stderr, "[deep_ep] WARNING: %s buffer released without destroy(); its symmetric memory is "
+                                 "freed without a final barrier\n", name);
+            release_without_barrier();
+        } else {
+            try { destroy(); } catch (const std::exception& e) {
+                std::fprintf(stderr, "[deep_ep] WARNING: destroying %s buffer failed: %s\n", name, e.what());
+            }
+        }
+    }
+    virtual void release_without_barrier() {}
+
+public:
+    std::shared_ptr<comm::Context> main_context;
+
+    explicit BufferBase(bool explicitly_destroy) : explicitly_destroy(explicitly_destroy) {}
+    virtual ~BufferBase() noexcept(false) = default;
+    virtual void destroy() = 0;
+
+    void print_memory_usage() const {
+        EP_HOST_ASSERT(main_context != nullptr);
+        const auto mib = [](int64_t b) { return static_cast<double>(b) / (1 << 20); };
+        std::printf("[deep_ep] rank %d/%d: workspace %.1f MiB, buffer %.1f MiB, storage %.1f MiB\n",
+                    main_context->rank_idx, main_context->num_ranks, mib(main_context->num_workspace_bytes),
+                    mib(main_context->num_gpu_buffer_bytes), mib(main_context->num_rdma_storage_bytes));
+        std::fflush(stdout);
+    }
+};
+
+}  // namespace deep_ep

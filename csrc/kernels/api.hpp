@@ -1,0 +1,39 @@
+// Host-callable launchers of the sm_100a kernels (defined in `launch.cu`, compiled by nvcc).
+// Same role as the reference's `csrc/kernels/**` launchers: choose grid, shared memory and
+// pipeline depth, then launch on the given stream.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <deep_ep/kernels/ep_args.hpp>
+#include <deep_ep/kernels/misc_args.hpp>
+
+namespace deep_ep::launch {
+
+struct PipelineConfig {
+    int num_warps;
+    int num_stages;
+    int64_t smem_bytes;
+};
+
+// Largest warp/stage combination that fits the opt-in shared memory of one CTA.
+PipelineConfig choose_dispatch_config(int token_bytes, int src_row_bytes, int num_topk, int num_experts);
+PipelineConfig choose_expand_config(int token_bytes, int num_topk, int num_local_experts);
+PipelineConfig choose_combine_config(int token_bytes);
+
+void dispatch(kernels::DispatchArgs args, int num_sms, cudaStream_t stream);
+void dispatch_expand(kernels::ExpandArgs args, int num_sms, cudaStream_t stream);
+void combine(kernels::CombineArgs args, int num_sms, cudaStream_t stream);
+void combine_reduce(kernels::CombineReduceArgs args, int num_sms, cudaStream_t stream);
+
+void barrier(const kernels::BarrierArgs& args, cudaStream_t stream);
+void engram_fetch(const kernels::EngramFetchArgs& args, int num_sms, cudaStream_t stream);
+void all_gather(const kernels::AllGatherArgs& args, int num_sms, cudaStream_t stream);
+void pp_send(const kernels::PPArgs& args, int num_sms, cudaStream_t stream);
+void pp_recv(const kernels::PPArgs& args, int num_sms, cudaStream_t stream);
+
+// Test hook: a one-warp kernel that waits (bounded) for a flag nobody sets and records the status.
+void bounded_wait_probe(layout::CommonSignals* cs, layout::HostStatus* host_status, long long timeout_ns,
+                        cudaStream_t stream);
+
+}  // namespace deep_ep::launch

@@ -1,0 +1,140 @@
+// Launchers for the sm_100a kernels. Persistent kernels that synchronise their CTAs are launched
+// cooperatively so that every CTA is resident; the grid never exceeds the SM count.
+#include <algorithm>
+#include <string>
+
+#include <deep_ep/common/exception.hpp>
+#include <deep_ep/kernels/ep_combine.cuh>
+#include <deep_ep/kernels/ep_dispatch.cuh>
+#include <deep_ep/kernels/ep_expand.cuh>
+#include <deep_ep/kernels/misc.cuh>
+
+#include "api.hpp"
+
+namespace deep_ep::launch {
+
+namespace {
+
+constexpr int64_t kSmemBudget = 200 * 1024;   // of the 227 KiB a CTA may opt into
+
+template <typename Kernel, typename Args>
+void launch_kernel(Kernel kernel, const Args& args, int grid, int block, int64_t smem, bool cooperative,
+                   cudaStream_t stream) {
+    if (smem > 48 * 1024)
+        CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid), config.blockDim = dim3(block);
+    config.dynamicSmemBytes = static_cast<size_t>(smem), config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative, attr[0].val.cooperative = cooperative ? 1 : 0;
+    config.attrs = attr, config.numAttrs = 1;
+    CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, args));
+}
+
+int clamp_sms(int num_sms) {
+    int device = 0, count = 0;
+    CUDA_CHECK(cudaGetDevice(&device));
+    CUDA_CHECK(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device));
+    return std::max(1, std::min({num_sms, count, kMaxCtas}));
+}
+
+}  // namespace
+
+PipelineConfig choose_dispatch_config(int token_bytes, int src_row_bytes, int num_topk, int num_experts) {
+    for (int stages : {3, 2}) {
+        for (int warps = 8; warps >= 2; --warps) {
+            const auto bytes = kernels::dispatch_detail::smem_bytes(warps, stages, num_topk, num_experts, token_bytes, src_row_bytes);
+            if (bytes <= kSmemBudget and (warps >= 4 or stages == 2)) return {warps, stages, bytes};
+        }
+    }
+    EP_HOST_UNREACHABLE("dispatch message too large for shared memory: " + std::to_string(token_bytes) + " bytes");
+}
+
+PipelineConfig choose_expand_config(int token_bytes, int num_topk, int num_local_experts) {
+    for (int stages : {3, 2}) {
+        for (int warps = 8; warps >= 2; --warps) {
+            const auto bytes = kernels::expand_detail::smem_bytes(warps, stages, num_topk, num_local_experts, token_bytes);
+            if (bytes <= kSmemBudget and (warps >= 4 or stages == 2)) return {warps, stages, bytes};
+        }
+    }
+    EP_HOST_UNREACHABLE("dispatch message too large for shared memory: " + std::to_string(token_bytes) + " bytes");
+}
+
+PipelineConfig choose_combine_config(int token_bytes) {
+    for (int stages : {3, 2}) {
+        for (int warps = 8; warps >= 2; --warps) {
+            const auto bytes = kernels::combine_detail::smem_bytes(warps, stages, token_bytes);
+            if (bytes <= kSmemBudget and (warps >= 4 or stages == 2)) return {warps, stages, bytes};
+        }
+    }
+    EP_HOST_UNREACHABLE("combine message too large for shared memory: " + std::to_string(token_bytes) + " bytes");
+}
+
+void dispatch(kernels::DispatchArgs args, int num_sms, cudaStream_t stream) {
+    const layout::DispatchTokenLayout tl(args.hidden_bytes, args.sf_bytes, args.num_topk);
+    const auto config = choose_dispatch_config(tl.num_bytes(), args.fused_quant ? args.hidden_bytes * 2 : 0,
+                                               args.num_topk, args.num_experts);
+    args.num_warps = config.num_warps, args.num_stages = config.num_stages;
+    launch_kernel(kernels::ep_dispatch_kernel, args, clamp_sms(num_sms), 32 * (config.num_warps + 1),
+                  config.smem_bytes, true, stream);
+}
+
+void dispatch_expand(kernels::ExpandArgs args, int num_sms, cudaStream_t stream) {
+    const layout::DispatchTokenLayout tl(args.hidden_bytes, args.sf_bytes, args.num_topk);
+    const auto config = choose_expand_config(tl.num_bytes(), args.num_topk, args.num_experts / args.num_ranks);
+    args.num_warps = config.num_warps, args.num_stages = config.num_stages;
+    launch_kernel(kernels::ep_dispatch_expand_kernel, args, clamp_sms(num_sms), 32 * config.num_warps,
+                  config.smem_bytes, true, stream);
+}
+
+void combine(kernels::CombineArgs args, int num_sms, cudaStream_t stream) {
+    const layout::CombineTokenLayout tl(args.hidden_bytes, args.num_topk);
+    const auto config = choose_combine_config(tl.num_bytes());
+    args.num_warps = config.num_warps, args.num_stages = config.num_stages;
+    launch_kernel(kernels::ep_combine_kernel, args, clamp_sms(num_sms), 32 * config.num_warps,
+                  config.smem_bytes, true, stream);
+}
+
+void combine_reduce(kernels::CombineReduceArgs args, int num_sms, cudaStream_t stream) {
+    launch_kernel(kernels::ep_combine_reduce_kernel, args, clamp_sms(num_sms), 256, 0, false, stream);
+}
+
+void barrier(const kernels::BarrierArgs& args, cudaStream_t stream) {
+    launch_kernel(kernels::rank_barrier_kernel, args, 1, 32, 0, false, stream);
+}
+
+void engram_fetch(const kernels::EngramFetchArgs& args, int num_sms, cudaStream_t stream) {
+    launch_kernel(kernels::engram_fetch_kernel, args, clamp_sms(num_sms) * 4, 256, 0, false, stream);
+}
+
+void all_gather(const kernels::AllGatherArgs& args, int num_sms, cudaStream_t stream) {
+    launch_kernel(kernels::bucket_all_gather_kernel, args, clamp_sms(num_sms), 512, 0, true, stream);
+}
+
+void pp_send(const kernels::PPArgs& args, int num_sms, cudaStream_t stream) {
+    launch_kernel(kernels::pp_send_kernel, args, clamp_sms(num_sms), 512, 0, true, stream);
+}
+
+void pp_recv(const kernels::PPArgs& args, int num_sms, cudaStream_t stream) {
+    launch_kernel(kernels::pp_recv_kernel, args, clamp_sms(num_sms), 512, 0, true, stream);
+}
+
+namespace {
+
+__global__ void bounded_wait_probe_kernel(layout::CommonSignals* cs, layout::HostStatus* hs, long long timeout_ns) {
+    // waits for a generation change that no one produces; must give up and record a status
+    const unsigned gen = ptx::ld_acquire_gpu(&cs->grid_gen);
+    const dev::Deadline deadline(timeout_ns);
+    const bool ok = dev::spin_until(deadline, [&]() { return ptx::ld_acquire_gpu(&cs->grid_gen) != gen; });
+    if (not ok) dev::report_status(cs, hs, kStatusGridSyncTimeout, -1, -1, /*where=*/99, gen + 1, gen);
+}
+
+}  // namespace
+
+void bounded_wait_probe(layout::CommonSignals* cs, layout::HostStatus* host_status, long long timeout_ns,
+                        cudaStream_t stream) {
+    bounded_wait_probe_kernel<<<1, 1, 0, stream>>>(cs, host_status, timeout_ns);
+    CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace deep_ep::launch

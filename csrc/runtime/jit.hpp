@@ -1,0 +1,146 @@
+// Runtime kernel specialisation (the role DeepJIT plays for the reference, `csrc/runtime/jit.hpp:15-118`):
+// generate a small translation unit that instantiates a kernel template with compile-time constants,
+// compile it with nvcc for sm_100a into a cubin, cache it on disk by content hash, load it through
+// the driver API and launch it. The ahead-of-time kernels linked into this extension remain the
+// default path; the JIT is for specialisations chosen at run time.
+#pragma once
+
+#include <cuda.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cstdlib>
+#include <filesystem>
+#include <fstream>
+#include <functional>
+#include <map>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include <deep_ep/common/exception.hpp>
+
+namespace deep_ep::jit {
+
+// `EP_JIT_<NAME>` with `DJ_JIT_<NAME>` as fallback (the reference's environment contract).
+inline std::string get_env(const std::string& name, const std::string& fallback = "") {
+    for (const char* prefix : {"EP_JIT_", "DJ_JIT_"}) {
+        const char* v = std::getenv((std::string(prefix) + name).c_str());
+        if (v != nullptr and *v != '\0') return v;
+    }
+    return fallback;
+}
+inline bool get_env_flag(const std::string& name) {
+    const auto v = get_env(name, "0");
+    return v != "0" and v != "false" and v != "False";
+}
+
+inline uint64_t fnv1a(const std::string& s, uint64_t h = 1469598103934665603ull) {
+    for (const unsigned char c : s) h = (h ^ c) * 1099511628211ull;
+    return h;
+}
+
+class Compiler {
+    std::string package_dir;
+    std::map<std::string, CUfunction> loaded;     // cache key -> function
+    std::vector<CUmodule> modules;
+    std::mutex mutex;
+
+    std::string cache_dir() const {
+        auto dir = get_env("CACHE_DIR");
+        if (dir.empty()) {
+            const char* home = std::getenv("HOME");
+            dir = std::string(home != nullptr ? home : "/tmp") + "/.deep_ep_b200/cache";
+        }
+        std::filesystem::create_directories(dir);
+        return dir;
+    }
+
+public:
+    static Compiler& get() {
+        static Compiler instance;
+        return instance;
+    }
+
+    void init(const std::string& dir) { package_dir = dir; }
+    const std::string& get_package_dir() const { return package_dir; }
+    std::string include_dir() const { return package_dir + "/include"; }
+
+    std::string nvcc_path() const {
+        auto p = get_env("NVCC");
+        if (not p.empty()) return p;
+        const char* home = std::getenv("CUDA_HOME");
+        return std::string(home != nullptr ? home : "/usr/local/cuda") + "/bin/nvcc";
+    }
+
+    // Compile `source` (a full translation unit) to a cubin; returns the cubin path. Cached by hash
+    // of source + flags + arch.
+    std::string compile(const std::string& name, const std::string& source, const std::string& arch = "sm_100a") {
+        EP_HOST_ASSERT_MSG(not package_dir.empty(), "init_jit(package_dir) has not been called");
+        std::string flags = "-std=c++20 -O3 --expt-relaxed-constexpr -cubin";
+        if (get_env_flag("KERNEL_DEBUG_INFO")) flags += " -lineinfo";
+        const std::string arch_num = arch.substr(3);
+        flags += " -gencode arch=compute_" + arch_num + ",code=" + arch + " -I" + include_dir();
+        std::ostringstream key;
+        key << std::hex << fnv1a(source, fnv1a(flags));
+        const auto dir = cache_dir() + "/" + name + "-" + key.str();
+        const auto cubin = dir + "/kernel.cubin";
+        if (std::filesystem::exists(cubin)) return cubin;
+        std::filesystem::create_directories(dir);
+        {
+            std::ofstream out(dir + "/kernel.cu");
+            out << source;
+        }
+        const auto tmp = cubin + ".tmp." + std::to_string(::getpid());
+        const auto command = nvcc_path() + " " + flags + " " + dir + "/kernel.cu -o " + tmp + " > " + dir + "/nvcc.log 2>&1";
+        if (get_env_flag("PRINT_COMPILER_COMMAND") or get_env_flag("DEBUG")) std::fprintf(stderr, "[deep_ep jit] %s\n", command.c_str());
+        const int rc = std::system(command.c_str());
+        if (rc != 0) {
+            std::ifstream log(dir + "/nvcc.log");
+            std::stringstream text;
+            text << log.rdbuf();
+            throw EPException("JIT compile", __FILE__, __LINE__, name + ": nvcc failed\n" + text.str());
+        }
+        std::filesystem::rename(tmp, cubin);     // atomic publish: concurrent ranks may race on the same key
+        return cubin;
+    }
+
+    // Load (once) and return the kernel `symbol` of a compiled cubin.
+    CUfunction load(const std::string& cubin, const std::string& symbol) {
+        std::lock_guard<std::mutex> guard(mutex);
+        const auto key = cubin + "::" + symbol;
+        auto it = loaded.find(key);
+        if (it != loaded.end()) return it->second;
+        CUmodule module;
+        CU_CHECK(cuModuleLoad(&module, cubin.c_str()));
+        modules.push_back(module);
+        CUfunction fn;
+        CU_CHECK(cuModuleGetFunction(&fn, module, symbol.c_str()));
+        loaded[key] = fn;
+        return fn;
+    }
+
+    void launch(CUfunction fn, int grid, int block, int smem_bytes, CUstream stream, std::vector<void*>& args, bool cooperative = false) {
+        if (smem_bytes > 48 * 1024)
+            CU_CHECK(cuFuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, smem_bytes));
+        CUlaunchConfig config = {};
+        config.gridDimX = grid, config.gridDimY = 1, config.gridDimZ = 1;
+        config.blockDimX = block, config.blockDimY = 1, config.blockDimZ = 1;
+        config.sharedMemBytes = smem_bytes, config.hStream = stream;
+        CUlaunchAttribute attr[1];
+        attr[0].id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE, attr[0].value.cooperative = cooperative ? 1 : 0;
+        config.attrs = attr, config.numAttrs = 1;
+        CU_CHECK(cuLaunchKernelEx(&config, fn, args.data(), nullptr));
+    }
+};
+
+inline void register_python_api(pybind11::module_& m) {
+    m.def("init_jit", [](const std::string& package_dir) { Compiler::get().init(package_dir); });
+    m.def("jit_compile", [](const std::string& name, const std::string& source, const std::string& arch) {
+        return Compiler::get().compile(name, source, arch);
+    }, pybind11::arg("name"), pybind11::arg("source"), pybind11::arg("arch") = "sm_100a");
+    m.def("jit_include_dir", [] { return Compiler::get().include_dir(); });
+}
+
+}  // namespace deep_ep::jit

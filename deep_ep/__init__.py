@@ -1,0 +1,45 @@
+"""deep_ep for NVIDIA B200: expert-parallel dispatch/combine, pipeline send/recv, batched all-gather
+and remote embedding gathers over NVLink peer memory. Public surface of the reference's
+`deep_ep/__init__.py:26-40`."""
+import os
+
+import torch
+
+# Environment defaults persisted at build time never override the caller's environment.
+try:
+    from .envs import persistent_envs
+    for _key, _value in persistent_envs.items():
+        os.environ.setdefault(_key, _value)
+except ImportError:
+    pass
+
+from ._C_loader import _C
+
+
+def init_jit() -> None:
+    """Point the runtime kernel compiler at this package (its `include/` tree ships with the package)."""
+    _C.init_jit(os.path.dirname(os.path.abspath(__file__)))
+
+
+init_jit()
+
+from . import comm
+from .comm import (destroy_all_managed_comm, destroy_all_managed_hccl_comm, get_logical_domain_size,
+                   get_physical_domain_size)
+from .buffers.allocator import BufferAllocator
+from .buffers.base import BufferBase
+from .buffers.ep import EPBuffer, EPHandle
+from .buffers.engram import EngramBuffer
+from .buffers.bucket import BucketBuffer, BucketSession
+from .buffers.pp import PPBuffer
+from .utils.event import EventOverlap, EventHandle
+from .utils.envs import init_seed, get_local_seed, get_global_seed, dist_print, init_dist
+from .utils.testing import KernelProfile, bench, bench_kineto, bench_msprof
+
+get_num_allocation_alignment = _C.get_num_allocation_alignment
+get_num_rdma_alignment = _C.get_num_rdma_alignment
+get_num_tma_alignment = _C.get_num_tma_alignment
+topk_idx_t = _C.topk_idx_t
+EPException = _C.EPException
+
+__version__ = '1.0.0'

@@ -1,0 +1,54 @@
+"""Lifecycle shared by all communication buffers (reference: `deep_ep/buffers/base.py:4-27`)."""
+from abc import ABC, abstractmethod
+from typing import List
+
+import torch
+import torch.distributed as dist
+
+
+class BufferBase(ABC):
+    """Holds the native runtime object and enforces the explicit-destroy contract."""
+
+    def __init__(self, explicitly_destroy: bool = False):
+        self.explicitly_destroy = explicitly_destroy
+        self.runtime = None
+
+    @property
+    def main_context(self):
+        """The first communication context, or `None` once destroyed."""
+        return None if self.runtime is None else self.runtime.main_context
+
+    def print_memory_usage(self) -> None:
+        """Print workspace / buffer / storage bytes of this rank."""
+        assert self.runtime is not None
+        self.runtime.print_memory_usage()
+
+    @abstractmethod
+    def destroy(self) -> None:
+        """Collective teardown; only legal for buffers created with `explicitly_destroy=True`."""
+        assert self.explicitly_destroy, '`destroy()` requires `explicitly_destroy=True` at construction'
+        if self.runtime is not None:
+            self.runtime.destroy()
+            self.runtime = None
+
+
+def connect_peers(context, group: dist.ProcessGroup) -> None:
+    """Exchange the CUDA-IPC handles of a context's symmetric allocation over `group` and map the peers.
+
+    Plays the role of the reference's channel bring-up (`csrc/kernels/comm/hccl.hpp:173-331`): afterwards
+    every rank holds a device-usable base address for every peer's allocation.
+    """
+    if group.size() == 1 or context.peers_ready:
+        return
+    handles: List[bytes] = [b''] * group.size()
+    dist.all_gather_object(handles, context.get_local_handle(), group)
+    context.set_peer_handles(handles)
+
+
+def sync_group(group: dist.ProcessGroup) -> None:
+    """Device sync, process-group barrier, device sync: construction is complete on every rank afterwards."""
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    dist.barrier(group)
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()

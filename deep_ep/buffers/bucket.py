@@ -1,0 +1,225 @@
+"""`BucketBuffer` and `BucketSession`: batched all-gather over registered storage
+(reference: `deep_ep/buffers/bucket.py:19-356`)."""
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple, Union
+
+import torch
+import torch.distributed as dist
+
+from .. import comm
+from .._C_loader import _C
+from ..utils.event import EventOverlap
+from ..utils.math import align
+from .allocator import BufferAllocator
+from .base import BufferBase, connect_peers
+
+
+class BucketSession:
+    """Context manager under which the buffer's collectives accept tensors that live outside its storage.
+
+    Inside a session a bump allocator (32-byte aligned, restarting at offset 0 on entry) hands out
+    registered regions; outputs requested outside the storage are produced in such a region and copied to
+    the caller's tensor inside the wait hook, which then returns the caller's tensor. One group per
+    session; sessions do not nest; the buffer's methods are restored on exit even after an exception;
+    leaving a session adds no barrier.
+    """
+
+    _ALIGNMENT = 32
+
+    def __init__(self, buffer: 'BucketBuffer'):
+        self.buffer = buffer
+        self.offset = 0
+        self.group: Optional[dist.ProcessGroup] = None
+        self._saved: Dict[str, Any] = {}
+
+    def __enter__(self) -> 'BucketSession':
+        assert self.buffer._active_session is None, 'BucketBuffer sessions cannot be nested'
+        self.buffer._active_session = self
+        self.offset, self.group = 0, None
+        for name in ('all_gather', 'reduce_scatter', 'all_reduce'):
+            self._saved[name] = getattr(self.buffer, name)
+        self.buffer.all_gather = self._all_gather
+        return self
+
+    def __exit__(self, exc_type, exc_val, exc_tb) -> None:
+        for name in self._saved:
+            if name in self.buffer.__dict__:
+                del self.buffer.__dict__[name]
+        self._saved.clear()
+        self.buffer._active_session = None
+
+    def _bind_group(self, group: Optional[dist.ProcessGroup]) -> dist.ProcessGroup:
+        group = self.buffer.groups[self.buffer.get_context_idx(group)]
+        assert self.group is None or self.group is group, 'a session is bound to the first group it used'
+        self.group = group
+        return group
+
+    def _carve(self, num_bytes: int) -> torch.Tensor:
+        start = align(self.offset, self._ALIGNMENT)
+        assert start + num_bytes <= self.buffer.storage.numel(), 'BucketBuffer storage exhausted in this session'
+        self.offset = start + num_bytes
+        return self.buffer.storage.narrow(0, start, num_bytes)
+
+    def allocate(self, shape, dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None):
+        """Registered tensor(s) of `shape` (or a list of shapes) inside the storage."""
+        self._bind_group(group)
+        def one(s):
+            numel = 1
+            for d in (s if isinstance(s, (tuple, list, torch.Size)) else (s,)):
+                numel *= d
+            return self._carve(numel * dtype.itemsize).view(dtype).view(s)
+        if isinstance(shape, (list, tuple)) and shape and isinstance(shape[0], (list, tuple, torch.Size)):
+            return [one(s) for s in shape]
+        return one(shape)
+
+    def _inside(self, t: torch.Tensor) -> bool:
+        base = self.buffer.storage.data_ptr()
+        return base <= t.data_ptr() and t.data_ptr() + t.nbytes <= base + self.buffer.storage.numel()
+
+    def _all_gather(self, srcs, dsts=None, group: Optional[dist.ProcessGroup] = None, num_sms: Optional[int] = None):
+        group = self._bind_group(group)
+        is_packed, srcs, dsts = BucketBuffer._pack_tensors(srcs, dsts)
+        size, rank = group.size(), group.rank()
+        inner_dsts: List[torch.Tensor] = []
+        copy_back: List[Tuple[torch.Tensor, int]] = []
+        for i, src in enumerate(srcs):
+            user_dst = dsts[i] if dsts else None
+            if user_dst is None and self._inside(src):
+                # in-place form: src already is this rank's shard of a registered gathered tensor
+                offset = src.data_ptr() - self.buffer.storage.data_ptr() - rank * src.nbytes
+                inner_dsts.append(self.buffer.storage.narrow(0, offset, size * src.nbytes).view(src.dtype))
+            elif user_dst is not None and self._inside(user_dst):
+                inner_dsts.append(user_dst)
+            else:
+                staged = self._carve(size * src.nbytes).view(src.dtype)
+                inner_dsts.append(staged)
+                if user_dst is not None:
+                    assert user_dst.nbytes == size * src.nbytes and user_dst.dtype == src.dtype
+                    copy_back.append((user_dst, i))
+        handle = self._saved['all_gather'](srcs, inner_dsts, group=group, num_sms=num_sms)
+        inner_hook = handle.hook_after_wait
+        handle.hook_after_wait = None
+        external = {i: t for t, i in copy_back}
+
+        def hook():
+            gathered = inner_hook()
+            gathered = [gathered] if isinstance(gathered, torch.Tensor) else list(gathered)
+            for i, user_dst in external.items():
+                user_dst.view(-1).copy_(gathered[i].view(-1))
+                gathered[i] = user_dst
+            return gathered[0] if is_packed else gathered
+        handle.register_hook_after_wait(hook)
+        return handle
+
+
+class BucketBuffer(BufferBase):
+    """Contiguous symmetric storage registered with one to eight process groups.
+
+    Stream usage: communication runs on the communication stream; epilogues run on the current stream.
+    """
+
+    get_comm_stream = comm.get_comm_stream
+
+    @staticmethod
+    def _pack_tensors(*tensors):
+        """Normalise `tensor | sequence | None` arguments to lists; report whether a bare tensor was given."""
+        is_packed = isinstance(tensors[0], torch.Tensor)
+        lists = tuple([] if t is None else [t] if isinstance(t, torch.Tensor) else list(t) for t in tensors)
+        assert all(len(item) in (0, len(lists[0])) for item in lists)
+        return is_packed, *lists
+
+    def __init__(self, group: Union[dist.ProcessGroup, Sequence[dist.ProcessGroup]],
+                 allocation_plan_or_num_bytes: Union[BufferAllocator, int], sl_idx: Optional[int] = None,
+                 num_gpu_timeout_secs: int = 100, explicitly_destroy: bool = False, *, use_huge1g_page: bool = True):
+        plan = allocation_plan_or_num_bytes if isinstance(allocation_plan_or_num_bytes, BufferAllocator) else None
+        num_bytes = allocation_plan_or_num_bytes if plan is None else plan.num_bytes
+        if plan is not None:
+            assert not plan.materialized
+        assert isinstance(num_bytes, int) and num_bytes > 0 and num_gpu_timeout_secs > 0
+        self.groups = [group] if isinstance(group, dist.ProcessGroup) else list(group)
+        assert self.groups and len(self.groups) <= _C.MAX_CONTEXTS
+        assert len(set(self.groups)) == len(self.groups), 'Duplicate communication groups'
+        assert num_bytes % _C.get_num_allocation_alignment() == 0
+        if sl_idx is not None:
+            raise NotImplementedError('RDMA service levels do not exist on NVLink')
+        self.comm_handles = [comm.get_comm_handle(g) for g in self.groups]
+        for context_idx, g in enumerate(self.groups):
+            seen = [None] * g.size()
+            dist.all_gather_object(seen, context_idx, g)
+            assert all(i == context_idx for i in seen), 'All ranks must use the same context index within a group'
+        self.num_bytes = num_bytes
+        self._active_session: Optional[BucketSession] = None
+        super().__init__(explicitly_destroy)
+        self.runtime = _C.BucketBuffer([g.rank() for g in self.groups], [g.size() for g in self.groups],
+                                       [h.get() for h in self.comm_handles], num_bytes, use_huge1g_page,
+                                       num_gpu_timeout_secs, explicitly_destroy)
+        self.contexts = self.runtime.contexts
+        for context, g in zip(self.contexts, self.groups):
+            connect_peers(context, g)
+        self.storage = self.runtime.storage
+        torch.cuda.synchronize()
+        for g in self.groups:
+            dist.barrier(g)
+        torch.cuda.synchronize()
+        if plan is not None:
+            plan.materialize(self.storage)
+
+    @property
+    def context(self):
+        return self.contexts[0] if self.contexts else None
+
+    def get_theoretical_num_sms(self, op: str, group: Optional[dist.ProcessGroup] = None) -> int:
+        self.get_context_idx(group)
+        if op == 'all_gather':
+            return 0
+        if op in ('reduce_scatter', 'all_reduce'):
+            return _C.get_num_sms()
+        raise NotImplementedError(op)
+
+    def get_context_idx(self, group: Optional[dist.ProcessGroup]) -> int:
+        assert len(self.groups) == 1 or group is not None, '`group` is required when the buffer has multiple groups'
+        return 0 if group is None else self.groups.index(group)
+
+    def session(self) -> BucketSession:
+        """Open a session in which collectives accept unregistered tensors."""
+        return BucketSession(self)
+
+    def barrier(self, wait_comm_stream: bool = True, with_cpu_sync: bool = False, sequential: bool = True,
+                group: Optional[dist.ProcessGroup] = None) -> None:
+        """Device barrier over the selected group."""
+        comm.barrier(self, wait_comm_stream, with_cpu_sync, sequential, self.get_context_idx(group))
+
+    def reduce_scatter(self, srcs, comm_precision: str = 'fp32', scale: float = 1.0,
+                       group: Optional[dist.ProcessGroup] = None, num_sms: Optional[int] = None) -> EventOverlap:
+        """Batched reduce-scatter (API of the reference, whose native kernel is also absent)."""
+        raise NotImplementedError('BucketBuffer.reduce_scatter is not implemented')
+
+    def all_reduce(self, srcs, scale: float = 1.0, group: Optional[dist.ProcessGroup] = None,
+                   num_sms: Optional[int] = None) -> EventOverlap:
+        """Batched in-place all-reduce (API of the reference, whose native kernel is also absent)."""
+        raise NotImplementedError('BucketBuffer.all_reduce is not implemented')
+
+    def all_gather(self, srcs: Union[torch.Tensor, Sequence[torch.Tensor]],
+                   dsts: Optional[Union[torch.Tensor, Sequence[torch.Tensor]]] = None,
+                   group: Optional[dist.ProcessGroup] = None, num_sms: Optional[int] = None) -> EventOverlap:
+        """Launch a batched all-gather of up to 64 tensors on the communication stream.
+
+        Without `dsts` each `src` must be this rank's shard *inside* the storage and the gather is in place.
+        With `dsts`, each `dst` lies in the storage with `dst.nbytes == group.size() * src.nbytes` and `src` may be
+        any contiguous device tensor of the same dtype. All ranks pass equal shard sizes.
+        `handle.wait()` is where completion is guaranteed; it returns flat 1-D views of the gathered tensors
+        (a single tensor if a single tensor was passed).
+        """
+        is_packed, srcs, dsts = self._pack_tensors(srcs, dsts)
+        context_idx = self.get_context_idx(group)
+        assert num_sms in (None, 0) or num_sms > 0
+        event, epilogue, used_sms = self.runtime.all_gather(srcs, dsts, context_idx, 0 if num_sms is None else num_sms)
+        handle = EventOverlap(event, extra_tensors=tuple(srcs) + tuple(dsts) + (self.storage,))
+        handle.register_hook_after_wait(lambda: epilogue()[0] if is_packed else epilogue())
+        setattr(handle, 'num_sms', 0 if num_sms is None else num_sms)
+        return handle
+
+    def destroy(self) -> None:
+        super().destroy()
+        self.contexts = None
+        self.storage = None
+        self.comm_handles = None

@@ -1,0 +1,54 @@
+"""`PPBuffer`: buffered send/recv between ring neighbours (reference: `deep_ep/buffers/pp.py:13-86`)."""
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import comm
+from .._C_loader import _C
+from .base import BufferBase, connect_peers, sync_group
+
+
+class PPBuffer(BufferBase):
+    """Symmetric ring storage for pipeline-parallel activations.
+
+    `send` returns (on the stream) once the payload sits in the neighbour's landing slot; up to
+    `num_max_inflight_tensors` sends per direction may run ahead of the matching `recv`. Messages
+    between a pair are FIFO and carry no header: sender and receiver agree on sizes by convention.
+
+    Stream usage: every operation runs on the current stream.
+    """
+
+    barrier = comm.barrier
+    get_comm_stream = comm.get_comm_stream
+
+    def __init__(self, group: dist.ProcessGroup, num_max_tensor_bytes: int, num_max_inflight_tensors: int,
+                 sl_idx: Optional[int] = None, num_gpu_timeout_secs: int = 100, explicitly_destroy: bool = False,
+                 *, use_huge1g_page: bool = True):
+        if sl_idx is not None:
+            raise NotImplementedError('RDMA service levels do not exist on NVLink')
+        assert num_max_tensor_bytes > 0 and num_max_inflight_tensors > 0 and num_gpu_timeout_secs > 0
+        self.group = group
+        self.rank_idx, self.num_ranks = group.rank(), group.size()
+        self.comm_handle = comm.get_comm_handle(group)
+        super().__init__(explicitly_destroy)
+        self.runtime = _C.PPBuffer(self.rank_idx, self.num_ranks, self.comm_handle.get(), num_max_tensor_bytes,
+                                   num_max_inflight_tensors, use_huge1g_page, num_gpu_timeout_secs, explicitly_destroy)
+        connect_peers(self.runtime.context, group)
+        self.context = self.runtime.context
+        self.storage = self.runtime.storage
+        sync_group(group)
+
+    def send(self, x: torch.Tensor, dst_rank_idx: int, num_sms: Optional[int] = None) -> None:
+        """Send contiguous `x` (at most `num_max_tensor_bytes`) to the previous or next rank of the ring."""
+        self.runtime.send(x, dst_rank_idx, 0 if num_sms is None else num_sms)
+
+    def recv(self, x: torch.Tensor, src_rank_idx: int, num_sms: Optional[int] = None) -> None:
+        """Receive into contiguous `x` from the previous or next rank of the ring."""
+        self.runtime.recv(x, src_rank_idx, 0 if num_sms is None else num_sms)
+
+    def destroy(self) -> None:
+        super().destroy()
+        self.storage = None
+        self.context = None
+        self.comm_handle = None

@@ -1,0 +1,100 @@
+// Bounded waits, the sticky status word, the grid-wide sync of persistent kernels and the
+// cross-rank barrier. Role of the reference's `comm/barrier.hpp:27-179` and `common/reduction.hpp`,
+// with one difference that matters on shared GPUs: a wait that runs out records a status code and
+// returns false; nothing traps.
+#pragma once
+
+#include "../layout/signals.hpp"
+#include "ptx.cuh"
+
+namespace deep_ep::dev {
+
+struct Deadline {
+    unsigned long long end_ns;
+    EP_DEVICE explicit Deadline(long long timeout_ns) : end_ns(ptx::globaltimer_ns() + static_cast<unsigned long long>(timeout_ns)) {}
+    EP_DEVICE bool expired() const { return ptx::globaltimer_ns() > end_ns; }
+};
+
+// Spin on `pred()` until true or the deadline passes; the timer is read every 128 polls.
+template <typename Pred>
+EP_DEVICE bool spin_until(const Deadline& deadline, Pred pred) {
+    while (true) {
+        #pragma unroll 1
+        for (int i = 0; i < 128; ++i)
+            if (pred()) return true;
+        if (deadline.expired()) return pred();
+    }
+}
+
+// First failure wins; details go to mapped host memory (may be nullptr).
+EP_DEVICE void report_status(layout::CommonSignals* cs, layout::HostStatus* hs, int code, int rank, int peer,
+                             int where, long long expected, long long observed) {
+    if (atomicCAS(&cs->status, 0, code) == 0 and hs != nullptr) {
+        hs->rank = rank, hs->peer = peer, hs->where = where;
+        hs->expected = expected, hs->observed = observed;
+        __threadfence_system();
+        hs->code = code;
+    }
+}
+
+EP_DEVICE bool healthy(const layout::CommonSignals* cs) {
+    return ptx::ld_relaxed_gpu(&cs->status) == 0;
+}
+
+// Grid-wide sync for kernels whose CTAs are all resident (cooperative launch). Returns false on
+// timeout or when another CTA has already failed.
+EP_DEVICE bool grid_sync(layout::CommonSignals* cs, layout::HostStatus* hs, int num_ctas, long long timeout_ns,
+                         int rank, int where) {
+    __shared__ int ok_smem;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        bool ok = true;
+        if (num_ctas > 1) {
+            const unsigned gen = ptx::ld_acquire_gpu(&cs->grid_gen);
+            __threadfence();
+            if (atomicAdd(&cs->grid_count, 1u) == static_cast<unsigned>(num_ctas - 1)) {
+                cs->grid_count = 0;
+                __threadfence();
+                ptx::st_release_gpu(&cs->grid_gen, gen + 1);
+            } else {
+                const Deadline deadline(timeout_ns);
+                ok = spin_until(deadline, [&]() { return ptx::ld_acquire_gpu(&cs->grid_gen) != gen or not healthy(cs); });
+                if (not ok)
+                    report_status(cs, hs, kStatusGridSyncTimeout, rank, -1, where, gen + 1, cs->grid_gen);
+            }
+        }
+        ok_smem = ok and healthy(cs);
+    }
+    __syncthreads();
+    return ok_smem != 0;
+}
+
+// Cross-rank barrier executed by one warp of one CTA. Call n uses phase n&1 and sign +1/-1
+// alternating every two calls, so the signal swings 0 -> N -> 0 and never needs a reset
+// (the scheme of the reference's `comm/barrier.hpp:141-175`). All prior writes of the calling
+// thread block that were ordered before this call (e.g. by `__syncthreads`) are released.
+EP_DEVICE bool rank_barrier_warp(layout::CommonSignals* cs, layout::HostStatus* hs, const layout::PeerTable& peers,
+                                 long long timeout_ns, int where) {
+    const int lane = ptx::lane_id();
+    int n = 0;
+    if (lane == 0) n = cs->barrier_counter;
+    n = __shfl_sync(0xffffffffu, n, 0);
+    const int phase = n & 1, sign = (n & 2) ? -1 : 1;
+    __threadfence_system();
+    for (int r = lane; r < peers.num_ranks; r += 32)
+        ptx::red_add_release_sys(&peers.sym(cs, r)->barrier_signals[phase], sign);
+    const int target = sign > 0 ? peers.num_ranks : 0;
+    bool ok = true;
+    if (lane == 0) {
+        const Deadline deadline(timeout_ns);
+        ok = spin_until(deadline, [&]() { return ptx::ld_acquire_sys(&cs->barrier_signals[phase]) == target; });
+        if (not ok)
+            report_status(cs, hs, kStatusBarrierTimeout, peers.rank, -1, where, target, cs->barrier_signals[phase]);
+        cs->barrier_counter = n + 1;
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __threadfence_system();
+    return ok;
+}
+
+}  // namespace deep_ep::dev

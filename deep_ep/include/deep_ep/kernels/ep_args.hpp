@@ -1,0 +1,118 @@
+// Plain-data argument blocks of the expert-parallel kernels and their shared-memory sizing, usable
+// from the host runtime (g++) and from device code. The kernels themselves live in the `.cuh` files
+// next to this header.
+#pragma once
+
+#include "../layout/ep.hpp"
+
+namespace deep_ep::kernels {
+
+struct DispatchArgs {
+    // inputs
+    const uint8_t* x;               // [T, row_bytes]: wire bytes, or BF16 source rows when fused_quant
+    const sf_pack_t* sf;            // [T, sf_bytes / 2] packs with strides below, or nullptr
+    int64_t sf_token_stride, sf_pack_stride;
+    const int64_t* topk_idx;        // [T, k]
+    const float* topk_weights;      // [T, k] or nullptr
+    int num_tokens, hidden_bytes, sf_bytes, num_topk, num_experts, num_max_tokens, expert_alignment;
+    int cached, fused_quant, do_cpu_sync, wait_arrival;
+    // handle tensors
+    int* dst_slot_idx;              // [T, k]
+    int* psum_rank;                 // [R]
+    int* psum_expert;               // [E_local]
+    int* num_unaligned;             // [E_local]
+    int* cumulative_stats;          // [E_local] or nullptr
+    // communication
+    layout::EPSignals* ws;
+    int64_t buffer_offset;          // receive buffer offset inside the symmetric allocation
+    layout::PeerTable peers;
+    layout::EPHostCounts* host;
+    long long timeout_ns;
+    int num_warps, num_stages;      // pusher warps per CTA, message stages per warp
+};
+
+struct ExpandArgs {
+    layout::EPSignals* ws;
+    const uint8_t* buffer;            // local receive buffer ([source rank][max tokens] messages)
+    layout::EPHostCounts* host;
+    const int* psum_rank;             // [R] inclusive
+    const int* psum_expert;           // [E_local]
+    const int* num_unaligned;         // [E_local]
+    uint8_t* recv_x;                  // [num_expanded, hidden_bytes]
+    sf_pack_t* recv_sf;               // strided, or nullptr
+    int64_t recv_sf_token_stride, recv_sf_pack_stride;
+    float* recv_topk_weights;         // [num_expanded] or nullptr
+    int* recv_src_metadata;           // [num_recv_rows, k + 2]
+    int num_metadata_rows, num_expanded_rows;   // capacities of the output tensors
+    int rank, num_ranks, num_max_tokens, num_experts, num_topk, expert_alignment;
+    int hidden_bytes, sf_bytes;
+    int cached, do_zero_padding, wait_arrival;
+    long long timeout_ns;
+    int num_warps, num_stages;
+};
+
+struct CombineArgs {
+    const uint8_t* x;                 // [num_expanded, hidden_bytes] bf16
+    const float* topk_weights;        // [num_expanded] or nullptr
+    const int* recv_src_metadata;     // [rows, k + 2]
+    const int* psum_rank;             // [R]
+    int num_metadata_rows;
+    int num_topk, num_max_tokens, hidden_bytes;
+    int wait_arrival;
+    layout::EPSignals* ws;
+    int64_t buffer_offset;
+    layout::PeerTable peers;
+    layout::EPHostCounts* host;
+    long long timeout_ns;
+    int num_warps, num_stages;
+};
+
+struct CombineReduceArgs {
+    layout::EPSignals* ws;
+    const uint8_t* buffer;            // local landing buffer
+    layout::EPHostCounts* host;
+    const int64_t* topk_idx;          // [T, k]
+    const uint8_t* bias_0;            // [T, hidden_bytes] bf16 or nullptr
+    const uint8_t* bias_1;
+    uint8_t* combined_x;              // [T, hidden_bytes]
+    float* combined_topk_weights;     // [T, k] or nullptr
+    int num_tokens, num_topk, num_experts, num_max_tokens, hidden_bytes;
+    int rank, num_ranks;
+    int wait_arrival;
+    long long timeout_ns;
+};
+
+namespace dispatch_detail {
+EP_HOST_DEVICE int64_t smem_bytes(int num_warps, int num_stages, int num_topk, int num_experts, int token_bytes,
+                                  int src_row_bytes) {
+    int64_t n = 0;
+    n += int64_t(num_warps) * (num_stages + 2) * 8;
+    n += int64_t(num_warps) * kMaxRanks * 4 * 2;
+    n += int64_t(num_experts) * 4;
+    n += int64_t(num_warps) * 32 * num_topk * 4;
+    n = math::align<int64_t>(n, 128);
+    n += int64_t(num_warps) * num_stages * token_bytes;
+    n = math::align<int64_t>(n, 128);
+    n += int64_t(num_warps) * 2 * src_row_bytes;
+    return n + 128;
+}
+}  // namespace dispatch_detail
+
+namespace expand_detail {
+EP_HOST_DEVICE int64_t smem_bytes(int num_warps, int num_stages, int num_topk, int num_local_experts, int token_bytes) {
+    int64_t n = int64_t(num_warps) * num_stages * 8;
+    n += int64_t(num_warps) * num_local_experts * 4 * 2;      // running bases + hit bitmaps
+    n += int64_t(num_warps) * 32 * (num_topk + 1) * 4;        // slots (+ source row index)
+    n = math::align<int64_t>(n, 128);
+    n += int64_t(num_warps) * num_stages * token_bytes;
+    return n + 128;
+}
+}  // namespace expand_detail
+
+namespace combine_detail {
+EP_HOST_DEVICE int64_t smem_bytes(int num_warps, int num_stages, int token_bytes) {
+    return int64_t(num_warps) * num_stages * 8 + 128 + int64_t(num_warps) * num_stages * token_bytes + 128;
+}
+}  // namespace combine_detail
+
+}  // namespace deep_ep::kernels

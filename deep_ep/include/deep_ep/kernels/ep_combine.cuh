@@ -1,0 +1,277 @@
+// Expert-parallel combine for sm_100a.
+//   `ep_combine_kernel` (issue): for every token this rank received, gather its expanded rows,
+//       reduce them in fp32 in top-k order, round once to bf16 and push the partial (plus the
+//       positionally routed top-k weights) into the owner rank's landing buffer with one
+//       `cp.async.bulk` store. Single-row tokens go global -> shared -> peer without touching registers.
+//   `ep_combine_reduce_kernel` (epilogue): after every peer's "push finished" flag, the owner sums
+//       bias + partials in top-k slot order in fp32 and rounds once to bf16.
+// Roles of the reference's `impls/ep/combine.hpp:25-364` and `impls/ep/combine_reduce_epilogue.hpp:19-155`;
+// the accumulation order is the one its oracle demands bit for bit (`deep_ep/utils/refs.py:178-247`).
+#pragma once
+
+#include "../device/sync.cuh"
+#include "ep_args.hpp"
+#include "ep_dispatch.cuh"
+
+namespace deep_ep::kernels {
+
+
+
+namespace combine_detail {
+
+constexpr int kSiteEntryBarrier = 30, kSiteGridSync = 31, kSiteLoad = 32, kSiteArrival = 33;
+constexpr int kUnroll = 8;
+
+
+EP_DEVICE void accumulate(float (&acc)[8], const int4& v) {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = ptx::bf16x2_to_float2(w[i]);
+        acc[2 * i] += f.x, acc[2 * i + 1] += f.y;
+    }
+}
+
+EP_DEVICE int4 pack(const float (&acc)[8]) {
+    int4 out;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&out);
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = ptx::float2_to_bf16x2(acc[2 * i], acc[2 * i + 1]);
+    return out;
+}
+
+// index (0-based) of the q-th set bit of m; requires q < popc(m)
+EP_DEVICE int nth_set_bit(unsigned m, int q) { return __fns(m, 0, q + 1); }
+
+}  // namespace combine_detail
+
+__global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_constant__ CombineArgs a) {
+    using namespace combine_detail;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int psum_rank_smem[kMaxRanks];
+
+    const int num_ranks = a.peers.num_ranks, rank = a.peers.rank;
+    const int num_ctas = gridDim.x, cta = blockIdx.x;
+    const int warp = threadIdx.x / 32, lane = ptx::lane_id();
+    const int W = a.num_warps, S = a.num_stages, k = a.num_topk;
+    layout::CommonSignals* cs = &a.ws->common;
+    layout::HostStatus* hs = a.host ? &a.host->status : nullptr;
+    const layout::CombineTokenLayout tl(a.hidden_bytes, k);
+    const int token_bytes = tl.num_bytes();
+    const int num_groups = min(k, num_ranks);
+    const layout::BufferLayout bl(token_bytes, num_groups, a.num_max_tokens);
+
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(base) + warp * S;
+    uint8_t* stages = base + math::align<int64_t>(int64_t(W) * S * 8, 128) + int64_t(warp) * S * token_bytes;
+
+    if (not dev::healthy(cs)) return;
+    const unsigned epoch = a.ws->combine_epoch + 1;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < W * S; ++i) ptx::mbarrier_init(reinterpret_cast<uint64_t*>(base) + i, 1);
+        ptx::fence_mbarrier_init();
+    }
+    for (int s = threadIdx.x; s < num_ranks; s += blockDim.x) psum_rank_smem[s] = a.psum_rank[s];
+    __syncthreads();
+
+    // Entry barrier: every peer has finished the dispatch epilogue that read the shared buffer.
+    if (cta == 0 and warp == 0) dev::rank_barrier_warp(cs, hs, a.peers, a.timeout_ns, kSiteEntryBarrier);
+    if (not dev::grid_sync(cs, hs, num_ctas, a.timeout_ns, rank, kSiteGridSync)) return;
+
+    const int gw = cta * W + warp, num_gw = num_ctas * W;
+    const int meta_cols = k + 2;
+    const int chunks = a.hidden_bytes / 16;
+    int n = 0;            // rows processed by this warp (stage / parity counter)
+    int num_loads[4] = {0, 0, 0, 0};   // bulk loads issued per stage (mbarrier parity)
+    bool failed = false;
+
+    for (int q = 0; q < num_ranks and not failed; ++q) {
+        // visit sources in an order rotated by rank and warp so that, at any moment, the ranks of
+        // the node spread their pushes over all destinations instead of converging on one
+        const int s = (rank + 1 + gw + q) % num_ranks;
+        const int begin = s == 0 ? 0 : psum_rank_smem[s - 1];
+        const int end = min(psum_rank_smem[s], a.num_metadata_rows);
+        for (int row = begin + gw; row < end; row += num_gw, ++n) {
+            const int stage_idx = n % S;
+            uint8_t* stage = stages + stage_idx * token_bytes;
+            const int my_slot = lane < k ? a.recv_src_metadata[int64_t(row) * meta_cols + lane] : -1;
+            int src_global = 0, master = 0;
+            if (lane == 0) {
+                src_global = a.recv_src_metadata[int64_t(row) * meta_cols + k];
+                master = a.recv_src_metadata[int64_t(row) * meta_cols + k + 1];
+            }
+            src_global = __shfl_sync(0xffffffffu, src_global, 0);
+            master = __shfl_sync(0xffffffffu, master, 0);
+            const unsigned valid = __ballot_sync(0xffffffffu, my_slot >= 0);
+            const int count = __popc(valid);
+            const int token = src_global - s * a.num_max_tokens;
+            if (count == 0 or token < 0 or token >= a.num_max_tokens or master < 0) { ptx::bulk_commit(); continue; }
+
+            // the stage may still be read by the store issued S rows ago
+            dispatch_detail::wait_read_pending(S - 1);
+            __syncwarp();
+
+            if (count == 1) {
+                const int slot = __shfl_sync(0xffffffffu, my_slot, __ffs(valid) - 1);
+                if (lane == 0) {
+                    ptx::mbarrier_arrive_expect_tx(&mbar[stage_idx], a.hidden_bytes);
+                    ptx::bulk_load(stage, a.x + int64_t(slot) * a.hidden_bytes, a.hidden_bytes, &mbar[stage_idx]);
+                }
+            } else {
+                int sl[kUnroll];
+                #pragma unroll
+                for (int u = 0; u < kUnroll; ++u)
+                    sl[u] = u < count ? __shfl_sync(0xffffffffu, my_slot, nth_set_bit(valid, min(u, count - 1))) : -1;
+                for (int c = lane; c < chunks; c += 32) {
+                    int4 v[kUnroll];
+                    #pragma unroll
+                    for (int u = 0; u < kUnroll; ++u)
+                        if (sl[u] >= 0) v[u] = ptx::ld_nc_v4(a.x + int64_t(sl[u]) * a.hidden_bytes + c * 16);
+                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    #pragma unroll
+                    for (int u = 0; u < kUnroll; ++u)
+                        if (sl[u] >= 0) accumulate(acc, v[u]);
+                    for (int u = kUnroll; u < count; ++u) {     // rare: more than 8 local experts
+                        const int slot = __shfl_sync(0xffffffffu, my_slot, nth_set_bit(valid, u));
+                        accumulate(acc, ptx::ld_nc_v4(a.x + int64_t(slot) * a.hidden_bytes + c * 16));
+                    }
+                    *reinterpret_cast<int4*>(stage + c * 16) = pack(acc);
+                }
+            }
+            if (lane < k)
+                reinterpret_cast<float*>(stage + tl.weight_offset())[lane] =
+                    (my_slot >= 0 and a.topk_weights != nullptr) ? a.topk_weights[my_slot] : 0.f;
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (count == 1) {
+                if (not ptx::mbarrier_wait(&mbar[stage_idx], num_loads[stage_idx] & 1)) failed = true;
+                ++num_loads[stage_idx];
+                if (__any_sync(0xffffffffu, failed)) {
+                    if (lane == 0) dev::report_status(cs, hs, kStatusMbarrierTimeout, rank, s, kSiteLoad, row, 0);
+                    break;
+                }
+            }
+            if (lane == 0) {
+                const int group = num_ranks >= k ? master : rank;
+                ptx::bulk_store(a.peers.base[s] + a.buffer_offset + bl.offset(group, token), stage, token_bytes);
+            }
+            ptx::bulk_commit();
+        }
+    }
+
+    // completion: all stores performed, then one flag per destination from the last CTA
+    ptx::bulk_wait<0>();
+    ptx::fence_proxy_async();
+    __threadfence_system();
+    __syncthreads();
+    if (warp == 0) {
+        unsigned last = 0;
+        if (lane == 0) {
+            last = atomicAdd(&cs->done_ctas, 1u) == unsigned(num_ctas - 1);
+            if (last) cs->done_ctas = 0;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+            __threadfence_system();
+            for (int r = lane; r < num_ranks; r += 32)
+                ptx::st_release_sys(a.peers.sym(&a.ws->combine_done[rank], r), static_cast<unsigned long long>(epoch));
+            if (lane == 0) a.ws->combine_epoch = epoch;
+            if (a.wait_arrival) {
+                const dev::Deadline deadline(a.timeout_ns);
+                for (int s = lane; s < num_ranks; s += 32) {
+                    unsigned long long w = 0;
+                    if (not dev::spin_until(deadline, [&]() { return (w = ptx::ld_acquire_sys(&a.ws->combine_done[s])) == epoch; }))
+                        dev::report_status(cs, hs, kStatusArrivalTimeout, rank, s, kSiteArrival, epoch, w);
+                }
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_constant__ CombineReduceArgs a) {
+    using namespace combine_detail;
+    const int num_local_experts = a.num_experts / a.num_ranks;
+    const int warps_per_cta = blockDim.x / 32;
+    const int warp = threadIdx.x / 32, lane = ptx::lane_id();
+    const int k = a.num_topk;
+    layout::CommonSignals* cs = &a.ws->common;
+    layout::HostStatus* hs = a.host ? &a.host->status : nullptr;
+    const layout::CombineTokenLayout tl(a.hidden_bytes, k);
+    const int token_bytes = tl.num_bytes();
+    const layout::BufferLayout bl(token_bytes, min(k, a.num_ranks), a.num_max_tokens);
+
+    if (not dev::healthy(cs)) return;
+    const unsigned epoch = a.ws->combine_epoch;
+    if (a.wait_arrival and warp == 0) {
+        const dev::Deadline deadline(a.timeout_ns);
+        for (int s = lane; s < a.num_ranks; s += 32) {
+            unsigned long long w = 0;
+            if (not dev::spin_until(deadline, [&]() { return (w = ptx::ld_acquire_sys(&a.ws->combine_done[s])) == epoch; }))
+                dev::report_status(cs, hs, kStatusArrivalTimeout, a.rank, s, kSiteArrival, epoch, w);
+        }
+    }
+    __syncthreads();
+    if (not dev::healthy(cs)) return;
+
+    const int chunks = a.hidden_bytes / 16;
+    for (int t = blockIdx.x * warps_per_cta + warp; t < a.num_tokens; t += gridDim.x * warps_per_cta) {
+        // lane j owns top-k position j
+        int r = -1;
+        if (lane < k) {
+            const int64_t e = a.topk_idx[int64_t(t) * k + lane];
+            if (e >= 0 and e < a.num_experts) r = int(e) / num_local_experts;
+        }
+        // master position of a rank = last top-k position that selects it
+        bool is_master = r >= 0;
+        for (int d = 1; d < k; ++d) {
+            const int other = __shfl_down_sync(0xffffffffu, r, d);
+            if (lane + d < k and other == r) is_master = false;
+        }
+        const int group = a.num_ranks >= k ? lane : r;
+        const unsigned masters = __ballot_sync(0xffffffffu, is_master);
+        const int count = __popc(masters);
+
+        const uint8_t* part[kUnroll];
+        #pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int g = __shfl_sync(0xffffffffu, group, u < count ? nth_set_bit(masters, u) : 0);
+            part[u] = u < count ? a.buffer + bl.offset(g, t) : nullptr;
+        }
+        for (int c = lane; c < chunks; c += 32) {
+            int4 v[kUnroll], b0 = make_int4(0, 0, 0, 0), b1 = make_int4(0, 0, 0, 0);
+            if (a.bias_0 != nullptr) b0 = ptx::ld_nc_v4(a.bias_0 + int64_t(t) * a.hidden_bytes + c * 16);
+            if (a.bias_1 != nullptr) b1 = ptx::ld_nc_v4(a.bias_1 + int64_t(t) * a.hidden_bytes + c * 16);
+            #pragma unroll
+            for (int u = 0; u < kUnroll; ++u)
+                if (part[u] != nullptr) v[u] = ptx::ld_v4(part[u] + c * 16);
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (a.bias_0 != nullptr) accumulate(acc, b0);
+            if (a.bias_1 != nullptr) accumulate(acc, b1);
+            #pragma unroll
+            for (int u = 0; u < kUnroll; ++u)
+                if (part[u] != nullptr) accumulate(acc, v[u]);
+            for (int u = kUnroll; u < count; ++u) {
+                const int g = __shfl_sync(0xffffffffu, group, nth_set_bit(masters, u));
+                accumulate(acc, ptx::ld_v4(a.buffer + bl.offset(g, t) + c * 16));
+            }
+            ptx::st_na_v4(a.combined_x + int64_t(t) * a.hidden_bytes + c * 16, pack(acc));
+        }
+        if (a.combined_topk_weights != nullptr) {
+            // position j reads its weight from the partial produced by the rank that owns expert j
+            int master_group = -1;
+            for (int j = 0; j < k; ++j) {
+                const int rj = __shfl_sync(0xffffffffu, r, j);
+                const int gj = __shfl_sync(0xffffffffu, group, j);
+                if ((masters >> j) & 1 and rj == r) master_group = gj;
+            }
+            if (lane < k) {
+                float w = 0.f;
+                if (r >= 0 and master_group >= 0)
+                    w = *reinterpret_cast<const float*>(a.buffer + bl.offset(master_group, t) + tl.weight_offset() + 4 * lane);
+                a.combined_topk_weights[int64_t(t) * k + lane] = w;
+            }
+        }
+    }
+}
+
+}  // namespace deep_ep::kernels

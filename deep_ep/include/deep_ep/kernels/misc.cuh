@@ -1,0 +1,216 @@
+// Barrier, Engram fetch, batched all-gather and pipeline send/recv kernels for sm_100a.
+// Reference roles: `impls/comm/barrier.hpp:13-21`, `impls/engram/engram_fetch.hpp:15-138`,
+// `impls/bucket/all_gather/urma.hpp:9-48`, `impls/pp/pp_send_recv.hpp:14-166`. All of them move data
+// with ordinary peer loads/stores (or NVLS `multimem.st`) issued by the SMs over NVLink.
+#pragma once
+
+#include "../device/sync.cuh"
+#include "misc_args.hpp"
+
+namespace deep_ep::kernels {
+
+// ---------------------------------------------------------------------------------------- barrier
+__global__ void __launch_bounds__(32) rank_barrier_kernel(const __grid_constant__ BarrierArgs a) {
+    if (not dev::healthy(a.cs)) return;
+    dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, /*where=*/1);
+}
+
+// ---------------------------------------------------------------------------------------- engram
+// One warp per (layer, token, entry); four entries are kept in flight per warp so that small
+// (512 B) remote reads overlap. Negative indices are skipped and leave the destination untouched.
+__global__ void __launch_bounds__(256) engram_fetch_kernel(const __grid_constant__ EngramFetchArgs a) {
+    constexpr int kInflight = 4;
+    const int lane = ptx::lane_id();
+    const int64_t gw = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) / 32;
+    const int64_t num_gw = int64_t(gridDim.x) * blockDim.x / 32;
+    const int64_t per_layer = int64_t(a.num_tokens) * a.num_entries_per_token;
+    const int64_t total = per_layer * a.num_layers;
+    const int chunks = a.hidden_bytes / 16;
+
+    for (int64_t base = gw * kInflight; base < total; base += num_gw * kInflight) {
+        const uint8_t* src[kInflight];
+        uint8_t* dst[kInflight];
+        #pragma unroll
+        for (int u = 0; u < kInflight; ++u) {
+            src[u] = nullptr, dst[u] = nullptr;
+            const int64_t i = base + u;
+            if (i >= total) continue;
+            const int layer = int(i / per_layer);
+            const int64_t in_layer = i % per_layer;
+            const int idx = a.indices[i];
+            if (idx < 0) continue;
+            const int entries = a.table.num_entries_per_rank[layer];
+            const int owner = idx / entries, entry = idx % entries;
+            if (owner >= a.peers.num_ranks) continue;
+            src[u] = a.peers.base[owner] + a.table.storage_offset[layer] + int64_t(entry) * a.hidden_bytes;
+            const int64_t token = in_layer / a.num_entries_per_token, p = in_layer % a.num_entries_per_token;
+            dst[u] = a.recv + ((int64_t(layer) * a.num_max_tokens + token) * a.num_entries_per_token + p) * a.hidden_bytes;
+            if (a.sf_out != nullptr) {
+                const sf_pack_t* sf_src = reinterpret_cast<const sf_pack_t*>(
+                    a.peers.base[owner] + a.table.sf_offset[layer]) + int64_t(entry) * a.num_sf_packs;
+                sf_pack_t* sf_dst = a.sf_out + layer * a.sf_layer_stride + token * a.sf_token_stride;
+                for (int q = lane; q < a.num_sf_packs; q += 32)
+                    sf_dst[(p * a.num_sf_packs + q) * a.sf_pack_stride] = sf_src[q];
+            }
+        }
+        for (int c = lane; c < chunks; c += 32) {
+            int4 v[kInflight];
+            #pragma unroll
+            for (int u = 0; u < kInflight; ++u)
+                if (src[u] != nullptr) v[u] = ptx::ld_nc_v4(src[u] + c * 16);
+            #pragma unroll
+            for (int u = 0; u < kInflight; ++u)
+                if (src[u] != nullptr) ptx::st_na_v4(dst[u] + c * 16, v[u]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------- all-gather
+namespace ag_detail {
+
+EP_DEVICE void multimem_st_v4(void* mc_ptr, const int4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+                 ::"l"(mc_ptr), "f"(__int_as_float(v.x)), "f"(__int_as_float(v.y)), "f"(__int_as_float(v.z)),
+                   "f"(__int_as_float(v.w)) : "memory");
+}
+
+}  // namespace ag_detail
+
+// Every rank writes its shard of every bucket into all peers at `dst_offset + rank * num_bytes`.
+// Work is cut into 32 KiB tiles spread over all CTAs; each tile is read once and written to every
+// destination (peer order rotated by rank), or written once through the NVLS multicast mapping.
+__global__ void __launch_bounds__(512) bucket_all_gather_kernel(const __grid_constant__ AllGatherArgs a) {
+    constexpr int64_t kTileBytes = 32 * 1024;
+    const int rank = a.peers.rank, num_ranks = a.peers.num_ranks;
+
+    // "destinations have been consumed" barrier, then release the other CTAs
+    if (not dev::healthy(a.cs)) return;
+    if (blockIdx.x == 0 and threadIdx.x < 32)
+        dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, /*where=*/40);
+    if (not dev::grid_sync(a.cs, a.host_status, gridDim.x, a.timeout_ns, rank, /*where=*/41)) return;
+
+    int64_t tile_base = 0;
+    for (int b = 0; b < a.list.num_buckets; ++b) {
+        const layout::Bucket& bucket = a.list.buckets[b];
+        const int64_t num_tiles = math::ceil_div(bucket.num_bytes, kTileBytes);
+        const int64_t dst_off = bucket.dst_offset + int64_t(rank) * bucket.num_bytes;
+        // widest access that keeps source and every destination aligned (bases are 2 MiB aligned)
+        const uint64_t mis = reinterpret_cast<uint64_t>(bucket.src) | uint64_t(dst_off) | uint64_t(bucket.num_bytes);
+        const bool vec16 = (mis & 15) == 0;
+        for (int64_t tile = (blockIdx.x + gridDim.x - tile_base % gridDim.x) % gridDim.x; tile < num_tiles; tile += gridDim.x) {
+            const int64_t begin = tile * kTileBytes, end = min(begin + kTileBytes, bucket.num_bytes);
+            if (vec16) {
+                for (int64_t o = begin + threadIdx.x * 16; o < end; o += blockDim.x * 16) {
+                    const int4 v = ptx::ld_nc_v4(bucket.src + o);
+                    if (a.use_multicast) {
+                        ag_detail::multimem_st_v4(a.peers.mc_base + dst_off + o, v);
+                    } else {
+                        for (int i = 0; i < num_ranks; ++i) {
+                            const int p = (rank + 1 + i) % num_ranks;
+                            if (p == rank and a.skip_local) continue;
+                            ptx::st_na_v4(a.peers.base[p] + dst_off + o, v);
+                        }
+                    }
+                }
+            } else {
+                // odd sizes or unaligned addresses: byte granularity (rare, small tensors)
+                for (int64_t o = begin + threadIdx.x; o < end; o += blockDim.x) {
+                    const uint8_t v = bucket.src[o];
+                    for (int i = 0; i < num_ranks; ++i) {
+                        const int p = (rank + 1 + i) % num_ranks;
+                        if (p == rank and a.skip_local) continue;
+                        a.peers.base[p][dst_off + o] = v;
+                    }
+                }
+            }
+        }
+        tile_base += num_tiles;
+    }
+    __threadfence_system();
+}
+
+// ---------------------------------------------------------------------------------------- pipeline
+namespace pp_detail {
+
+EP_DEVICE void copy_bytes(uint8_t* dst, const uint8_t* src, int64_t n) {
+    const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x, nthreads = int64_t(gridDim.x) * blockDim.x;
+    if (((reinterpret_cast<uint64_t>(dst) | reinterpret_cast<uint64_t>(src)) & 15) == 0) {
+        const int64_t nvec = n / 16;
+        for (int64_t i = tid; i < nvec; i += nthreads) ptx::st_na_v4(dst + i * 16, ptx::ld_v4(src + i * 16));
+        for (int64_t i = nvec * 16 + tid; i < n; i += nthreads) dst[i] = src[i];
+    } else {
+        for (int64_t i = tid; i < n; i += nthreads) dst[i] = src[i];
+    }
+}
+
+// true for exactly one CTA: the last one to arrive
+EP_DEVICE bool last_cta(layout::CommonSignals* cs) {
+    __shared__ int is_last;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        is_last = atomicAdd(&cs->done_ctas, 1u) == gridDim.x - 1;
+        if (is_last) cs->done_ctas = 0;
+    }
+    __syncthreads();
+    return is_last != 0;
+}
+
+}  // namespace pp_detail
+
+// Buffered send to a ring neighbour: wait for a free slot (credit), copy the tensor into the
+// neighbour's landing slot, then publish the arrival counter with release semantics.
+__global__ void __launch_bounds__(512) pp_send_kernel(const __grid_constant__ PPArgs a) {
+    layout::CommonSignals* cs = &a.ws->common;
+    if (not dev::healthy(cs)) return;
+    const int d = a.direction;
+    const unsigned long long n = a.ws->send_count[d];
+    __shared__ int ok_smem;
+    if (threadIdx.x == 0) {
+        const dev::Deadline deadline(a.timeout_ns);
+        unsigned long long freed = 0;
+        const bool ok = dev::spin_until(deadline, [&]() {
+            freed = ptx::ld_acquire_sys(&a.ws->release[d]);
+            return freed + a.num_inflight >= n + 1;
+        });
+        if (not ok) dev::report_status(cs, a.host_status, kStatusCreditTimeout, a.peers.rank, a.peer, 50, n + 1, freed);
+        ok_smem = ok;
+    }
+    __syncthreads();
+    if (not ok_smem) return;
+    // the receiver sees data from its previous rank in region 1 and from its next rank in region 0
+    const int region = 1 - d;
+    uint8_t* slot = a.peers.base[a.peer] + a.storage_offset + (int64_t(region) * a.num_inflight + n % a.num_inflight) * a.slot_bytes;
+    pp_detail::copy_bytes(slot, a.x, a.num_bytes);
+    if (pp_detail::last_cta(cs) and threadIdx.x == 0) {
+        ptx::st_release_sys(a.peers.sym(&a.ws->arrival[region], a.peer), n + 1);
+        a.ws->send_count[d] = n + 1;
+    }
+}
+
+// Matching receive: wait for the arrival counter, copy out of the landing slot, return the credit.
+__global__ void __launch_bounds__(512) pp_recv_kernel(const __grid_constant__ PPArgs a) {
+    layout::CommonSignals* cs = &a.ws->common;
+    if (not dev::healthy(cs)) return;
+    const int d = a.direction;            // region index == direction of the source
+    const unsigned long long n = a.ws->recv_count[d];
+    __shared__ int ok_smem;
+    if (threadIdx.x == 0) {
+        const dev::Deadline deadline(a.timeout_ns);
+        unsigned long long arrived = 0;
+        const bool ok = dev::spin_until(deadline, [&]() { return (arrived = ptx::ld_acquire_sys(&a.ws->arrival[d])) >= n + 1; });
+        if (not ok) dev::report_status(cs, a.host_status, kStatusArrivalTimeout, a.peers.rank, a.peer, 51, n + 1, arrived);
+        ok_smem = ok;
+    }
+    __syncthreads();
+    if (not ok_smem) return;
+    const uint8_t* slot = a.peers.base[a.peers.rank] + a.storage_offset + (int64_t(d) * a.num_inflight + n % a.num_inflight) * a.slot_bytes;
+    pp_detail::copy_bytes(a.x, slot, a.num_bytes);
+    if (pp_detail::last_cta(cs) and threadIdx.x == 0) {
+        // the sender addressed me through its direction 1 - d
+        ptx::st_release_sys(a.peers.sym(&a.ws->release[1 - d], a.peer), n + 1);
+        a.ws->recv_count[d] = n + 1;
+    }
+}
+
+}  // namespace deep_ep::kernels

@@ -1,0 +1,37 @@
+"""Spawns N worker processes that form a process group (gloo on CPU, NCCL on GPUs) on 127.0.0.1."""
+import os
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world_size, port, backend, fn, args):
+    if ROOT not in sys.path:
+        sys.path.insert(0, ROOT)
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    kwargs = dict(backend=backend, init_method=f'tcp://127.0.0.1:{port}', world_size=world_size, rank=rank)
+    if backend == 'nccl':
+        torch.cuda.set_device(rank)
+        kwargs['device_id'] = torch.device('cuda', rank)
+    dist.init_process_group(**kwargs)
+    try:
+        fn(rank, world_size, *args)
+    except Exception:
+        traceback.print_exc()
+        raise
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def run_distributed(fn, world_size, port, backend='gloo', args=()):
+    """Run `fn(rank, world_size, *args)` in `world_size` processes; raises if any of them fails."""
+    mp.spawn(_worker, args=(world_size, port, backend, fn, args), nprocs=world_size, join=True)

@@ -1,0 +1,107 @@
+"""CPU unit tests of the Python utilities: math, allocator, event overlap, gate generators, parsers."""
+import pytest
+import torch
+
+import deep_ep
+from deep_ep.buffers.allocator import BufferAllocator
+from deep_ep.utils.event import EventOverlap
+from deep_ep.utils.gate import get_unbalanced_scores
+from deep_ep.utils.math import align, calc_diff, ceil_div, count_bytes, per_token_cast_back, per_token_cast_to_fp8, safe_div
+from deep_ep.utils.testing import KernelProfile, parse_num_bytes
+
+
+def test_public_constants():
+    assert deep_ep.get_num_allocation_alignment() == 2 << 20
+    assert deep_ep.get_num_rdma_alignment() == 32 and deep_ep.get_num_tma_alignment() == 32
+    assert deep_ep.topk_idx_t == torch.int64
+    assert deep_ep.__version__ == '1.0.0'
+
+
+def test_math_helpers():
+    assert ceil_div(7, 4) == 2 and align(7, 4) == 8 and align(8, 4) == 8
+    assert safe_div(0, 0) == 0 and safe_div(3, 2) == 1.5
+    with pytest.raises(ZeroDivisionError):
+        safe_div(1, 0)
+    a, b = torch.randn(4, 8), torch.randn(4, 8, dtype=torch.bfloat16)
+    assert count_bytes(a, (b, None), [a]) == 2 * a.numel() * 4 + b.numel() * 2
+    assert calc_diff(a, a) < 1e-12
+
+
+@pytest.mark.parametrize('n', [128, 300, 7168])
+def test_fp8_cast_roundtrip(n):
+    x = torch.randn(16, n, dtype=torch.bfloat16)
+    q, s = per_token_cast_to_fp8(x)
+    assert q.dtype == torch.float8_e4m3fn and q.shape == x.shape and s.shape == (16, ceil_div(n, 128))
+    assert s.dtype == torch.float32 and bool((s > 0).all())
+    back = per_token_cast_back(q, s)
+    assert calc_diff(back, x) < 2e-3
+    # |q| never exceeds the e4m3 maximum and every group uses its full range
+    assert q.float().abs().max() <= 448
+
+
+def test_allocator_plan_and_materialize():
+    plan = BufferAllocator()
+    a = plan.allocate((3, 5), torch.float32)
+    b = plan.allocate((7,), torch.int16)
+    assert a.device.type == 'meta' and plan.num_bytes == 2 * (2 << 20)
+    storage = torch.zeros(plan.num_bytes, dtype=torch.uint8)
+    plan.materialize(storage)
+    assert a.device.type == 'cpu' and a.shape == (3, 5) and b.shape == (7,)
+    a.fill_(1.0)
+    assert storage[:60].view(torch.float32).sum() == 15
+    assert b.data_ptr() - storage.data_ptr() == 2 << 20
+    with pytest.raises(AssertionError):
+        plan.materialize(storage)
+    with pytest.raises(AssertionError):
+        plan.allocate((1,), torch.int8)
+
+
+def test_event_overlap_hook_runs_once():
+    calls = []
+    ev = EventOverlap(deep_ep.EventHandle())
+    ev.register_hook_after_wait(lambda: calls.append(1) or 'done')
+    with pytest.raises(AssertionError):
+        ev.register_hook_after_wait(lambda: None)
+    assert ev.current_stream_wait() == 'done'
+    assert ev.current_stream_wait() is None and calls == [1]
+    ev2 = EventOverlap(deep_ep.EventHandle())
+    ev2.register_hook_after_wait(lambda: calls.append(2))
+    with ev2(release_handle=True):
+        pass
+    assert calls == [1, 2] and ev2.event is None
+
+
+def test_parse_num_bytes_and_profile():
+    assert parse_num_bytes('1G') == 1 << 30 and parse_num_bytes('64M') == 64 << 20
+    assert parse_num_bytes('512KiB') == 512 << 10 and parse_num_bytes('1048576') == 1048576
+    with pytest.raises(ValueError):
+        parse_num_bytes('abc')
+    p = KernelProfile(2000.0) + KernelProfile(1000.0)
+    assert p.us == 3.0 and abs(p.gbps(3000) - 1.0) < 1e-9 and abs(p.tflops(3e6) - 1.0) < 1e-9
+
+
+@pytest.mark.parametrize('ratio', [1.0, 2.0, 4.0])
+@pytest.mark.parametrize('num_ranks,num_experts,num_topk', [(8, 64, 6), (8, 256, 8), (2, 16, 4), (16, 64, 4)])
+def test_precise_gate_imbalance(ratio, num_ranks, num_experts, num_topk):
+    torch.manual_seed(0)
+    per_rank = num_experts // num_ranks
+    upper = min(num_topk, num_ranks, int((num_ranks - 1) / ratio) + 1)
+    if max(1, ceil_div(num_topk, per_rank)) > upper:
+        pytest.skip('ratio not reachable for this shape')
+    total = torch.zeros(num_ranks)
+    for _ in range(num_ranks):
+        scores = get_unbalanced_scores(4096, num_experts, num_ranks, num_topk, ratio, True, device=torch.device('cpu'))
+        idx = scores.topk(num_topk, dim=-1).indices
+        assert idx.unique(dim=1).shape == idx.shape
+        total += torch.nn.functional.one_hot(idx // per_rank, num_ranks).any(dim=1).float().sum(0)
+    practical = total[0] / total[1:].min().clamp(min=1)
+    assert abs(practical - ratio) / ratio < 0.1
+    if num_ranks > 2:
+        assert total[1:].max() / total[1:].min().clamp(min=1) < 1.02
+
+
+def test_random_gate_direction():
+    torch.manual_seed(0)
+    scores = get_unbalanced_scores(2048, 64, 8, 6, 2.0, False, device=torch.device('cpu'))
+    hits = torch.nn.functional.one_hot(scores.topk(6, dim=-1).indices // 8, 8).any(dim=1).float().sum(0)
+    assert 1.5 < (hits[0] / hits[1:].mean()).item() < 2.6
