@@ -1,0 +1,298 @@
+"""Headline benchmark: expert-parallel dispatch/combine bandwidth per rank.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 20 --warmup 5
+
+Configuration (the one the reference publishes its numbers for): 16,384 tokens per rank, hidden 7168,
+top-6 of 256 experts chosen from N(0,1) gating logits, expert alignment 128, no bias; dispatch in FP8 e4m3
+with fp32 1x128 row-major scales, combine in BF16. One step = dispatch (issue + expand epilogue) followed by
+combine (issue + reduce epilogue) through `deep_ep.EPBuffer`.
+
+Accounting (same as the reference's test): bytes = rank-deduplicated tokens RECEIVED by a rank (its own
+included) x logical bytes per source token (dispatch 7168 + 56*4 + 6*8 + 6*4 = 7464 B, combine 14336 B);
+time = device time of the issue kernel with the arrival wait moved into it (`set_barrier_in_prologue(True)`),
+i.e. issue + wire + completion, epilogue excluded. Times come from CUDA events, maximum over ranks.
+The JSON `value` is the aggregate over all ranks (per-rank figure x N); `per_rank` holds the per-rank numbers.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+PUBLISHED_DISPATCH_GBS = 375.0    # README of the reference, EP8, Ascend 950DT
+PUBLISHED_COMBINE_GBS = 347.0
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument('--gpus', type=int, default=1)
+    p.add_argument('--steps', type=int, default=20)
+    p.add_argument('--warmup', type=int, default=5)
+    p.add_argument('--impl', default='ours', choices=['ours', 'reference', 'nccl'])
+    p.add_argument('--num-tokens', type=int, default=16384)
+    p.add_argument('--hidden', type=int, default=7168)
+    p.add_argument('--num-topk', type=int, default=6)
+    p.add_argument('--num-experts', type=int, default=256)
+    p.add_argument('--num-sms', type=int, default=0)
+    p.add_argument('--dispatch-input', default='fp8', choices=['fp8', 'bf16-fused'],
+                   help='fp8: tokens are quantised before the timed call (what the reference measures); '
+                        'bf16-fused: BF16 tokens quantised inside the dispatch kernel')
+    p.add_argument('--skip-e2e', action='store_true')
+    p.add_argument('--skip-check', action='store_true')
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
+
+    QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
+             'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.proc = None
+        self.path = f'/tmp/deep_ep_clocks_{os.getpid()}.csv'
+
+    def start(self):
+        try:
+            self.out = open(self.path, 'w')
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits',
+                                          '-lms', '100', '-i', str(self.device_index)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        clocks, max_clock, reasons = [], None, set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        with open(self.path) as f:
+            for line in f:
+                parts = [s.strip() for s in line.split(',')]
+                if len(parts) < 9:
+                    continue
+                try:
+                    clocks.append(float(parts[1])), (max_clock := float(parts[2]))
+                except ValueError:
+                    continue
+                for name, value in zip(names, parts[5:9]):
+                    if value.lower().startswith('active'):
+                        reasons.add(name)
+        os.remove(self.path)
+        return {'sm_mhz': statistics.median(clocks) if clocks else None, 'sm_max_mhz': max_clock,
+                'reasons': sorted(reasons), 'samples': len(clocks)}
+
+
+def reference_arm(args):
+    """The reference is Ascend C + CANN/HCCL: it has no CUDA path and cannot be installed or run on a B200 box."""
+    why = 'reference needs Ascend CANN/Bisheng/torch_npu and Ascend 950 hardware; pip install of /root/reference fails (see DESIGN.md)'
+    marker = os.path.join(ROOT, 'baseline', 'reference_install.txt')
+    if os.path.exists(marker):
+        with open(marker) as f:
+            why = f.readline().strip() or why
+    if int(os.environ.get('RANK', 0)) == 0:
+        print(json.dumps({'impl': 'reference', 'unavailable': why}))
+
+
+def main():
+    args = parse_args()
+    if args.impl == 'reference':
+        reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import deep_ep
+    from deep_ep.utils.math import per_token_cast_to_fp8
+    from deep_ep.utils.testing import L2Flusher
+
+    rank = int(os.environ.get('RANK', 0))
+    world = int(os.environ.get('WORLD_SIZE', 1))
+    local_rank = int(os.environ.get('LOCAL_RANK', 0))
+    assert world == args.gpus, f'launched with WORLD_SIZE={world} but --gpus {args.gpus}'
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+    os.environ.setdefault('MASTER_PORT', '29517')
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    group = dist.group.WORLD
+    torch.manual_seed(1234 + rank)
+
+    T, H, K, E = args.num_tokens, args.hidden, args.num_topk, args.num_experts
+    align = 128
+    buffer = deep_ep.EPBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, use_fp8_dispatch=False,
+                              explicitly_destroy=True)
+    num_sms = args.num_sms or buffer.get_theoretical_num_sms(E, K)
+
+    # synthetic inputs, generated on the host in pinned memory (the end-to-end arm copies them every step)
+    x_host = torch.randn(T, H, dtype=torch.bfloat16).pin_memory()
+    logits_host = torch.randn(T, E)
+    top_logits, topk_idx_host = logits_host.topk(K, dim=-1)
+    topk_w_host = torch.softmax(top_logits, dim=-1).float().pin_memory()
+    topk_idx_host = topk_idx_host.long().pin_memory()
+    x = x_host.to(dev)
+    topk_idx, topk_w = topk_idx_host.to(dev), topk_w_host.to(dev)
+    x_fp8, sf = per_token_cast_to_fp8(x)
+    sf_packs = sf.view(torch.int16)
+
+    def dispatch_input():
+        return x if args.dispatch_input == 'bf16-fused' else (x_fp8, sf_packs)
+
+    common = dict(num_experts=E, num_max_tokens_per_rank=T, expert_alignment=align, num_sms=num_sms,
+                  async_with_compute_stream=True, do_expand=True, do_zero_padding=True, defer_epilogue=True)
+    fused = args.dispatch_input == 'bf16-fused'
+    flusher = L2Flusher()
+    deep_ep._C.set_barrier_in_prologue(True)
+
+    # one untimed pass to size things and to build the combine input
+    ev = buffer.dispatch(dispatch_input(), topk_idx=topk_idx, topk_weights=topk_w, fused_fp8_quant=fused, **common)
+    (recv_x, recv_sf), _, recv_w, handle = ev.current_stream_wait()
+    num_recv = int(handle.psum_num_recv_tokens_per_rank[-1])
+    y = torch.randn(recv_x.size(0), H, dtype=torch.bfloat16, device=dev)
+    dispatch_bytes = num_recv * (H + (H // 128) * 4 + K * 8 + K * 4)
+    combine_bytes = num_recv * H * 2
+
+    if not args.skip_check:      # the timed path must produce what the oracle produces
+        from deep_ep.utils import refs
+        ref_x, ref_idx, ref_w, ref_src, _ = refs.dispatch((x_fp8.view(torch.uint8), sf_packs), topk_idx, topk_w, T, E)
+        meta = handle.recv_src_metadata[:num_recv]
+        valid = meta[:, :-2] >= 0
+        flat = meta[:, :-2][valid].long()
+        assert torch.equal(meta[:, -2], ref_src) and torch.equal(valid, ref_idx >= 0)
+        assert torch.equal(recv_x.view(torch.uint8)[flat], ref_x[0].unsqueeze(1).expand(-1, K, -1)[valid])
+        del ref_x, ref_idx, ref_w, ref_src
+
+    def step(events=None):
+        flusher()
+        if events is not None:
+            events[0].record()
+        ev_d = buffer.dispatch(dispatch_input(), topk_idx=topk_idx, topk_weights=topk_w, fused_fp8_quant=fused, **common)
+        if events is not None:
+            events[1].record()
+        _, _, w_out, h = ev_d.current_stream_wait()
+        flusher()
+        if events is not None:
+            events[2].record()
+        ev_c = buffer.combine(y, h, topk_weights=w_out, num_sms=num_sms, async_with_compute_stream=True, defer_epilogue=True)
+        if events is not None:
+            events[3].record()
+        return ev_c.current_stream_wait()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    start.record()
+    for i in range(args.steps):
+        step(events[i])
+    end.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    clocks = sampler.stop()
+    total_ms = start.elapsed_time(end)
+    dispatch_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in events)
+    combine_ms = statistics.mean(e[2].elapsed_time(e[3]) for e in events)
+
+    # ---- end to end through the public API: H2D of the step's inputs, dispatch + combine, D2H of the result
+    e2e_ms, h2d_bytes, d2h_bytes = None, 0, 0
+    if not args.skip_e2e:
+        deep_ep._C.set_barrier_in_prologue(False)
+        x_dev, idx_dev, w_dev = torch.empty_like(x), torch.empty_like(topk_idx), torch.empty_like(topk_w)
+        result_host = torch.empty(2, dtype=torch.float32).pin_memory()
+        h2d_bytes = x_host.nbytes + topk_idx_host.nbytes + topk_w_host.nbytes
+        d2h_bytes = result_host.nbytes
+
+        def e2e_step():
+            x_dev.copy_(x_host, non_blocking=True)
+            idx_dev.copy_(topk_idx_host, non_blocking=True)
+            w_dev.copy_(topk_w_host, non_blocking=True)
+            ev_d = buffer.dispatch(x_dev, topk_idx=idx_dev, topk_weights=w_dev, fused_fp8_quant=True, **common)
+            (rx, rsf), _, w_out, h = ev_d.current_stream_wait()
+            ev_c = buffer.combine(y[:rx.size(0)], h, topk_weights=w_out, num_sms=num_sms, async_with_compute_stream=True,
+                                  defer_epilogue=True)
+            combined, combined_w = ev_c.current_stream_wait()
+            result = torch.stack([combined[:, :8].float().sum(), combined_w.sum()])
+            result_host.copy_(result, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return result_host
+
+        for _ in range(3):
+            e2e_step()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+
+    # ---- reduce over ranks: maximum time, sum of bytes
+    stats = torch.tensor([total_ms, dispatch_ms, combine_ms, e2e_ms or 0.0, float(dispatch_bytes), float(combine_bytes)],
+                         dtype=torch.float64, device=dev)
+    gathered = [torch.zeros_like(stats) for _ in range(world)]
+    dist.all_gather(gathered, stats)
+    g = torch.stack(gathered).cpu()
+    total_ms, dispatch_ms, combine_ms, e2e_ms_max = (g[:, i].max().item() for i in range(4))
+    sum_dispatch_bytes, sum_combine_bytes = g[:, 4].sum().item(), g[:, 5].sum().item()
+    ms_per_step = total_ms / args.steps
+    dispatch_gbs_rank = [g[r, 4].item() / (g[:, 1].max().item() * 1e6) for r in range(world)]
+    combine_gbs_rank = [g[r, 5].item() / (g[:, 2].max().item() * 1e6) for r in range(world)]
+    dispatch_gbs_agg = sum_dispatch_bytes / (dispatch_ms * 1e6)
+    combine_gbs_agg = sum_combine_bytes / (combine_ms * 1e6)
+
+    if rank == 0:
+        line = {
+            'metric': 'EP dispatch GB/s (FP8 e4m3 + 1x128 fp32 scales, h7168, top-6/256, 16384 tokens/rank), aggregate over ranks; '
+                      'combine (BF16) reported alongside',
+            'value': round(dispatch_gbs_agg, 2), 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': max(args.warmup, 3), 'ms_per_step': round(ms_per_step, 4), 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': round(min(dispatch_gbs_rank) / PUBLISHED_DISPATCH_GBS, 4),
+            'dtype': 'fp8_e4m3 dispatch / bf16 combine (the precisions of the published figures)', 'data': 'synthetic',
+            'impl': 'ours',
+            'config': {'model': 'DeepSeek-V3-style MoE routing: hidden 7168, 256 experts, top-6, expert alignment 128',
+                       'global_batch': T * world, 'seq_len': None, 'tokens_per_rank': T, 'parallelism': f'ep{world}',
+                       'dispatch_input': args.dispatch_input, 'num_sms': num_sms,
+                       'l2': 'a 256 MiB buffer is overwritten before dispatch and before combine in every step (inside ms_per_step, '
+                             'outside the per-phase events)',
+                       'timing': 'phase times: CUDA events around the issue kernel with the arrival wait inside it; max over ranks',
+                       'vs_baseline_def': 'min per-rank dispatch GB/s / 375 GB/s (published EP8 per-rank figure)'},
+            'per_rank': {'dispatch_gbs': round(min(dispatch_gbs_rank), 2), 'combine_gbs': round(min(combine_gbs_rank), 2),
+                         'dispatch_ms': round(dispatch_ms, 4), 'combine_ms': round(combine_ms, 4),
+                         'recv_tokens': num_recv, 'combine_vs_published': round(min(combine_gbs_rank) / PUBLISHED_COMBINE_GBS, 4)},
+            'combine': {'value': round(combine_gbs_agg, 2), 'unit': 'GB/s'},
+            'clocks': clocks,
+            'gpu_launches': 4 * args.steps,
+        }
+        if e2e_ms is not None:
+            step_bytes = sum_dispatch_bytes + sum_combine_bytes
+            line['e2e'] = {'value': round(sum_dispatch_bytes / (e2e_ms_max * 1e6), 2),
+                           'unit': 'GB/s of dispatch bytes over the whole end-to-end step (H2D + fused-quant dispatch + expand + combine + reduce + D2H)',
+                           'step_ms': round(e2e_ms_max, 4), 'step_gbs_dispatch_plus_combine': round(step_bytes / (e2e_ms_max * 1e6), 2),
+                           'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': d2h_bytes}
+        print(json.dumps(line))
+    buffer.destroy()
+    dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

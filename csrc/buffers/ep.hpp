@@ -89,8 +89,9 @@ public:
         host_counts_device = static_cast<layout::EPHostCounts*>(device_view);
 
         auto options = torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, c10::cuda::current_device());
-        lb_storage = torch::from_blob(static_cast<uint8_t*>(context->buffer) + num_bytes, {num_lb_bytes},
-                                      [ctx = context](void*) {}, options);
+        lb_storage = num_lb_bytes > 0
+            ? torch::from_blob(static_cast<uint8_t*>(context->buffer) + num_bytes, {num_lb_bytes}, [ctx = context](void*) {}, options)
+            : torch::empty({0}, options);
     }
 
     ~EPBuffer() noexcept(false) override { destroy_on_destruction("EP"); }

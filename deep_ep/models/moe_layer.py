@@ -1,0 +1,122 @@
+"""An expert-parallel MoE layer built on `EPBuffer`: gate -> dispatch -> per-expert SwiGLU FFN -> combine,
+with a backward pass that reuses the routing handle (the gradient of dispatch is a combine and the
+gradient of combine is a cached dispatch). This is the "one model" of a communication library: the
+layer shape follows the DeepSeek-V3 expert FFN (hidden 7168, intermediate 2048, 256 routed experts,
+top-8, one shared expert), cf. the usage sketch in the reference's `README.md:178-194`.
+"""
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..buffers.ep import EPBuffer, EPHandle
+
+
+@dataclass
+class MoEConfig:
+    hidden: int = 7168
+    intermediate: int = 2048
+    num_experts: int = 256
+    num_topk: int = 8
+    num_shared_experts: int = 0
+    num_max_tokens_per_rank: int = 4096
+    expert_alignment: int = 128
+    fp8_dispatch: bool = False          # quantise to e4m3 (1x128 scales) inside the dispatch kernel
+    expert_backend: str = 'grouped'     # 'grouped': hand-written grouped GEMM kernels, 'torch': per-expert torch.mm
+    num_sms: int = 0
+    init_std: float = 0.02
+
+
+class _Dispatch(torch.autograd.Function):
+    """y = dispatch(x). Backward: grad_x = combine(grad_y) with the same handle."""
+
+    @staticmethod
+    def forward(ctx, x, topk_idx, topk_weights, layer):
+        cfg = layer.config
+        recv_x, _, recv_w, handle, _ = layer.buffer.dispatch(
+            x, topk_idx=topk_idx, topk_weights=topk_weights, num_experts=cfg.num_experts,
+            expert_alignment=cfg.expert_alignment, num_sms=cfg.num_sms, do_expand=True, do_zero_padding=True,
+            do_cpu_sync=True)
+        ctx.layer, ctx.handle = layer, handle
+        layer._handle = handle
+        ctx.mark_non_differentiable(recv_w)
+        return recv_x, recv_w
+
+    @staticmethod
+    def backward(ctx, grad_recv_x, _grad_w):
+        grad_x, _, _ = ctx.layer.buffer.combine(grad_recv_x.contiguous(), ctx.handle)
+        return grad_x, None, None, None
+
+
+class _Combine(torch.autograd.Function):
+    """y = combine(x). Backward: grad_x = cached dispatch(grad_y) (every expanded row receives its token's gradient)."""
+
+    @staticmethod
+    def forward(ctx, x, layer, handle):
+        ctx.layer, ctx.handle = layer, handle
+        combined, _, _ = layer.buffer.combine(x, handle)
+        return combined
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        grad_x, _, _, _, _ = ctx.layer.buffer.dispatch(grad_y.contiguous(), handle=ctx.handle, do_expand=True,
+                                                       do_zero_padding=True)
+        return grad_x, None, None
+
+
+class MoELayer(nn.Module):
+    """Expert-parallel MoE FFN. Experts `[rank * E_local, (rank + 1) * E_local)` live on this rank."""
+
+    def __init__(self, group: dist.ProcessGroup, config: MoEConfig, buffer: Optional[EPBuffer] = None):
+        super().__init__()
+        self.group, self.config = group, config
+        self.num_ranks, self.rank = group.size(), group.rank()
+        assert config.num_experts % self.num_ranks == 0
+        self.num_local_experts = config.num_experts // self.num_ranks
+        h, i, e = config.hidden, config.intermediate, self.num_local_experts
+        std = config.init_std
+        self.gate = nn.Parameter(torch.randn(config.num_experts, h, dtype=torch.float32) * std)
+        self.w_gate_up = nn.Parameter(torch.randn(e, 2 * i, h, dtype=torch.bfloat16) * std)   # [gate; up] rows
+        self.w_down = nn.Parameter(torch.randn(e, h, i, dtype=torch.bfloat16) * std)
+        if config.num_shared_experts > 0:
+            si = i * config.num_shared_experts
+            self.shared_gate_up = nn.Parameter(torch.randn(2 * si, h, dtype=torch.bfloat16) * std)
+            self.shared_down = nn.Parameter(torch.randn(h, si, dtype=torch.bfloat16) * std)
+        self._own_buffer = buffer is None
+        self.buffer = buffer if buffer is not None else EPBuffer(
+            group, num_max_tokens_per_rank=config.num_max_tokens_per_rank, hidden=h, num_topk=config.num_topk,
+            explicitly_destroy=True)
+        self._handle: Optional[EPHandle] = None
+
+    def destroy(self) -> None:
+        if self._own_buffer and self.buffer is not None:
+            self.buffer.destroy()
+        self.buffer = None
+
+    def route(self, x: torch.Tensor):
+        logits = F.linear(x.float(), self.gate)
+        scores = torch.softmax(logits, dim=-1)
+        topk_weights, topk_idx = scores.topk(self.config.num_topk, dim=-1)
+        topk_weights = topk_weights / topk_weights.sum(dim=-1, keepdim=True)
+        return topk_idx, topk_weights
+
+    def experts(self, recv_x: torch.Tensor, handle: EPHandle) -> torch.Tensor:
+        from ..ops.grouped_gemm import grouped_swiglu_ffn
+        return grouped_swiglu_ffn(recv_x, self.w_gate_up, self.w_down, handle.psum_num_recv_tokens_per_expert,
+                                  handle.num_unaligned_recv_tokens_per_expert, handle.num_recv_tokens_per_expert_list,
+                                  self.config.expert_alignment, backend=self.config.expert_backend)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        topk_idx, topk_weights = self.route(x.detach())
+        recv_x, recv_w = _Dispatch.apply(x, topk_idx, topk_weights.float().contiguous(), self)
+        handle = self._handle
+        y = self.experts(recv_x, handle)
+        y = y * recv_w.unsqueeze(1).to(y.dtype)
+        out = _Combine.apply(y, self, handle)
+        if self.config.num_shared_experts > 0:
+            g, u = F.linear(x, self.shared_gate_up).chunk(2, dim=-1)
+            out = out + F.linear(F.silu(g) * u, self.shared_down)
+        return out

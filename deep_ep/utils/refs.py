@@ -39,7 +39,11 @@ def dispatch(x: Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]], topk_idx
     def exchange(t: torch.Tensor) -> torch.Tensor:
         payload = t[order].contiguous()
         out = torch.empty((total, *t.shape[1:]), dtype=t.dtype, device=dev)
-        dist.all_to_all_single(out, payload, recv_counts, send_counts, group=group)
+        if t.dtype in (torch.int16, torch.float8_e4m3fn) and t.dim() == 2:
+            # collective libraries do not know these element types: ship the rows as bytes
+            dist.all_to_all_single(out.view(torch.uint8), payload.view(torch.uint8), recv_counts, send_counts, group=group)
+        else:
+            dist.all_to_all_single(out, payload, recv_counts, send_counts, group=group)
         return out
 
     recv_x = exchange(x)
