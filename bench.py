@@ -34,7 +34,7 @@ PUBLISHED_COMBINE_GBS = 347.0
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument('--gpus', type=int, default=1)
-    p.add_argument('--steps', type=int, default=20)
+    p.add_argument('--steps', type=int, default=50)
     p.add_argument('--warmup', type=int, default=5)
     p.add_argument('--impl', default='ours', choices=['ours', 'reference', 'nccl'])
     p.add_argument('--num-tokens', type=int, default=16384)
@@ -65,7 +65,7 @@ class ClockSampler:
         try:
             self.out = open(self.path, 'w')
             self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits',
-                                          '-lms', '100', '-i', str(self.device_index)], stdout=self.out, stderr=subprocess.DEVNULL)
+                                          '-lms', '50', '-i', str(self.device_index)], stdout=self.out, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 

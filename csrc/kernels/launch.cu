@@ -121,20 +121,26 @@ void pp_recv(const kernels::PPArgs& args, int num_sms, cudaStream_t stream) {
 
 namespace {
 
-__global__ void bounded_wait_probe_kernel(layout::CommonSignals* cs, layout::HostStatus* hs, long long timeout_ns) {
+struct ProbeArgs {
+    layout::CommonSignals* cs;
+    layout::HostStatus* hs;
+    long long timeout_ns;
+};
+
+__global__ void bounded_wait_probe_kernel(const __grid_constant__ ProbeArgs a) {
     // waits for a generation change that no one produces; must give up and record a status
-    const unsigned gen = ptx::ld_acquire_gpu(&cs->grid_gen);
-    const dev::Deadline deadline(timeout_ns);
-    const bool ok = dev::spin_until(deadline, [&]() { return ptx::ld_acquire_gpu(&cs->grid_gen) != gen; });
-    if (not ok) dev::report_status(cs, hs, kStatusGridSyncTimeout, -1, -1, /*where=*/99, gen + 1, gen);
+    const unsigned gen = ptx::ld_acquire_gpu(&a.cs->grid_gen);
+    const dev::Deadline deadline(a.timeout_ns);
+    const bool ok = dev::spin_until(deadline, [&]() { return ptx::ld_acquire_gpu(&a.cs->grid_gen) != gen; });
+    if (not ok) dev::report_status(a.cs, a.hs, kStatusGridSyncTimeout, -1, -1, /*where=*/99, gen + 1, gen);
 }
 
 }  // namespace
 
 void bounded_wait_probe(layout::CommonSignals* cs, layout::HostStatus* host_status, long long timeout_ns,
                         cudaStream_t stream) {
-    bounded_wait_probe_kernel<<<1, 1, 0, stream>>>(cs, host_status, timeout_ns);
-    CUDA_CHECK(cudaGetLastError());
+    const ProbeArgs args = {cs, host_status, timeout_ns};
+    launch_kernel(bounded_wait_probe_kernel, args, 1, 32, 0, false, stream);
 }
 
 }  // namespace deep_ep::launch

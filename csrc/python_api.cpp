@@ -22,8 +22,8 @@ namespace {
 // The reference compares a device-side call against a host wait that runs out; this is the hook
 // the failure-detection test uses: a bounded wait on a flag nobody sets, then the status check.
 void run_bounded_wait_probe(comm::Context& context, double timeout_secs) {
-    EP_HOST_ASSERT(context.common_signals != nullptr);
-    const auto stream = c10::cuda::getCurrentCUDAStream();
+    EP_HOST_ASSERT(context.common_signals != nullptr and context.host_status_device != nullptr);
+    const cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
     launch::bounded_wait_probe(context.common_signals, context.host_status_device,
                                static_cast<long long>(timeout_secs * 1e9), stream);
     CUDA_CHECK(cudaStreamSynchronize(stream));
@@ -39,7 +39,7 @@ void clear_status(comm::Context& context) {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "deep_ep native runtime for NVIDIA B200 (sm_100a)";
-    py::register_exception<EPException>(m, "EPException");
+    py::register_exception<EPException>(m, "EPException", PyExc_RuntimeError);
 
     m.attr("topk_idx_t") = py::reinterpret_borrow<py::object>(
         reinterpret_cast<PyObject*>(torch::getTHPDtype(c10::ScalarType::Long)));

@@ -2,22 +2,22 @@
 // it records a status code and returns, and the host turns that code into an `EPException`.
 #pragma once
 
-#include <exception>
 #include <sstream>
+#include <stdexcept>
 #include <string>
 
 namespace deep_ep {
 
-class EPException : public std::exception {
-    std::string message;
-
-public:
-    EPException(const char* kind, const char* file, int line, const std::string& what) {
+class EPException : public std::runtime_error {
+    static std::string format(const char* kind, const char* file, int line, const std::string& what) {
         std::ostringstream os;
         os << kind << " failed (" << file << ":" << line << "): " << what;
-        message = os.str();
+        return os.str();
     }
-    const char* what() const noexcept override { return message.c_str(); }
+
+public:
+    EPException(const char* kind, const char* file, int line, const std::string& what)
+        : std::runtime_error(format(kind, file, line, what)) {}
 };
 
 }  // namespace deep_ep

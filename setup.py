@@ -16,6 +16,11 @@ from torch.utils.cpp_extension import BuildExtension, CUDAExtension
 ROOT = os.path.dirname(os.path.abspath(__file__))
 # torch's own arch list would add `-gencode` flags for other GPUs; the explicit flag below is the only target.
 os.environ['TORCH_CUDA_ARCH_LIST'] = '10.0a'
+# Link against the shared libstdc++ that PyTorch itself uses: a toolchain that links the C++ runtime
+# statically gives this module a second, private copy, and exceptions that cross into pybind11's shared
+# translators then crash.
+if os.path.exists('/usr/bin/g++') and os.path.exists('/usr/bin/gcc'):
+    os.environ['CC'], os.environ['CXX'] = '/usr/bin/gcc', '/usr/bin/g++'
 
 sources = ['csrc/python_api.cpp'] + sorted(glob.glob('csrc/kernels/*.cu'))
 include_dirs = [os.path.join(ROOT, 'deep_ep', 'include'), os.path.join(ROOT, 'csrc')]

@@ -11,6 +11,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _worker(rank, world_size, port, backend, fn, args):
+    import faulthandler
+    faulthandler.enable()
     if ROOT not in sys.path:
         sys.path.insert(0, ROOT)
     os.environ['MASTER_ADDR'] = '127.0.0.1'

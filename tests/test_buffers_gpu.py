@@ -279,7 +279,8 @@ def _pp_worker(rank, world):
     sent = {0: 0, 1: 0}
     received = {0: 0, 1: 0}
     for _ in range(60):
-        d = rng.randrange(2)                       # 0: data flows towards next ranks, 1: towards previous ranks
+        # 0: data flows towards next ranks, 1: towards previous ranks (the two are one channel when world <= 2)
+        d = rng.randrange(2) if world > 2 else 0
         if sent[d] - received[d] < inflight and rng.random() < 0.6:
             x = torch.full((4096,), float(100 * d + sent[d] + rank), device='cuda', dtype=torch.bfloat16)
             pp.send(x, nxt if d == 0 else prv)
