@@ -53,7 +53,7 @@ def parse_args():
 class ClockSampler:
     """Samples SM clocks and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
 
-    QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
+    QUERY = ('timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
              'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
 
     def __init__(self, device_index: int):
@@ -69,7 +69,9 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
-    def stop(self) -> dict:
+    def stop(self, t_begin: float = 0.0, t_end: float = float('inf')) -> dict:
+        """Summarise the samples whose wall-clock timestamp lies in [t_begin, t_end] (the timed region)."""
+        import datetime
         if self.proc is None:
             return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
         self.proc.terminate()
@@ -86,6 +88,9 @@ class ClockSampler:
                 if len(parts) < 9:
                     continue
                 try:
+                    stamp = datetime.datetime.strptime(parts[0], '%Y/%m/%d %H:%M:%S.%f').timestamp()
+                    if not (t_begin - 0.05 <= stamp <= t_end + 0.05):
+                        continue
                     clocks.append(float(parts[1])), (max_clock := float(parts[2]))
                 except ValueError:
                     continue
@@ -108,10 +113,95 @@ def reference_arm(args):
         print(json.dumps({'impl': 'reference', 'unavailable': why}))
 
 
+def nccl_arm(args):
+    """Baseline on the same box: dispatch/combine built from NCCL `all_to_all_single` (what a framework without
+    this library would do), same configuration and byte accounting. Dispatch = permute + count exchange + payload
+    exchanges; combine = exchange back + index-add reduction. Whole-operation times, CUDA events, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from deep_ep.utils.math import per_token_cast_to_fp8
+    from deep_ep.utils.testing import L2Flusher
+    rank, world = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1))
+    local_rank = int(os.environ.get('LOCAL_RANK', 0))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+    os.environ.setdefault('MASTER_PORT', '29517')
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    torch.manual_seed(1234 + rank)
+    T, H, K, E = args.num_tokens, args.hidden, args.num_topk, args.num_experts
+    per_rank = E // world
+    x = torch.randn(T, H, dtype=torch.bfloat16, device=dev)
+    top_logits, topk_idx = torch.randn(T, E, device=dev).topk(K, dim=-1)
+    topk_w = torch.softmax(top_logits, dim=-1).float()
+    x_fp8, sf = per_token_cast_to_fp8(x)
+    flusher = L2Flusher()
+
+    def dispatch():
+        dst = topk_idx // per_rank
+        hit = torch.zeros(T, world, dtype=torch.bool, device=dev).scatter_(1, dst, True)
+        order = hit.t().reshape(-1).nonzero(as_tuple=True)[0] % T            # tokens grouped by destination rank
+        send_counts = hit.sum(0)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts)
+        sc, rc = send_counts.tolist(), recv_counts.tolist()
+        outs = []
+        for t in (x_fp8.view(torch.uint8), sf, topk_idx, topk_w):
+            out = torch.empty((sum(rc), t.size(1)), dtype=t.dtype, device=dev)
+            dist.all_to_all_single(out, t[order].contiguous(), rc, sc)
+            outs.append(out)
+        return outs, order, sc, rc
+
+    def combine(y, order, sc, rc):
+        back = torch.empty((sum(sc), H), dtype=torch.bfloat16, device=dev)
+        dist.all_to_all_single(back, y, sc, rc)
+        return torch.zeros(T, H, dtype=torch.float32, device=dev).index_add_(0, order, back.float()).to(torch.bfloat16)
+
+    outs, order, sc, rc = dispatch()
+    num_recv = sum(rc)
+    y = torch.randn(num_recv, H, dtype=torch.bfloat16, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        o, order, sc, rc = dispatch()
+        combine(y, order, sc, rc)
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    dist.barrier()
+    torch.cuda.synchronize()
+    for ev in events:
+        flusher()
+        ev[0].record()
+        o, order, sc, rc = dispatch()
+        ev[1].record()
+        flusher()
+        ev[2].record()
+        combine(y, order, sc, rc)
+        ev[3].record()
+    torch.cuda.synchronize()
+    d_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in events)
+    c_ms = statistics.mean(e[2].elapsed_time(e[3]) for e in events)
+    stats = torch.tensor([d_ms, c_ms, float(num_recv)], dtype=torch.float64, device=dev)
+    gathered = [torch.zeros_like(stats) for _ in range(world)]
+    dist.all_gather(gathered, stats)
+    g = torch.stack(gathered).cpu()
+    d_ms, c_ms = g[:, 0].max().item(), g[:, 1].max().item()
+    d_bytes = g[:, 2] * (H + (H // 128) * 4 + K * 8 + K * 4)
+    c_bytes = g[:, 2] * H * 2
+    if rank == 0:
+        print(json.dumps({'impl': 'nccl', 'metric': 'EP dispatch GB/s with NCCL all_to_all_single (same accounting)',
+                          'value': round(d_bytes.sum().item() / (d_ms * 1e6), 2), 'unit': 'GB/s', 'n_gpus': world,
+                          'steps': args.steps, 'warmup': max(args.warmup, 3),
+                          'per_rank': {'dispatch_gbs': round(d_bytes.min().item() / (d_ms * 1e6), 2),
+                                       'combine_gbs': round(c_bytes.min().item() / (c_ms * 1e6), 2),
+                                       'dispatch_ms': round(d_ms, 4), 'combine_ms': round(c_ms, 4)}}))
+    dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == 'reference':
         reference_arm(args)
+        return
+    if args.impl == 'nccl':
+        nccl_arm(args)
         return
 
     import torch
@@ -192,23 +282,25 @@ def main():
             events[3].record()
         return ev_c.current_stream_wait()
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()                      # nvidia-smi needs a moment to start: launch it before the warm-up
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank)
     events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     dist.barrier()
     torch.cuda.synchronize()
-    sampler.start()
+    t_begin = time.time()
     start.record()
     for i in range(args.steps):
         step(events[i])
     end.record()
     torch.cuda.synchronize()
+    t_end = time.time()
     dist.barrier()
-    clocks = sampler.stop()
+    clocks = sampler.stop(t_begin, t_end)
     total_ms = start.elapsed_time(end)
     dispatch_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in events)
     combine_ms = statistics.mean(e[2].elapsed_time(e[3]) for e in events)

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <deep_ep/kernels/ep_args.hpp>
+#include <deep_ep/kernels/grouped_gemm_args.hpp>
 #include <deep_ep/kernels/misc_args.hpp>
 
 namespace deep_ep::launch {
@@ -31,6 +32,11 @@ void engram_fetch(const kernels::EngramFetchArgs& args, int num_sms, cudaStream_
 void all_gather(const kernels::AllGatherArgs& args, int num_sms, cudaStream_t stream);
 void pp_send(const kernels::PPArgs& args, int num_sms, cudaStream_t stream);
 void pp_recv(const kernels::PPArgs& args, int num_sms, cudaStream_t stream);
+
+// Grouped BF16 GEMM on tcgen05 tensor cores over the expanded layout. `a`/`b` are row-major bf16 matrices
+// ([a_rows, a_cols], [b_rows, b_cols]); their roles depend on `args.mode` (see grouped_gemm.cuh).
+void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, int64_t a_cols,
+                  const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream);
 
 // Test hook: a one-warp kernel that waits (bounded) for a flag nobody sets and records the status.
 void bounded_wait_probe(layout::CommonSignals* cs, layout::HostStatus* host_status, long long timeout_ns,

@@ -1,0 +1,63 @@
+// Launcher of the grouped tcgen05 GEMM: builds the two TMA tensor maps (128-byte swizzle) and starts one
+// persistent CTA per SM.
+#include <algorithm>
+
+#include <deep_ep/common/exception.hpp>
+#include <deep_ep/kernels/grouped_gemm.cuh>
+
+#include "../runtime/driver.hpp"
+#include "api.hpp"
+
+namespace deep_ep::launch {
+
+namespace {
+
+// 2-D bf16 tensor map over a row-major [rows, cols] matrix with a {box_cols, box_rows} box.
+CUtensorMap make_map_2d(const void* base, int64_t rows, int64_t cols, int box_cols, int box_rows) {
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    EP_HOST_ASSERT(reinterpret_cast<uintptr_t>(base) % 16 == 0 and (cols * 2) % 16 == 0);
+    DRV_CHECK(driver::cuTensorMapEncodeTiled()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                                               box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+    return map;
+}
+
+}  // namespace
+
+void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, int64_t a_cols,
+                  const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream) {
+    using namespace kernels;
+    EP_HOST_ASSERT(args.num_groups > 0 and args.num_groups <= kMaxLocalExperts);
+    if (args.epilogue == kEpilogueSwiGLU) {
+        EP_HOST_ASSERT(args.mode == kModeForward and args.n % 256 == 0);
+        args.block_n = 256, args.block_n_out = 128, args.n_out = args.n / 2;
+    } else {
+        args.block_n = args.n % 256 == 0 ? 256 : 128;
+        EP_HOST_ASSERT_MSG(args.n % args.block_n == 0, "N must be a multiple of 128");
+        args.block_n_out = args.block_n, args.n_out = args.n;
+    }
+    if (args.mode == kModeWgrad) EP_HOST_ASSERT(args.m % kGemmBlockM == 0);
+    const int64_t budget = 200 * 1024;
+    args.num_stages = static_cast<int>(std::min<int64_t>(kGemmMaxStages, (budget - 1024) / ((kGemmBlockM + args.block_n) * kGemmBlockK * 2)));
+    EP_HOST_ASSERT(args.num_stages >= 2);
+
+    // A: K-major activations (box 64 x 128) or, for wgrad, MN-major (box 64 x 64)
+    const CUtensorMap map_a = args.mode == kModeWgrad ? make_map_2d(a, a_rows, a_cols, 64, 64) : make_map_2d(a, a_rows, a_cols, 64, 128);
+    // B: K-major weights (box 64 x 128) for forward, MN-major (box 64 x 64) otherwise
+    const CUtensorMap map_b = args.mode == kModeForward ? make_map_2d(b, b_rows, b_cols, 64, 128) : make_map_2d(b, b_rows, b_cols, 64, 64);
+
+    int device = 0, sms = 0;
+    CUDA_CHECK(cudaGetDevice(&device));
+    CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const int grid = num_sms > 0 ? std::min(num_sms, sms) : sms;
+    const auto smem = grouped_gemm_smem_bytes(args.block_n, args.num_stages);
+    CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    grouped_gemm_kernel<<<grid, 192, smem, stream>>>(map_a, map_b, args);
+    CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace deep_ep::launch

@@ -61,7 +61,8 @@ PipelineConfig choose_expand_config(int token_bytes, int num_topk, int num_local
 }
 
 PipelineConfig choose_combine_config(int token_bytes) {
-    for (int stages : {3, 2}) {
+    // two stages per warp are enough to overlap a row's store with the next row's loads; warps matter more
+    for (int stages : {2}) {
         for (int warps = 8; warps >= 2; --warps) {
             const auto bytes = kernels::combine_detail::smem_bytes(warps, stages, token_bytes);
             if (bytes <= kSmemBudget and (warps >= 4 or stages == 2)) return {warps, stages, bytes};

@@ -35,6 +35,58 @@ void clear_status(comm::Context& context) {
     if (context.common_signals != nullptr) CUDA_CHECK(cudaMemset(&context.common_signals->status, 0, sizeof(int)));
 }
 
+// Grouped GEMM over the expanded layout. mode 0: d[rows, n_out] = a[rows, k] * b[g, n, k]^T (optionally SwiGLU);
+// mode 1: d[rows, n] = a[rows, k] * b[g, k, n]; mode 2: d[g, m, n] += a[rows, m]^T * b[rows, n] (fp32).
+void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const torch::Tensor& psum,
+                  const torch::Tensor& count, int mode, int epilogue, int num_sms) {
+    using namespace kernels;
+    EP_HOST_ASSERT(a.is_cuda() and b.is_cuda() and d.is_cuda() and a.is_contiguous() and b.is_contiguous() and d.is_contiguous());
+    EP_HOST_ASSERT(a.scalar_type() == torch::kBFloat16 and b.scalar_type() == torch::kBFloat16 and a.dim() == 2 and b.dim() == 3);
+    EP_HOST_ASSERT(psum.scalar_type() == torch::kInt32 and count.scalar_type() == torch::kInt32 and psum.numel() == count.numel());
+    EP_HOST_ASSERT(psum.is_cuda() and count.is_cuda() and psum.is_contiguous() and count.is_contiguous());
+    GroupedGemmArgs args = {};
+    args.mode = mode, args.epilogue = epilogue, args.num_groups = static_cast<int>(psum.numel());
+    args.psum = psum.data_ptr<int>(), args.count = count.data_ptr<int>();
+    args.d = d.data_ptr(), args.status = nullptr;
+    const int64_t rows = a.size(0), g = args.num_groups;
+    int64_t b_rows, b_cols;
+    if (mode == kModeForward) {
+        EP_HOST_ASSERT(b.size(0) == g and b.size(2) == a.size(1));
+        args.n = static_cast<int>(b.size(1)), args.k = static_cast<int>(a.size(1));
+        b_rows = g * b.size(1), b_cols = b.size(2);
+        const int64_t n_out = epilogue == kEpilogueSwiGLU ? args.n / 2 : args.n;
+        EP_HOST_ASSERT(d.scalar_type() == torch::kBFloat16 and d.dim() == 2 and d.size(0) == rows and d.size(1) == n_out);
+        EP_HOST_ASSERT(args.k % 8 == 0);
+    } else if (mode == kModeDgrad) {
+        EP_HOST_ASSERT(b.size(0) == g and b.size(1) == a.size(1) and epilogue == kEpilogueStore);
+        args.n = static_cast<int>(b.size(2)), args.k = static_cast<int>(a.size(1));
+        b_rows = g * b.size(1), b_cols = b.size(2);
+        EP_HOST_ASSERT(d.scalar_type() == torch::kBFloat16 and d.dim() == 2 and d.size(0) == rows and d.size(1) == args.n);
+        EP_HOST_ASSERT(args.k % kGemmBlockK == 0);     // a K block must not run into the next expert's weight rows
+    } else {
+        EP_HOST_UNREACHABLE("use grouped_gemm_wgrad for mode 2");
+    }
+    launch::grouped_gemm(args, a.data_ptr(), rows, a.size(1), b.data_ptr(), b_rows, b_cols, num_sms, c10::cuda::getCurrentCUDAStream());
+}
+
+// d[g, m, n] (fp32) += a[rows_e, m]^T * b[rows_e, n] for every expert e; padding rows of `a` or `b` must be zero.
+void grouped_gemm_wgrad(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const torch::Tensor& psum,
+                        const torch::Tensor& count, int num_sms) {
+    using namespace kernels;
+    EP_HOST_ASSERT(a.is_cuda() and b.is_cuda() and d.is_cuda() and a.is_contiguous() and b.is_contiguous() and d.is_contiguous());
+    EP_HOST_ASSERT(a.scalar_type() == torch::kBFloat16 and b.scalar_type() == torch::kBFloat16 and a.dim() == 2 and b.dim() == 2);
+    EP_HOST_ASSERT(a.size(0) == b.size(0) and d.scalar_type() == torch::kFloat32 and d.dim() == 3);
+    EP_HOST_ASSERT(psum.scalar_type() == torch::kInt32 and count.scalar_type() == torch::kInt32 and psum.numel() == count.numel());
+    GroupedGemmArgs args = {};
+    args.mode = kModeWgrad, args.epilogue = kEpilogueStore, args.num_groups = static_cast<int>(psum.numel());
+    args.psum = psum.data_ptr<int>(), args.count = count.data_ptr<int>();
+    args.m = static_cast<int>(a.size(1)), args.n = static_cast<int>(b.size(1)), args.k = 0;
+    EP_HOST_ASSERT(d.size(0) == args.num_groups and d.size(1) == args.m and d.size(2) == args.n);
+    args.d = d.data_ptr(), args.status = nullptr;
+    launch::grouped_gemm(args, a.data_ptr(), a.size(0), a.size(1), b.data_ptr(), b.size(0), b.size(1), num_sms,
+                         c10::cuda::getCurrentCUDAStream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -97,6 +149,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         CUDA_CHECK(cudaDeviceCanAccessPeer(&ok, device, peer));
         return ok != 0;
     });
+
+    m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
+          py::arg("mode"), py::arg("epilogue") = 0, py::arg("num_sms") = 0);
+    m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
+          py::arg("num_sms") = 0);
 
     py::class_<BufferBase, std::shared_ptr<BufferBase>>(m, "BufferBase")
         .def_readonly("main_context", &BufferBase::main_context)

@@ -21,6 +21,8 @@
 
 #include <deep_ep/common/exception.hpp>
 
+#include "driver.hpp"
+
 namespace deep_ep::jit {
 
 // `EP_JIT_<NAME>` with `DJ_JIT_<NAME>` as fallback (the reference's environment contract).
@@ -113,17 +115,17 @@ public:
         auto it = loaded.find(key);
         if (it != loaded.end()) return it->second;
         CUmodule module;
-        CU_CHECK(cuModuleLoad(&module, cubin.c_str()));
+        DRV_CHECK(driver::cuModuleLoad()(&module, cubin.c_str()));
         modules.push_back(module);
         CUfunction fn;
-        CU_CHECK(cuModuleGetFunction(&fn, module, symbol.c_str()));
+        DRV_CHECK(driver::cuModuleGetFunction()(&fn, module, symbol.c_str()));
         loaded[key] = fn;
         return fn;
     }
 
     void launch(CUfunction fn, int grid, int block, int smem_bytes, CUstream stream, std::vector<void*>& args, bool cooperative = false) {
         if (smem_bytes > 48 * 1024)
-            CU_CHECK(cuFuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, smem_bytes));
+            DRV_CHECK(driver::cuFuncSetAttribute()(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, smem_bytes));
         CUlaunchConfig config = {};
         config.gridDimX = grid, config.gridDimY = 1, config.gridDimZ = 1;
         config.blockDimX = block, config.blockDimY = 1, config.blockDimZ = 1;
@@ -131,7 +133,7 @@ public:
         CUlaunchAttribute attr[1];
         attr[0].id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE, attr[0].value.cooperative = cooperative ? 1 : 0;
         config.attrs = attr, config.numAttrs = 1;
-        CU_CHECK(cuLaunchKernelEx(&config, fn, args.data(), nullptr));
+        DRV_CHECK(driver::cuLaunchKernelEx()(&config, fn, args.data(), nullptr));
     }
 };
 

@@ -40,13 +40,3 @@ public:
         if (e_ != cudaSuccess)                                                        \
             throw deep_ep::EPException("CUDA runtime", __FILE__, __LINE__, std::string(#expr) + " -> " + cudaGetErrorString(e_)); \
     } while (0)
-
-#define CU_CHECK(expr)                                                                \
-    do {                                                                              \
-        CUresult r_ = (expr);                                                         \
-        if (r_ != CUDA_SUCCESS) {                                                     \
-            const char* s_ = nullptr;                                                 \
-            cuGetErrorString(r_, &s_);                                                \
-            throw deep_ep::EPException("CUDA driver", __FILE__, __LINE__, std::string(#expr) + " -> " + (s_ ? s_ : "unknown")); \
-        }                                                                             \
-    } while (0)

@@ -1,0 +1,96 @@
+// Inline-PTX wrappers for the fifth-generation tensor cores of sm_100a: tensor-memory allocation,
+// `tcgen05.mma` issued by one thread, commit-to-mbarrier, tensor-memory loads for the epilogue, the
+// shared-memory matrix descriptors and the tiled TMA load that feeds them. Every TMA load here is
+// CTA-local (no cluster multicast).
+#pragma once
+
+#include <cuda.h>
+
+#include "ptx.cuh"
+
+namespace deep_ep::tc {
+
+// ---------------------------------------------------------------- tensor memory
+// Executed by one full warp. Writes the base address (lane 0, first column) to `smem_slot`.
+EP_DEVICE void tmem_alloc(uint32_t* smem_slot, uint32_t num_columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(ptx::smem_addr(smem_slot)), "r"(num_columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+EP_DEVICE void tmem_dealloc(uint32_t tmem_base, uint32_t num_columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(num_columns) : "memory");
+}
+EP_DEVICE void fence_before_thread_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+EP_DEVICE void fence_after_thread_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+EP_DEVICE void wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives row (lane base + t).
+EP_DEVICE void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+
+// ---------------------------------------------------------------- MMA
+// Instruction descriptor of kind::f16 / kind::f8f6f4: fp32 accumulation, dense, no negation.
+//   [4,6) D format (1 = F32)   [7,10) A format   [10,13) B format   [15] A major   [16] B major (0 = K, 1 = MN)
+//   [17,23) N >> 3             [24,29) M >> 4
+constexpr uint32_t kFormatBF16 = 1, kFormatE4M3 = 0;
+EP_HOST_DEVICE constexpr uint32_t make_idesc(uint32_t ab_format, int m, int n, bool a_mn_major, bool b_mn_major) {
+    return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
+           (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, tile base aligned to 1024 bytes.
+//   [0,14) address >> 4   [16,30) leading byte offset >> 4   [32,46) stride byte offset >> 4
+//   [46,48) version = 1   [61,64) layout = 2 (SWIZZLE_128B)
+// K-major tile (rows of 128 bytes along K): 8-row groups are `stride` = 1024 bytes apart; the leading
+// offset is unused. MN-major tile (rows of 128 bytes along M/N, one row per K index): 8 K-rows form a
+// 1024-byte atom, atoms along K are `stride` bytes apart, 64-element blocks along M/N are `leading` bytes apart.
+EP_DEVICE uint64_t make_smem_desc(const void* smem_ptr, uint32_t leading_bytes, uint32_t stride_bytes) {
+    uint64_t desc = 0;
+    desc |= uint64_t((ptx::smem_addr(smem_ptr) & 0x3ffff) >> 4);
+    desc |= uint64_t(leading_bytes >> 4) << 16;
+    desc |= uint64_t(stride_bytes >> 4) << 32;
+    desc |= uint64_t(1) << 46;
+    desc |= uint64_t(2) << 61;
+    return desc;
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
+EP_DEVICE void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(uint32_t(accumulate)) : "memory");
+}
+EP_DEVICE void mma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(uint32_t(accumulate)) : "memory");
+}
+// The mbarrier receives one arrival when every MMA issued so far by this thread has completed.
+EP_DEVICE void commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(ptx::smem_addr(bar)) : "memory");
+}
+
+// ---------------------------------------------------------------- tiled TMA load (2-D, CTA-local)
+// `x` is the innermost coordinate; x * element size must be a multiple of 16 bytes.
+EP_DEVICE void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(ptx::smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(ptx::smem_addr(bar)) : "memory");
+}
+EP_DEVICE void prefetch_tensormap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+}  // namespace deep_ep::tc

@@ -43,6 +43,62 @@ EP_DEVICE int4 pack(const float (&acc)[8]) {
 // index (0-based) of the q-th set bit of m; requires q < popc(m)
 EP_DEVICE int nth_set_bit(unsigned m, int q) { return __fns(m, 0, q + 1); }
 
+// fp32 sum, in top-k order, of `count` expanded rows (slots held one per lane, `valid` = lanes that hold one)
+// into a bf16 row in shared memory. Several 16-byte chunks per lane are loaded before the first add so that
+// enough requests are in flight to cover memory latency.
+template <int kSlots, int kChunks>
+EP_DEVICE void reduce_rows_impl(const uint8_t* x, int hidden_bytes, int chunks, const int (&sl)[kSlots], uint8_t* stage, int lane) {
+    for (int c0 = lane; c0 < chunks; c0 += 32 * kChunks) {
+        int4 v[kChunks][kSlots];
+        #pragma unroll
+        for (int i = 0; i < kChunks; ++i)
+            #pragma unroll
+            for (int u = 0; u < kSlots; ++u)
+                if (c0 + 32 * i < chunks and sl[u] >= 0) v[i][u] = ptx::ld_nc_v4(x + int64_t(sl[u]) * hidden_bytes + (c0 + 32 * i) * 16);
+        #pragma unroll
+        for (int i = 0; i < kChunks; ++i) {
+            if (c0 + 32 * i >= chunks) break;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            #pragma unroll
+            for (int u = 0; u < kSlots; ++u)
+                if (sl[u] >= 0) accumulate(acc, v[i][u]);
+            *reinterpret_cast<int4*>(stage + (c0 + 32 * i) * 16) = pack(acc);
+        }
+    }
+}
+
+EP_DEVICE void reduce_rows(const uint8_t* x, int hidden_bytes, int chunks, int my_slot, unsigned valid, int count,
+                           uint8_t* stage, int lane) {
+    if (count <= 4) {
+        int sl[4];
+        #pragma unroll
+        for (int u = 0; u < 4; ++u)
+            sl[u] = u < count ? __shfl_sync(0xffffffffu, my_slot, nth_set_bit(valid, min(u, count - 1))) : -1;
+        if (count == 2) {
+            const int s2[2] = {sl[0], sl[1]};
+            reduce_rows_impl<2, 4>(x, hidden_bytes, chunks, s2, stage, lane);
+        } else {
+            reduce_rows_impl<4, 4>(x, hidden_bytes, chunks, sl, stage, lane);
+        }
+    } else if (count <= 8) {
+        int sl[8];
+        #pragma unroll
+        for (int u = 0; u < 8; ++u)
+            sl[u] = u < count ? __shfl_sync(0xffffffffu, my_slot, nth_set_bit(valid, min(u, count - 1))) : -1;
+        reduce_rows_impl<8, 2>(x, hidden_bytes, chunks, sl, stage, lane);
+    } else {
+        for (int base = 0; base < chunks; base += 32) {       // warp-uniform trip count: shuffles inside
+            const int c = base + lane;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int u = 0; u < count; ++u) {
+                const int slot = __shfl_sync(0xffffffffu, my_slot, nth_set_bit(valid, u));
+                if (c < chunks) accumulate(acc, ptx::ld_nc_v4(x + int64_t(slot) * hidden_bytes + c * 16));
+            }
+            if (c < chunks) *reinterpret_cast<int4*>(stage + c * 16) = pack(acc);
+        }
+    }
+}
+
 }  // namespace combine_detail
 
 __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_constant__ CombineArgs a) {
@@ -118,25 +174,7 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
                     ptx::bulk_load(stage, a.x + int64_t(slot) * a.hidden_bytes, a.hidden_bytes, &mbar[stage_idx]);
                 }
             } else {
-                int sl[kUnroll];
-                #pragma unroll
-                for (int u = 0; u < kUnroll; ++u)
-                    sl[u] = u < count ? __shfl_sync(0xffffffffu, my_slot, nth_set_bit(valid, min(u, count - 1))) : -1;
-                for (int c = lane; c < chunks; c += 32) {
-                    int4 v[kUnroll];
-                    #pragma unroll
-                    for (int u = 0; u < kUnroll; ++u)
-                        if (sl[u] >= 0) v[u] = ptx::ld_nc_v4(a.x + int64_t(sl[u]) * a.hidden_bytes + c * 16);
-                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    #pragma unroll
-                    for (int u = 0; u < kUnroll; ++u)
-                        if (sl[u] >= 0) accumulate(acc, v[u]);
-                    for (int u = kUnroll; u < count; ++u) {     // rare: more than 8 local experts
-                        const int slot = __shfl_sync(0xffffffffu, my_slot, nth_set_bit(valid, u));
-                        accumulate(acc, ptx::ld_nc_v4(a.x + int64_t(slot) * a.hidden_bytes + c * 16));
-                    }
-                    *reinterpret_cast<int4*>(stage + c * 16) = pack(acc);
-                }
+                reduce_rows(a.x, a.hidden_bytes, chunks, my_slot, valid, count, stage, lane);
             }
             if (lane < k)
                 reinterpret_cast<float*>(stage + tl.weight_offset())[lane] =

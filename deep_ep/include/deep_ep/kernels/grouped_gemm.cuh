@@ -1,0 +1,269 @@
+// Grouped BF16 GEMM for the expert FFNs of an MoE layer on sm_100a tensor cores.
+//
+// One persistent kernel, 192 threads per CTA, three roles:
+//   warp 0   TMA producer   tiled `cp.async.bulk.tensor` loads of A and B tiles (128-byte swizzle) into a
+//                           shared-memory ring, completion on mbarriers
+//   warp 1   MMA issuer     one elected thread issues `tcgen05.mma` (M = 128, N = BLOCK_N, K = 16 per
+//                           instruction) with the accumulator in tensor memory, double buffered so that
+//                           the epilogue of tile i overlaps the main loop of tile i + 1
+//   warps 2-5 epilogue      `tcgen05.ld` the accumulator (one row per thread), optional SwiGLU or fp32
+//                           accumulate, vector stores to global memory
+//
+// Three problem shapes, all over the expanded dispatch layout (expert e owns rows
+// `[psum[e] - count[e], psum[e])`, regions padded to the expert alignment):
+//   kModeForward   D[rows_e, N]  = A[rows_e, K] * B_e[N, K]^T          (A and B K-major)
+//   kModeDgrad     D[rows_e, N]  = A[rows_e, K] * B_e[K, N]            (B MN-major: the weight as stored)
+//   kModeWgrad     D_e[M, N]    += A[rows_e, M]^T * B[rows_e, N]       (both MN-major, K = tokens of expert e)
+// The reference contains no matrix math; this kernel exists for the fused MoE layer that the library is
+// benchmarked in.
+#pragma once
+
+#include "../device/sync.cuh"
+#include "../device/tcgen05.cuh"
+#include "grouped_gemm_args.hpp"
+
+namespace deep_ep::kernels {
+
+namespace gemm_detail {
+
+EP_DEVICE float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+struct Tile {
+    int expert, m0, n0, row_base, rows_valid, num_k_blocks;
+};
+
+// tile index -> (expert, m block, n block). `prefix` holds the exclusive prefix of tiles per expert.
+EP_DEVICE Tile locate_tile(const GroupedGemmArgs& a, const int* prefix, int tile) {
+    int lo = 0, hi = a.num_groups - 1;
+    while (lo < hi) {                       // last expert whose prefix <= tile
+        const int mid = (lo + hi + 1) >> 1;
+        if (prefix[mid] <= tile) lo = mid; else hi = mid - 1;
+    }
+    const int e = lo, local = tile - prefix[e];
+    const int count = a.count[e], start = a.psum[e] - count;
+    Tile t;
+    t.expert = e, t.row_base = start;
+    if (a.mode == kModeWgrad) {
+        const int m_tiles = a.m / kGemmBlockM;
+        t.m0 = (local % m_tiles) * kGemmBlockM, t.n0 = (local / m_tiles) * a.block_n;
+        t.rows_valid = kGemmBlockM, t.num_k_blocks = math::ceil_div(count, kGemmBlockK);
+    } else {
+        const int m_tiles = math::ceil_div(count, kGemmBlockM);
+        t.m0 = (local % m_tiles) * kGemmBlockM, t.n0 = (local / m_tiles) * a.block_n_out;
+        t.rows_valid = min(kGemmBlockM, count - t.m0), t.num_k_blocks = math::ceil_div(a.k, kGemmBlockK);
+    }
+    return t;
+}
+
+}  // namespace gemm_detail
+
+__global__ void __launch_bounds__(192, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ GroupedGemmArgs a) {
+    using namespace gemm_detail;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[kGemmMaxStages], empty_bar[kGemmMaxStages], tmem_full_bar[2], tmem_empty_bar[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int tile_prefix[kMaxLocalExperts + 1];
+    __shared__ volatile int error_flag;
+
+    const int warp = threadIdx.x / 32, lane = ptx::lane_id();
+    const int S = a.num_stages, BN = a.block_n;
+    const uint32_t a_bytes = kGemmBlockM * kGemmBlockK * 2, b_bytes = uint32_t(BN) * kGemmBlockK * 2;
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + size_t(S) * a_bytes;
+
+    // ---- setup: barriers, tile schedule, tensor memory
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) ptx::mbarrier_init(&full_bar[s], 1), ptx::mbarrier_init(&empty_bar[s], 1);
+        for (int i = 0; i < 2; ++i) ptx::mbarrier_init(&tmem_full_bar[i], 1), ptx::mbarrier_init(&tmem_empty_bar[i], 4);
+        ptx::fence_mbarrier_init();
+        error_flag = 0;
+        tc::prefetch_tensormap(&map_a), tc::prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) tc::tmem_alloc(&tmem_base_slot, 512);
+    if (warp == 2) {
+        // exclusive prefix of tiles per expert (one warp, chunks of 32 experts)
+        int carry = 0;
+        for (int base = 0; base < a.num_groups; base += 32) {
+            const int e = base + lane;
+            int tiles = 0;
+            if (e < a.num_groups) {
+                const int count = a.count[e];
+                if (a.mode == kModeWgrad) tiles = count > 0 ? (a.m / kGemmBlockM) * (a.n / BN) : 0;
+                else tiles = math::ceil_div(count, kGemmBlockM) * (a.n_out / a.block_n_out);
+            }
+            int incl = tiles;
+            #pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            if (e < a.num_groups) tile_prefix[e] = carry + incl - tiles;
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) tile_prefix[a.num_groups] = carry;
+    }
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    tc::fence_after_thread_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    const int num_tiles = tile_prefix[a.num_groups];
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int it = 0;       // k-block counter over all tiles of this CTA (ring position)
+            for (int tile = blockIdx.x; tile < num_tiles and not error_flag; tile += gridDim.x) {
+                const Tile t = locate_tile(a, tile_prefix, tile);
+                for (int kb = 0; kb < t.num_k_blocks; ++kb, ++it) {
+                    const int s = it % S;
+                    if (not ptx::mbarrier_wait(&empty_bar[s], ((it / S) & 1) ^ 1)) { error_flag = 1; break; }
+                    ptx::mbarrier_arrive_expect_tx(&full_bar[s], a_bytes + b_bytes);
+                    uint8_t* sa = smem_a + size_t(s) * a_bytes;
+                    uint8_t* sb = smem_b + size_t(s) * b_bytes;
+                    const int k0 = kb * kGemmBlockK;
+                    if (a.mode == kModeWgrad) {
+                        // A = dY^T: source rows are K, columns (contiguous) are M
+                        for (int i = 0; i < kGemmBlockM / 64; ++i)
+                            tc::tma_load_2d(sa + i * 8192, &map_a, t.m0 + 64 * i, t.row_base + k0, &full_bar[s]);
+                        for (int i = 0; i < BN / 64; ++i)
+                            tc::tma_load_2d(sb + i * 8192, &map_b, t.n0 + 64 * i, t.row_base + k0, &full_bar[s]);
+                    } else {
+                        tc::tma_load_2d(sa, &map_a, k0, t.row_base + t.m0, &full_bar[s]);
+                        if (a.mode == kModeForward) {
+                            // K-major weights [G * N, K]; with SwiGLU the tile pairs 128 gate rows with 128 up rows
+                            const int row = t.expert * a.n;
+                            if (a.epilogue == kEpilogueSwiGLU) {
+                                tc::tma_load_2d(sb, &map_b, k0, row + t.n0, &full_bar[s]);
+                                tc::tma_load_2d(sb + 128 * 128, &map_b, k0, row + a.n / 2 + t.n0, &full_bar[s]);
+                            } else {
+                                for (int i = 0; i < BN / 128; ++i)
+                                    tc::tma_load_2d(sb + i * 128 * 128, &map_b, k0, row + t.n0 + 128 * i, &full_bar[s]);
+                            }
+                        } else {
+                            // MN-major weights [G * K, N]
+                            for (int i = 0; i < BN / 64; ++i)
+                                tc::tma_load_2d(sb + i * 8192, &map_b, t.n0 + 64 * i, t.expert * a.k + k0, &full_bar[s]);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const bool a_mn = a.mode == kModeWgrad, b_mn = a.mode != kModeForward;
+            const uint32_t idesc = tc::make_idesc(tc::kFormatBF16, kGemmBlockM, BN, a_mn, b_mn);
+            // descriptor strides: K-major -> 8-row groups 1024 B apart; MN-major -> K atoms 1024 B apart, 64-wide blocks 8192 B apart
+            const uint32_t a_lead = a_mn ? 8192 : 16, b_lead = b_mn ? 8192 : 16;
+            const uint32_t a_kstep = a_mn ? 2048 : 32, b_kstep = b_mn ? 2048 : 32;     // bytes per K = 16
+            int it = 0, local_tile = 0;
+            for (int tile = blockIdx.x; tile < num_tiles and not error_flag; tile += gridDim.x, ++local_tile) {
+                const Tile t = locate_tile(a, tile_prefix, tile);
+                const int acc = local_tile & 1, use = local_tile >> 1;
+                if (not ptx::mbarrier_wait(&tmem_empty_bar[acc], (use & 1) ^ 1)) { error_flag = 1; break; }
+                tc::fence_after_thread_sync();
+                const uint32_t tmem_d = tmem_base + acc * 256;
+                for (int kb = 0; kb < t.num_k_blocks; ++kb, ++it) {
+                    const int s = it % S;
+                    if (not ptx::mbarrier_wait(&full_bar[s], (it / S) & 1)) { error_flag = 1; break; }
+                    tc::fence_after_thread_sync();
+                    const uint8_t* sa = smem_a + size_t(s) * a_bytes;
+                    const uint8_t* sb = smem_b + size_t(s) * b_bytes;
+                    #pragma unroll
+                    for (int k = 0; k < kGemmBlockK / 16; ++k) {
+                        const uint64_t da = tc::make_smem_desc(sa + k * a_kstep, a_lead, 1024);
+                        const uint64_t db = tc::make_smem_desc(sb + k * b_kstep, b_lead, 1024);
+                        tc::mma_f16(tmem_d, da, db, idesc, kb > 0 or k > 0);
+                    }
+                    tc::commit(&empty_bar[s]);          // stage is free once these MMAs have read it
+                }
+                tc::commit(&tmem_full_bar[acc]);        // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;                    // tensor-memory lane quarter this warp may access
+        const int row = quarter * 32 + lane;
+        int local_tile = 0;
+        for (int tile = blockIdx.x; tile < num_tiles and not error_flag; tile += gridDim.x, ++local_tile) {
+            const Tile t = locate_tile(a, tile_prefix, tile);
+            const int acc = local_tile & 1, use = local_tile >> 1;
+            if (not ptx::mbarrier_wait(&tmem_full_bar[acc], use & 1)) { error_flag = 1; break; }
+            tc::fence_after_thread_sync();
+            const uint32_t taddr = tmem_base + acc * 256 + (uint32_t(quarter * 32) << 16);
+            const bool valid = row < t.rows_valid;
+            if (a.mode == kModeWgrad) {
+                float* out = reinterpret_cast<float*>(a.d) + (size_t(t.expert) * a.m + t.m0 + row) * a.n + t.n0;
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(taddr + c, r);
+                    tc::wait_ld();
+                    #pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        float4 old = *reinterpret_cast<float4*>(out + c + 4 * v);
+                        old.x += __uint_as_float(r[4 * v]), old.y += __uint_as_float(r[4 * v + 1]);
+                        old.z += __uint_as_float(r[4 * v + 2]), old.w += __uint_as_float(r[4 * v + 3]);
+                        *reinterpret_cast<float4*>(out + c + 4 * v) = old;
+                    }
+                }
+            } else if (a.epilogue == kEpilogueSwiGLU) {
+                __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + size_t(t.row_base + t.m0 + row) * a.n_out + t.n0;
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t g[32], u[32];
+                    tc::tmem_ld_32x32(taddr + c, g);
+                    tc::tmem_ld_32x32(taddr + 128 + c, u);
+                    tc::wait_ld();
+                    if (valid) {
+                        #pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            int4 packed;
+                            uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+                            #pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int j = 8 * v + 2 * i;
+                                w[i] = ptx::float2_to_bf16x2(silu(__uint_as_float(g[j])) * __uint_as_float(u[j]),
+                                                             silu(__uint_as_float(g[j + 1])) * __uint_as_float(u[j + 1]));
+                            }
+                            *reinterpret_cast<int4*>(out + c + 8 * v) = packed;
+                        }
+                    }
+                }
+            } else {
+                __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + size_t(t.row_base + t.m0 + row) * a.n_out + t.n0;
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(taddr + c, r);
+                    tc::wait_ld();
+                    if (valid) {
+                        #pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            int4 packed;
+                            uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+                            #pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                w[i] = ptx::float2_to_bf16x2(__uint_as_float(r[8 * v + 2 * i]), __uint_as_float(r[8 * v + 2 * i + 1]));
+                            *reinterpret_cast<int4*>(out + c + 8 * v) = packed;
+                        }
+                    }
+                }
+            }
+            tc::fence_before_thread_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbarrier_arrive(&tmem_empty_bar[acc]);
+        }
+    }
+
+    // ---- teardown: every thread arrives here, then the allocating warp frees tensor memory
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_thread_sync();
+        tc::tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 and error_flag and a.status != nullptr) atomicExch(a.status, 1);
+}
+
+}  // namespace deep_ep::kernels

@@ -1,31 +1,128 @@
-"""Per-expert SwiGLU FFN over the expanded dispatch layout.
+"""Grouped GEMMs of the expert FFNs over the expanded dispatch layout, on tcgen05 tensor cores.
 
-`grouped_swiglu_ffn` computes, for every local expert e and its rows `[start_e, start_e + count_e)`,
-`(silu(x W_gate_e^T) * (x W_up_e^T)) W_down_e^T`. Backend `'torch'` loops over experts with library GEMMs
-(the comparison baseline); backend `'grouped'` uses the hand-written sm_100a grouped GEMM kernels when they
-are available for the shape and falls back to the loop otherwise.
+Expert e owns rows `[psum[e] - count[e], psum[e])` of the expanded activations (`psum` and `count` are the
+handle's `psum_num_recv_tokens_per_expert` and `num_unaligned_recv_tokens_per_expert`, on the device: no host
+synchronisation is needed to launch). Three kernels modes cover a linear layer's forward, data gradient and
+weight gradient; `GroupedLinear` ties them into autograd and `grouped_swiglu_ffn` builds the SwiGLU FFN.
+Backend `'torch'` is the library-GEMM loop used as the comparison baseline and as the oracle in tests.
 """
 from typing import List, Optional
 
 import torch
 import torch.nn.functional as F
 
+from .._C_loader import _C
 
-def _expert_ranges(psum: torch.Tensor, unaligned: torch.Tensor, per_expert_list: Optional[List[int]], alignment: int):
-    """(start, count) per local expert on the host; one device-to-host read when no host list exists."""
-    ends = psum.tolist()
-    counts = unaligned.tolist()
-    return [(e - c, c) for e, c in zip(ends, counts)]
+MODE_FORWARD, MODE_DGRAD, MODE_WGRAD = 0, 1, 2
+EPILOGUE_STORE, EPILOGUE_SWIGLU = 0, 1
+
+
+def grouped_gemm_forward(x: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
+                         swiglu: bool = False, num_sms: int = 0) -> torch.Tensor:
+    """`y[rows_e] = x[rows_e] @ w[e].T` with `w [G, N, K]`; with `swiglu`, `w[e] = [gate; up]` and
+    `y = silu(x @ gate.T) * (x @ up.T)` (`[rows, N / 2]`). Rows outside every expert's range are left untouched."""
+    n_out = w.size(1) // 2 if swiglu else w.size(1)
+    y = torch.empty((x.size(0), n_out), dtype=torch.bfloat16, device=x.device)
+    _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_SWIGLU if swiglu else EPILOGUE_STORE, num_sms)
+    return y
+
+
+def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
+                       num_sms: int = 0) -> torch.Tensor:
+    """`dx[rows_e] = dy[rows_e] @ w[e]` with `w [G, N, K]` read as stored (no transpose copy)."""
+    dx = torch.empty((dy.size(0), w.size(2)), dtype=torch.bfloat16, device=dy.device)
+    _C.grouped_gemm(dy, w, dx, psum, count, MODE_DGRAD, EPILOGUE_STORE, num_sms)
+    return dx
+
+
+def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, dw: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
+                       num_sms: int = 0) -> torch.Tensor:
+    """`dw[e] += dy[rows_e].T @ x[rows_e]` accumulated in fp32 (`dw [G, N, K]` fp32). Padding rows of `dy` or `x`
+    up to the next multiple of 64 rows must be zero."""
+    _C.grouped_gemm_wgrad(dy, x, dw, psum, count, num_sms)
+    return dw
+
+
+def _ranges(psum: torch.Tensor, count: torch.Tensor):
+    return [(e - c, c) for e, c in zip(psum.tolist(), count.tolist())]
+
+
+def _supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.size(1) % 128 == 0 and \
+        w.size(2) % 128 == 0
+
+
+class GroupedLinear(torch.autograd.Function):
+    """`y = x @ w[e].T` per expert. Weight gradients are accumulated in fp32: into `w.main_grad` when the parameter
+    carries such a buffer, otherwise into a fresh fp32 tensor that is cast to the parameter dtype."""
+
+    @staticmethod
+    def forward(ctx, x, w, psum, count, alignment):
+        ctx.save_for_backward(x, w, psum, count)
+        ctx.alignment = alignment
+        return grouped_gemm_forward(x, w, psum, count)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, psum, count = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = grouped_gemm_dgrad(dy, w, psum, count) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(w, 'main_grad', None)
+            acc = main_grad if main_grad is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+            if ctx.alignment % 64 == 0:
+                grouped_gemm_wgrad(dy, x, acc, psum, count)
+            else:
+                for e, (start, c) in enumerate(_ranges(psum, count)):
+                    if c:
+                        acc[e].addmm_(dy[start:start + c].float().t(), x[start:start + c].float())
+            dw = None if main_grad is not None else acc.to(w.dtype)
+        if dx is not None:
+            # rows that belong to no expert (alignment padding) carry no gradient
+            pass
+        return dx, dw, None, None, None
+
+
+def _torch_ffn(x, w_gate_up, w_down, psum, count):
+    out = torch.zeros((x.size(0), w_down.size(1)), dtype=x.dtype, device=x.device)
+    for e, (start, c) in enumerate(_ranges(psum, count)):
+        if c == 0:
+            continue
+        rows = x[start:start + c]
+        g, u = F.linear(rows, w_gate_up[e]).chunk(2, dim=-1)
+        out[start:start + c] = F.linear(F.silu(g) * u, w_down[e])
+    return out
 
 
 def grouped_swiglu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, psum: torch.Tensor,
                        unaligned: torch.Tensor, per_expert_list: Optional[List[int]], alignment: int,
                        backend: str = 'grouped') -> torch.Tensor:
-    out = torch.zeros_like(x)
-    for e, (start, count) in enumerate(_expert_ranges(psum, unaligned, per_expert_list, alignment)):
-        if count == 0:
-            continue
-        rows = x[start:start + count]
-        g, u = F.linear(rows, w_gate_up[e]).chunk(2, dim=-1)
-        out[start:start + count] = F.linear(F.silu(g) * u, w_down[e])
-    return out
+    """SwiGLU FFN of every local expert on its rows. `w_gate_up [G, 2I, H]` (gate rows first), `w_down [G, H, I]`.
+
+    Padding rows of the result are zero. In inference mode the SwiGLU is fused into the first GEMM's epilogue;
+    under autograd the pre-activation is kept for the backward pass.
+    """
+    if backend == 'torch' or not (_supported(x, w_gate_up) and _supported(x, w_down)):
+        return _torch_ffn(x, w_gate_up, w_down, psum, unaligned)
+    if not torch.is_grad_enabled() or not (x.requires_grad or w_gate_up.requires_grad or w_down.requires_grad):
+        if w_gate_up.size(1) % 256 == 0:
+            act = grouped_gemm_forward(x, w_gate_up, psum, unaligned, swiglu=True)
+        else:
+            g, u = grouped_gemm_forward(x, w_gate_up, psum, unaligned).chunk(2, dim=-1)
+            act = F.silu(g) * u
+        y = grouped_gemm_forward(act, w_down, psum, unaligned)
+    else:
+        h = GroupedLinear.apply(x, w_gate_up, psum, unaligned, alignment)
+        g, u = h.chunk(2, dim=-1)
+        y = GroupedLinear.apply((F.silu(g) * u).contiguous(), w_down, psum, unaligned, alignment)
+    return mask_padding_rows(y, psum, unaligned)
+
+
+def mask_padding_rows(y: torch.Tensor, psum: torch.Tensor, count: torch.Tensor) -> torch.Tensor:
+    """Zero the rows of `y` that belong to no expert (alignment padding), without a host synchronisation."""
+    rows = torch.arange(y.size(0), device=y.device)
+    idx = torch.searchsorted(psum.long(), rows, right=True).clamp(max=psum.numel() - 1)
+    start = (psum - count).long()[idx]
+    valid = (rows >= start) & (rows < psum.long()[idx])
+    return y * valid.unsqueeze(1).to(y.dtype)

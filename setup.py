@@ -38,7 +38,6 @@ setup(
         sources=sources,
         include_dirs=include_dirs,
         extra_compile_args={'cxx': cxx_flags, 'nvcc': nvcc_flags},
-        libraries=['cuda'],
     )],
     cmdclass={'build_ext': BuildExtension.with_options(use_ninja=True)},
 )
