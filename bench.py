@@ -65,7 +65,7 @@ class ClockSampler:
         try:
             self.out = open(self.path, 'w')
             self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits',
-                                          '-lms', '50', '-i', str(self.device_index)], stdout=self.out, stderr=subprocess.DEVNULL)
+                                          '-lms', '20', '-i', str(self.device_index)], stdout=self.out, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 

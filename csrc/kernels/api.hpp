@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <deep_ep/kernels/ep_args.hpp>
+#include <deep_ep/kernels/ep_layout_args.hpp>
 #include <deep_ep/kernels/grouped_gemm_args.hpp>
 #include <deep_ep/kernels/misc_args.hpp>
 
@@ -32,6 +33,10 @@ void engram_fetch(const kernels::EngramFetchArgs& args, int num_sms, cudaStream_
 void all_gather(const kernels::AllGatherArgs& args, int num_sms, cudaStream_t stream);
 void pp_send(const kernels::PPArgs& args, int num_sms, cudaStream_t stream);
 void pp_recv(const kernels::PPArgs& args, int num_sms, cudaStream_t stream);
+
+// Standalone routing layout (cooperative launch, at most `kLayoutMaxCtas` CTAs). `args.scratch` must point to a
+// zero-initialised `LayoutScratch` in device memory.
+void dispatch_layout(const kernels::LayoutArgs& args, int num_sms, cudaStream_t stream);
 
 // Grouped BF16 GEMM on tcgen05 tensor cores over the expanded layout. `a`/`b` are row-major bf16 matrices
 // ([a_rows, a_cols], [b_rows, b_cols]); their roles depend on `args.mode` (see grouped_gemm.cuh).

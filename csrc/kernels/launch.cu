@@ -7,6 +7,7 @@
 #include <deep_ep/kernels/ep_combine.cuh>
 #include <deep_ep/kernels/ep_dispatch.cuh>
 #include <deep_ep/kernels/ep_expand.cuh>
+#include <deep_ep/kernels/ep_layout.cuh>
 #include <deep_ep/kernels/misc.cuh>
 
 #include "api.hpp"
@@ -98,6 +99,14 @@ void combine(kernels::CombineArgs args, int num_sms, cudaStream_t stream) {
 
 void combine_reduce(kernels::CombineReduceArgs args, int num_sms, cudaStream_t stream) {
     launch_kernel(kernels::ep_combine_reduce_kernel, args, clamp_sms(num_sms), 256, 0, false, stream);
+}
+
+void dispatch_layout(const kernels::LayoutArgs& args, int num_sms, cudaStream_t stream) {
+    EP_HOST_ASSERT(args.num_experts <= kMaxExperts and args.num_ranks <= kMaxRanks and args.num_topk <= kMaxTopk);
+    EP_HOST_ASSERT(args.num_ranks > 0 and args.num_experts % args.num_ranks == 0);
+    const int grid = std::max(1, std::min({num_sms > 0 ? num_sms : kernels::kLayoutMaxCtas, kernels::kLayoutMaxCtas,
+                                           (args.num_tokens + 255) / 256 > 0 ? (args.num_tokens + 255) / 256 : 1}));
+    launch_kernel(kernels::ep_layout_kernel, args, grid, 256, 0, true, stream);
 }
 
 void barrier(const kernels::BarrierArgs& args, cudaStream_t stream) {

@@ -35,6 +35,29 @@ void clear_status(comm::Context& context) {
     if (context.common_signals != nullptr) CUDA_CHECK(cudaMemset(&context.common_signals->status, 0, sizeof(int)));
 }
 
+// Routing layout of a set of tokens without communication: (dst_buffer_slot_idx [T, k], num_tokens_per_rank [R],
+// num_tokens_per_expert [E]). Scratch memory is a zero-filled torch allocation per call.
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> get_dispatch_layout(const torch::Tensor& topk_idx, int num_experts,
+                                                                            int num_ranks, int num_sms) {
+    EP_HOST_ASSERT(topk_idx.is_cuda() and topk_idx.dim() == 2 and topk_idx.is_contiguous() and topk_idx.scalar_type() == torch::kInt64);
+    const auto int_options = torch::TensorOptions().dtype(torch::kInt32).device(topk_idx.device());
+    auto slots = torch::empty({topk_idx.size(0), topk_idx.size(1)}, int_options);
+    auto per_rank = torch::empty({num_ranks}, int_options);
+    auto per_expert = torch::empty({num_experts}, int_options);
+    auto scratch = torch::zeros({static_cast<int64_t>(sizeof(kernels::LayoutScratch))},
+                                torch::TensorOptions().dtype(torch::kUInt8).device(topk_idx.device()));
+    kernels::LayoutArgs args = {};
+    args.topk_idx = topk_idx.data_ptr<int64_t>();
+    args.num_tokens = static_cast<int>(topk_idx.size(0)), args.num_topk = static_cast<int>(topk_idx.size(1));
+    args.num_experts = num_experts, args.num_ranks = num_ranks;
+    args.dst_slot_idx = slots.data_ptr<int>(), args.num_tokens_per_rank = per_rank.data_ptr<int>();
+    args.num_tokens_per_expert = per_expert.data_ptr<int>();
+    args.scratch = reinterpret_cast<kernels::LayoutScratch*>(scratch.data_ptr());
+    args.timeout_ns = 10ll * 1000000000ll, args.status = nullptr;
+    launch::dispatch_layout(args, num_sms, c10::cuda::getCurrentCUDAStream());
+    return {slots, per_rank, per_expert};
+}
+
 // Grouped GEMM over the expanded layout. mode 0: d[rows, n_out] = a[rows, k] * b[g, n, k]^T (optionally SwiGLU);
 // mode 1: d[rows, n] = a[rows, k] * b[g, k, n]; mode 2: d[g, m, n] += a[rows, m]^T * b[rows, n] (fp32).
 void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const torch::Tensor& psum,
@@ -150,6 +173,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         return ok != 0;
     });
 
+    m.def("get_dispatch_layout", &get_dispatch_layout, py::arg("topk_idx"), py::arg("num_experts"), py::arg("num_ranks"),
+          py::arg("num_sms") = 0);
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
           py::arg("mode"), py::arg("epilogue") = 0, py::arg("num_sms") = 0);
     m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),

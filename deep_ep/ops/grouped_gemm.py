@@ -125,4 +125,4 @@ def mask_padding_rows(y: torch.Tensor, psum: torch.Tensor, count: torch.Tensor) 
     idx = torch.searchsorted(psum.long(), rows, right=True).clamp(max=psum.numel() - 1)
     start = (psum - count).long()[idx]
     valid = (rows >= start) & (rows < psum.long()[idx])
-    return y * valid.unsqueeze(1).to(y.dtype)
+    return torch.where(valid.unsqueeze(1), y, torch.zeros((), dtype=y.dtype, device=y.device))

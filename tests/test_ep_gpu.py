@@ -45,3 +45,17 @@ def test_ep_multi_gpu(master_port, case):
     if case[3] % world:
         pytest.skip('experts not divisible')
     run_distributed(_ep_worker, world, master_port, 'nccl', case)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('num_tokens,num_topk,num_experts,num_ranks', [(1, 4, 16, 2), (1000, 6, 256, 8), (16384, 8, 256, 8), (333, 32, 64, 64)])
+def test_dispatch_layout_matches_cpu_rule(num_tokens, num_topk, num_experts, num_ranks):
+    from deep_ep.ops.layout import get_dispatch_layout
+    torch.manual_seed(3)
+    idx = torch.rand(num_tokens, num_experts).topk(num_topk, dim=-1).indices
+    idx = idx.masked_fill(torch.rand(idx.shape) < 0.1, -1)
+    ref_slots, ref_rank, ref_expert = get_dispatch_layout(idx, num_experts, num_ranks)
+    for _ in range(2):        # scratch state must not leak between launches
+        slots, per_rank, per_expert = get_dispatch_layout(idx.cuda(), num_experts, num_ranks)
+        assert torch.equal(slots.cpu(), ref_slots) and torch.equal(per_rank.cpu(), ref_rank)
+        assert torch.equal(per_expert.cpu(), ref_expert)
