@@ -1,0 +1,152 @@
+"""MoE layer forward+backward: this library (EPBuffer dispatch/combine + tcgen05 grouped GEMMs) against the
+conventional NCCL `all_to_all_single` + per-expert library-GEMM layer, same shapes, same box.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 benchmarks/moe_layer.py
+
+DeepSeek-V3-like expert FFN: 4096 tokens per rank, hidden 7168, intermediate 2048, SwiGLU, 256 routed experts,
+top-8, one shared expert; random-init weights ~ N(0, 0.02), BF16 compute with fp32 weight-gradient accumulation.
+A step is forward + backward of the layer (no optimizer: the layer is a communication+GEMM benchmark).
+Times are CUDA events per step, maximum over ranks.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.distributed.nn.functional as dist_fn
+import torch.nn as nn
+import torch.nn.functional as F
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import deep_ep  # noqa: E402
+from deep_ep.models.moe_layer import MoEConfig, MoELayer  # noqa: E402
+
+
+class BaselineMoELayer(nn.Module):
+    """Permute by expert, `all_to_all_single` the (token, expert) copies, per-expert `F.linear`, exchange back, weighted sum."""
+
+    def __init__(self, ours: MoELayer):
+        super().__init__()
+        self.group, self.config = ours.group, ours.config
+        self.world = ours.num_ranks
+        self.num_local_experts = ours.num_local_experts
+        self.gate = ours.gate
+        self.w_gate_up = nn.Parameter(ours.w_gate_up.detach().clone())
+        self.w_down = nn.Parameter(ours.w_down.detach().clone())
+        self.shared_gate_up = nn.Parameter(ours.shared_gate_up.detach().clone()) if ours.config.num_shared_experts else None
+        self.shared_down = nn.Parameter(ours.shared_down.detach().clone()) if ours.config.num_shared_experts else None
+        self.route = ours.route
+
+    def forward(self, x):
+        cfg = self.config
+        topk_idx, topk_w = self.route(x.detach())
+        t, k = topk_idx.shape
+        flat_expert = topk_idx.reshape(-1)
+        order = torch.argsort(flat_expert, stable=True)                      # (token, slot) pairs grouped by expert
+        send = x[order // k]
+        per_expert = torch.bincount(flat_expert, minlength=cfg.num_experts)
+        send_counts = per_expert.view(self.world, self.num_local_experts).sum(1)
+        recv_per_expert = torch.empty_like(per_expert)
+        dist.all_to_all_single(recv_per_expert, per_expert, group=self.group)   # [src rank, local expert]
+        recv_counts = recv_per_expert.view(self.world, self.num_local_experts).sum(1)
+        sc, rc = send_counts.tolist(), recv_counts.tolist()
+        recv = dist_fn.all_to_all_single(torch.empty((sum(rc), x.size(1)), dtype=x.dtype, device=x.device), send, rc, sc,
+                                         group=self.group)
+        # received rows are (src rank, local expert) ordered: regroup by local expert
+        counts = recv_per_expert.view(self.world, self.num_local_experts)
+        expert_of_row = torch.repeat_interleave(torch.arange(self.num_local_experts, device=x.device).repeat(self.world),
+                                                counts.reshape(-1))
+        by_expert = torch.argsort(expert_of_row, stable=True)
+        rows = recv[by_expert]
+        out = torch.empty_like(rows)
+        start = 0
+        for e, c in enumerate(counts.sum(0).tolist()):
+            if c:
+                g, u = F.linear(rows[start:start + c], self.w_gate_up[e]).chunk(2, dim=-1)
+                out[start:start + c] = F.linear(F.silu(g) * u, self.w_down[e])
+            start += c
+        back_rows = torch.empty_like(out)
+        back_rows[by_expert] = out
+        back = dist_fn.all_to_all_single(torch.empty((sum(sc), x.size(1)), dtype=x.dtype, device=x.device), back_rows, sc, rc,
+                                         group=self.group)
+        weighted = back * topk_w.reshape(-1)[order].unsqueeze(1).to(back.dtype)
+        y = torch.zeros_like(x).index_add_(0, order // k, weighted)
+        if self.shared_gate_up is not None:
+            g, u = F.linear(x, self.shared_gate_up).chunk(2, dim=-1)
+            y = y + F.linear(F.silu(g) * u, self.shared_down)
+        return y
+
+
+def time_layer(layer, x, steps, warmup):
+    grad = torch.randn_like(x)
+    for _ in range(warmup):
+        layer(x).backward(grad)
+    for p in layer.parameters():
+        p.grad = None
+    torch.cuda.synchronize()
+    dist.barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in ev:
+        a.record()
+        layer(x).backward(grad)
+        b.record()
+    torch.cuda.synchronize()
+    ms = sum(a.elapsed_time(b) for a, b in ev) / steps
+    t = torch.tensor([ms], device=x.device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument('--num-tokens', type=int, default=4096)
+    p.add_argument('--hidden', type=int, default=7168)
+    p.add_argument('--intermediate', type=int, default=2048)
+    p.add_argument('--num-experts', type=int, default=256)
+    p.add_argument('--num-topk', type=int, default=8)
+    p.add_argument('--steps', type=int, default=10)
+    p.add_argument('--warmup', type=int, default=3)
+    p.add_argument('--skip-baseline', action='store_true')
+    args = p.parse_args()
+    rank, world = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1))
+    local_rank = int(os.environ.get('LOCAL_RANK', 0))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+    os.environ.setdefault('MASTER_PORT', '29551')
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    torch.manual_seed(7 + rank)
+    cfg = MoEConfig(hidden=args.hidden, intermediate=args.intermediate, num_experts=args.num_experts, num_topk=args.num_topk,
+                    num_shared_experts=1, num_max_tokens_per_rank=args.num_tokens, expert_alignment=128)
+    ours = MoELayer(dist.group.WORLD, cfg).to(dev)
+    x = torch.randn(args.num_tokens, args.hidden, device=dev, dtype=torch.bfloat16, requires_grad=True)
+
+    result = {'bench': 'moe_layer_fwd_bwd', 'n_gpus': world, 'tokens_per_rank': args.num_tokens, 'hidden': args.hidden,
+              'intermediate': args.intermediate, 'experts': args.num_experts, 'topk': args.num_topk, 'dtype': 'bf16'}
+    if not args.skip_baseline:
+        base = BaselineMoELayer(ours).to(dev)
+        with torch.no_grad():                      # same function, different plumbing: outputs must agree
+            y_ours, y_base = ours(x), base(x)
+        rel = ((y_ours.float() - y_base.float()).norm() / y_base.float().norm()).item()
+        result['rel_diff_vs_baseline'] = round(rel, 5)
+        result['baseline_ms'] = round(time_layer(base, x, args.steps, args.warmup), 3)
+        del base
+        torch.cuda.empty_cache()
+    result['ours_ms'] = round(time_layer(ours, x, args.steps, args.warmup), 3)
+    # useful FLOPs: 3 GEMMs (gate, up, down) x (fwd + dgrad + wgrad) over routed + shared expert rows
+    rows = args.num_tokens * (args.num_topk + 1)
+    flops = 3 * 2 * rows * args.hidden * args.intermediate * 3
+    result['ours_tflops_per_gpu'] = round(flops / (result['ours_ms'] * 1e-3) / 1e12, 1)
+    result['tokens_per_s_total'] = round(args.num_tokens * world / (result['ours_ms'] * 1e-3))
+    if 'baseline_ms' in result:
+        result['speedup'] = round(result['baseline_ms'] / result['ours_ms'], 3)
+    if rank == 0:
+        print(json.dumps(result))
+    ours.destroy()
+    dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

@@ -101,12 +101,18 @@ void combine_reduce(kernels::CombineReduceArgs args, int num_sms, cudaStream_t s
     launch_kernel(kernels::ep_combine_reduce_kernel, args, clamp_sms(num_sms), 256, 0, false, stream);
 }
 
+namespace {
+__global__ void __launch_bounds__(256, 1) ep_layout_kernel(const __grid_constant__ kernels::LayoutArgs a) {
+    kernels::ep_layout_body(a);
+}
+}  // namespace
+
 void dispatch_layout(const kernels::LayoutArgs& args, int num_sms, cudaStream_t stream) {
     EP_HOST_ASSERT(args.num_experts <= kMaxExperts and args.num_ranks <= kMaxRanks and args.num_topk <= kMaxTopk);
     EP_HOST_ASSERT(args.num_ranks > 0 and args.num_experts % args.num_ranks == 0);
     const int grid = std::max(1, std::min({num_sms > 0 ? num_sms : kernels::kLayoutMaxCtas, kernels::kLayoutMaxCtas,
                                            (args.num_tokens + 255) / 256 > 0 ? (args.num_tokens + 255) / 256 : 1}));
-    launch_kernel(kernels::ep_layout_kernel, args, grid, 256, 0, true, stream);
+    launch_kernel(ep_layout_kernel, args, grid, 256, 0, true, stream);
 }
 
 void barrier(const kernels::BarrierArgs& args, cudaStream_t stream) {

@@ -11,6 +11,8 @@
 
 namespace deep_ep::kernels {
 
+// Body of the kernel; each translation unit that launches it wraps it in its own `__global__` function
+// (256 threads per CTA, cooperative launch, at most `kLayoutMaxCtas` CTAs).
 EP_DEVICE void ep_layout_body(const LayoutArgs& a) {
     __shared__ int warp_rank[8][kMaxRanks];
     __shared__ unsigned hit_all[8][kMaxRanks];
@@ -116,7 +118,5 @@ EP_DEVICE void ep_layout_body(const LayoutArgs& a) {
         __syncwarp();
     }
 }
-
-__global__ void __launch_bounds__(256, 1) ep_layout_kernel(const __grid_constant__ LayoutArgs a) { ep_layout_body(a); }
 
 }  // namespace deep_ep::kernels
