@@ -1,0 +1,89 @@
+"""Throughput of the tcgen05 grouped GEMM kernels against the per-expert library-GEMM loop (single GPU).
+
+    python benchmarks/grouped_gemm.py [--experts 32 --rows 1024 --hidden 7168 --inter 2048]
+
+Shapes follow one rank of an EP8 DeepSeek-V3-like layer: 32 local experts, about 1024 rows each, GEMM1
+[rows, 7168] x [4096, 7168]^T and GEMM2 [rows, 2048] x [7168, 2048]^T. Inputs exceed the 126 MB L2. Times are
+CUDA events after warm-up; fractions are relative to the measured cuBLAS BF16 burst peak in MEASURED_PEAKS.json.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from deep_ep.ops import grouped_gemm as gg  # noqa: E402
+
+
+def bench(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for a, b in ev:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    return min(a.elapsed_time(b) for a, b in ev), sum(a.elapsed_time(b) for a, b in ev) / iters
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument('--experts', type=int, default=32)
+    p.add_argument('--rows', type=int, default=1024)
+    p.add_argument('--hidden', type=int, default=7168)
+    p.add_argument('--inter', type=int, default=2048)
+    p.add_argument('--iters', type=int, default=10)
+    p.add_argument('--skip-torch', action='store_true')
+    args = p.parse_args()
+    dev = torch.device('cuda')
+    torch.manual_seed(0)
+    g, h, i = args.experts, args.hidden, args.inter
+    counts = torch.randint(int(args.rows * 0.7), int(args.rows * 1.3), (g,)).clamp(min=1)
+    aligned = (counts + 127) // 128 * 128
+    starts = torch.cumsum(aligned, 0) - aligned
+    psum, count = (starts + counts).int().to(dev), counts.int().to(dev)
+    rows, useful = int(aligned.sum()), int(counts.sum())
+    x = torch.randn(rows, h, device=dev, dtype=torch.bfloat16)
+    w1 = (torch.randn(g, 2 * i, h, device=dev) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(g, h, i, device=dev) * 0.02).to(torch.bfloat16)
+    dy1 = torch.randn(rows, 2 * i, device=dev, dtype=torch.bfloat16)
+    act = torch.randn(rows, i, device=dev, dtype=torch.bfloat16)
+    dw1 = torch.zeros(g, 2 * i, h, device=dev, dtype=torch.float32)
+    peak = 1658.2
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        peak = json.load(open(path)).get('bf16_tflops', peak)
+    ranges = [(int(s), int(c)) for s, c in zip(starts, counts)]
+
+    def torch_fwd(a, w):
+        for e, (s, c) in enumerate(ranges):
+            torch.mm(a[s:s + c], w[e].t())
+
+    cases = {
+        'gemm1_forward': (lambda: gg.grouped_gemm_forward(x, w1, psum, count), lambda: torch_fwd(x, w1), 2 * useful * h * 2 * i),
+        'gemm1_forward_swiglu': (lambda: gg.grouped_gemm_forward(x, w1, psum, count, swiglu=True), None, 2 * useful * h * 2 * i),
+        'gemm2_forward': (lambda: gg.grouped_gemm_forward(act, w2, psum, count), lambda: torch_fwd(act, w2), 2 * useful * h * i),
+        'gemm1_dgrad': (lambda: gg.grouped_gemm_dgrad(dy1, w1, psum, count),
+                        lambda: [torch.mm(dy1[s:s + c], w1[e]) for e, (s, c) in enumerate(ranges)], 2 * useful * h * 2 * i),
+        'gemm1_wgrad': (lambda: gg.grouped_gemm_wgrad(dy1, x, dw1, psum, count),
+                        lambda: [torch.mm(dy1[s:s + c].t(), x[s:s + c]) for e, (s, c) in enumerate(ranges)], 2 * useful * h * 2 * i),
+    }
+    out = {'bench': 'grouped_gemm', 'experts': g, 'rows_total': rows, 'rows_useful': useful, 'hidden': h, 'inter': i,
+           'peak_tflops_measured': peak, 'results': {}}
+    for name, (ours, ref, flops) in cases.items():
+        t_min, t_avg = bench(ours, args.iters)
+        entry = {'ours_ms': round(t_avg, 4), 'ours_tflops': round(flops / (t_avg * 1e-3) / 1e12, 1),
+                 'ours_frac_of_measured_peak': round(flops / (t_avg * 1e-3) / 1e12 / peak, 3)}
+        if ref is not None and not args.skip_torch:
+            r_min, r_avg = bench(ref, args.iters)
+            entry.update({'torch_loop_ms': round(r_avg, 4), 'torch_loop_tflops': round(flops / (r_avg * 1e-3) / 1e12, 1)})
+        out['results'][name] = entry
+    print(json.dumps(out))
+
+
+if __name__ == '__main__':
+    main()

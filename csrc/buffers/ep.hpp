@@ -396,6 +396,66 @@ public:
         return pybind11::make_tuple(result, event, pybind11::none());
     }
 
+    // ------------------------------------------------------------------------------ load balancing
+    int64_t lb_offset_of(const torch::Tensor& t) const {
+        const auto base = reinterpret_cast<int64_t>(context->buffer) + num_bytes;
+        const auto ptr = reinterpret_cast<int64_t>(t.data_ptr());
+        EP_HOST_ASSERT_MSG(ptr >= base and ptr + static_cast<int64_t>(t.nbytes()) <= base + num_lb_bytes,
+                           "redundant expert tensors must live in this buffer's LB region");
+        return context->num_workspace_bytes + num_bytes + (ptr - base);
+    }
+
+    kernels::LBArgs lb_common(const torch::Tensor& mapping, int num_local_experts) const {
+        EP_HOST_ASSERT(not destroyed and context->peers_ready);
+        EP_HOST_ASSERT(mapping.is_cuda() and mapping.dim() == 2 and mapping.scalar_type() == torch::kInt32 and mapping.is_contiguous());
+        EP_HOST_ASSERT(mapping.size(0) == context->num_ranks and num_local_experts > 0);
+        kernels::LBArgs args = {};
+        args.peers = context->peers, args.cs = context->common_signals, args.host_status = context->host_status_device;
+        args.timeout_ns = context->num_gpu_timeout_ns;
+        args.mapping = mapping.data_ptr<int>(), args.num_redundant = static_cast<int>(mapping.size(1));
+        args.num_local_experts = num_local_experts;
+        return args;
+    }
+
+    EventHandle lb_prefetch_weights(const std::vector<torch::Tensor>& redundant_expert_weights,
+                                    const std::vector<torch::Tensor>& expert_weights, const torch::Tensor& redundancy_mapping,
+                                    int num_sms, const std::optional<EventHandle>& previous_event) const {
+        EP_HOST_ASSERT(not expert_weights.empty() and expert_weights.size() == redundant_expert_weights.size());
+        EP_HOST_ASSERT(static_cast<int>(expert_weights.size()) <= kernels::kMaxLBTensors);
+        auto args = lb_common(redundancy_mapping, static_cast<int>(expert_weights[0].size(0)));
+        args.mode = 0, args.num_tensors = static_cast<int>(expert_weights.size());
+        for (int i = 0; i < args.num_tensors; ++i) {
+            const auto &src = expert_weights[i], &dst = redundant_expert_weights[i];
+            EP_HOST_ASSERT(src.is_cuda() and src.is_contiguous() and src.dim() >= 2 and src.size(0) == args.num_local_experts);
+            EP_HOST_ASSERT(dst.is_cuda() and dst.is_contiguous() and dst.dim() >= 2 and dst.size(0) == args.num_redundant);
+            const int64_t bytes = static_cast<int64_t>(src.nbytes()) / src.size(0);
+            EP_HOST_ASSERT(bytes == static_cast<int64_t>(dst.nbytes()) / dst.size(0) and bytes % 16 == 0);
+            args.src[i] = static_cast<const uint8_t*>(src.data_ptr());
+            args.dst_offset[i] = lb_offset_of(dst), args.bytes_per_expert[i] = bytes;
+        }
+        if (previous_event.has_value()) previous_event->current_stream_wait();
+        launch::lb_exchange(args, num_sms > 0 ? num_sms : Runtime::get().get_num_sms(), c10::cuda::getCurrentCUDAStream());
+        return EventHandle();
+    }
+
+    EventHandle lb_reduce_grads(const torch::Tensor& redundant_expert_grads, const torch::Tensor& expert_grads,
+                                const torch::Tensor& redundancy_mapping, int num_sms,
+                                const std::optional<EventHandle>& previous_event) const {
+        EP_HOST_ASSERT(expert_grads.is_cuda() and expert_grads.is_contiguous() and expert_grads.dim() == 2 and
+                       expert_grads.scalar_type() == torch::kFloat32);
+        EP_HOST_ASSERT(redundant_expert_grads.is_cuda() and redundant_expert_grads.is_contiguous() and
+                       redundant_expert_grads.dim() == 2 and redundant_expert_grads.scalar_type() == torch::kFloat32 and
+                       redundant_expert_grads.size(1) == expert_grads.size(1));
+        auto args = lb_common(redundancy_mapping, static_cast<int>(expert_grads.size(0)));
+        EP_HOST_ASSERT(redundant_expert_grads.size(0) == args.num_redundant);
+        args.mode = 1, args.num_tensors = 1;
+        args.dst_offset[0] = lb_offset_of(redundant_expert_grads);
+        args.expert_grads = expert_grads.data_ptr<float>(), args.hidden = expert_grads.size(1);
+        if (previous_event.has_value()) previous_event->current_stream_wait();
+        launch::lb_exchange(args, num_sms > 0 ? num_sms : Runtime::get().get_num_sms(), c10::cuda::getCurrentCUDAStream());
+        return EventHandle();
+    }
+
     void check_status() const {
         if (host_counts != nullptr and host_counts->status.code != 0) throw_device_status();
         if (context != nullptr) context->check_status();

@@ -33,6 +33,7 @@ void engram_fetch(const kernels::EngramFetchArgs& args, int num_sms, cudaStream_
 void all_gather(const kernels::AllGatherArgs& args, int num_sms, cudaStream_t stream);
 void pp_send(const kernels::PPArgs& args, int num_sms, cudaStream_t stream);
 void pp_recv(const kernels::PPArgs& args, int num_sms, cudaStream_t stream);
+void lb_exchange(const kernels::LBArgs& args, int num_sms, cudaStream_t stream);
 
 // Standalone routing layout (cooperative launch, at most `kLayoutMaxCtas` CTAs). `args.scratch` must point to a
 // zero-initialised `LayoutScratch` in device memory.

@@ -135,6 +135,10 @@ void pp_recv(const kernels::PPArgs& args, int num_sms, cudaStream_t stream) {
     launch_kernel(kernels::pp_recv_kernel, args, clamp_sms(num_sms), 512, 0, true, stream);
 }
 
+void lb_exchange(const kernels::LBArgs& args, int num_sms, cudaStream_t stream) {
+    launch_kernel(kernels::lb_exchange_kernel, args, clamp_sms(num_sms), 512, 0, true, stream);
+}
+
 namespace {
 
 struct ProbeArgs {

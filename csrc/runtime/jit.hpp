@@ -10,12 +10,14 @@
 #include <pybind11/stl.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <filesystem>
 #include <fstream>
 #include <functional>
 #include <map>
 #include <mutex>
 #include <sstream>
+#include <unistd.h>
 #include <string>
 #include <vector>
 
@@ -143,6 +145,25 @@ inline void register_python_api(pybind11::module_& m) {
         return Compiler::get().compile(name, source, arch);
     }, pybind11::arg("name"), pybind11::arg("source"), pybind11::arg("arch") = "sm_100a");
     m.def("jit_include_dir", [] { return Compiler::get().include_dir(); });
+    // Launch `symbol` of a compiled cubin on the current CUDA stream. Each argument is a `(kind, value)` pair with
+    // kind in {"ptr", "i64", "i32", "f32"}; pointers are raw device addresses.
+    m.def("jit_launch", [](const std::string& cubin, const std::string& symbol, int grid, int block, int smem_bytes,
+                           const std::vector<std::pair<std::string, pybind11::object>>& args, bool cooperative,
+                           uint64_t stream) {
+        std::vector<uint64_t> storage(args.size(), 0);
+        std::vector<void*> pointers(args.size(), nullptr);
+        for (size_t i = 0; i < args.size(); ++i) {
+            const auto& [kind, value] = args[i];
+            if (kind == "ptr" or kind == "i64") storage[i] = static_cast<uint64_t>(value.cast<int64_t>());
+            else if (kind == "i32") { const int32_t v = value.cast<int32_t>(); std::memcpy(&storage[i], &v, 4); }
+            else if (kind == "f32") { const float v = value.cast<float>(); std::memcpy(&storage[i], &v, 4); }
+            else throw EPException("JIT launch", __FILE__, __LINE__, "unknown argument kind " + kind);
+            pointers[i] = &storage[i];
+        }
+        auto fn = Compiler::get().load(cubin, symbol);
+        Compiler::get().launch(fn, grid, block, smem_bytes, reinterpret_cast<CUstream>(stream), pointers, cooperative);
+    }, pybind11::arg("cubin"), pybind11::arg("symbol"), pybind11::arg("grid"), pybind11::arg("block"),
+       pybind11::arg("smem_bytes"), pybind11::arg("args"), pybind11::arg("cooperative") = false, pybind11::arg("stream") = 0);
 }
 
 }  // namespace deep_ep::jit

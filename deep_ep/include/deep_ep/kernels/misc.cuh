@@ -129,6 +129,54 @@ __global__ void __launch_bounds__(512) bucket_all_gather_kernel(const __grid_con
     __threadfence_system();
 }
 
+// ---------------------------------------------------------------------------------------- load balancing
+// Collective over the NVLink domain. Mode 0 pushes this rank's expert weights into every redundant slot that a
+// peer assigned to one of them; mode 1 pulls the gradients of those redundant copies and adds them to the
+// owner's fp32 gradient. Both start with a rank barrier (slots / gradients are ready everywhere) and end with
+// one (all transfers have landed), so the data is usable once the kernel has completed on every rank.
+// The reference exposes this API without a kernel behind it (`csrc/buffers/ep.hpp:75-86`).
+__global__ void __launch_bounds__(512) lb_exchange_kernel(const __grid_constant__ LBArgs a) {
+    const int rank = a.peers.rank, num_ranks = a.peers.num_ranks;
+    if (not dev::healthy(a.cs)) return;
+    if (blockIdx.x == 0 and threadIdx.x < 32) dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, 70);
+    if (not dev::grid_sync(a.cs, a.host_status, gridDim.x, a.timeout_ns, rank, 71)) return;
+
+    const int num_slots = num_ranks * a.num_redundant;
+    if (a.mode == 0) {
+        int task = 0;
+        for (int s = 0; s < num_slots; ++s) {
+            const int e = a.mapping[s];
+            if (e < 0 or e / a.num_local_experts != rank) continue;
+            const int r = s / a.num_redundant, c = s % a.num_redundant, local = e % a.num_local_experts;
+            for (int i = 0; i < a.num_tensors; ++i, ++task) {
+                if (task % gridDim.x != blockIdx.x) continue;
+                const int64_t bytes = a.bytes_per_expert[i];
+                const uint8_t* src = a.src[i] + local * bytes;
+                uint8_t* dst = a.peers.base[r] + a.dst_offset[i] + c * bytes;
+                for (int64_t o = threadIdx.x * 16; o < bytes; o += blockDim.x * 16)
+                    ptx::st_na_v4(dst + o, ptx::ld_nc_v4(src + o));
+            }
+        }
+    } else {
+        // one thread owns a column of one local expert, so additions to an element are ordered
+        const int64_t total = int64_t(a.num_local_experts) * a.hidden;
+        for (int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += int64_t(gridDim.x) * blockDim.x) {
+            const int local = int(idx / a.hidden);
+            const int64_t col = idx % a.hidden;
+            float acc = a.expert_grads[idx];
+            for (int s = 0; s < num_slots; ++s) {
+                if (a.mapping[s] != rank * a.num_local_experts + local) continue;
+                const int r = s / a.num_redundant, c = s % a.num_redundant;
+                acc += *reinterpret_cast<const float*>(a.peers.base[r] + a.dst_offset[0] + (int64_t(c) * a.hidden + col) * 4);
+            }
+            a.expert_grads[idx] = acc;
+        }
+    }
+    __threadfence_system();
+    if (not dev::grid_sync(a.cs, a.host_status, gridDim.x, a.timeout_ns, rank, 72)) return;
+    if (blockIdx.x == 0 and threadIdx.x < 32) dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, 73);
+}
+
 // ---------------------------------------------------------------------------------------- pipeline
 namespace pp_detail {
 

@@ -50,4 +50,24 @@ struct PPArgs {
     long long timeout_ns;
 };
 
+constexpr int kMaxLBTensors = 16;
+
+// Expert load balancing over redundant expert slots. `mapping[r * num_redundant + c]` is the global expert id
+// that rank r keeps in its redundant slot c (-1 = empty); every rank passes the same mapping.
+struct LBArgs {
+    layout::PeerTable peers;
+    layout::CommonSignals* cs;
+    layout::HostStatus* host_status;
+    long long timeout_ns;
+    const int* mapping;
+    int num_redundant, num_local_experts;
+    int mode;                                 // 0: push weights into peers' redundant slots, 1: pull and add gradients
+    int num_tensors;
+    const uint8_t* src[kMaxLBTensors];        // mode 0: local `[num_local_experts, bytes_per_expert]` sources
+    int64_t dst_offset[kMaxLBTensors];        // offset of the `[num_redundant, ...]` tensor inside the allocation
+    int64_t bytes_per_expert[kMaxLBTensors];
+    float* expert_grads;                      // mode 1: `[num_local_experts, hidden]` fp32, accumulated into
+    int64_t hidden;
+};
+
 }  // namespace deep_ep::kernels

@@ -375,3 +375,43 @@ def _engram_worker(rank, world, use_fp8):
 @pytest.mark.parametrize('use_fp8', [False, True])
 def test_engram_fetch(master_port, use_fp8):
     run_distributed(_engram_worker, _world(), master_port, 'nccl', (use_fp8,))
+
+
+# ---------------------------------------------------------------------------------------------------- load balancing
+def _lb_worker(rank, world):
+    import torch.distributed as dist
+    import deep_ep
+    group = dist.group.WORLD
+    num_local, num_redundant, hidden = 4, 3, 256
+    plan = deep_ep.BufferAllocator()
+    red_w = plan.allocate((num_redundant, 8, hidden), torch.bfloat16)
+    red_g = plan.allocate((num_redundant, hidden), torch.float32)
+    ep = deep_ep.EPBuffer(group, num_max_tokens_per_rank=64, hidden=256, num_topk=2, lb_allocation_plan_or_num_bytes=plan,
+                          explicitly_destroy=True, num_gpu_timeout_secs=10)
+    torch.manual_seed(0)                                   # the mapping is identical on every rank
+    mapping = torch.randint(-1, world * num_local, (world, num_redundant), dtype=torch.int32).cuda()
+    weights = torch.stack([torch.full((8, hidden), float(rank * num_local + e)) for e in range(num_local)]).cuda().to(torch.bfloat16)
+    red_w.fill_(-5)
+    ep.lb_prefetch_weights(red_w, weights, mapping).current_stream_wait()
+    torch.cuda.synchronize()
+    for c in range(num_redundant):
+        e = int(mapping[rank, c])
+        assert torch.all(red_w[c] == (e if e >= 0 else -5)), f'slot {c} expected expert {e}'
+
+    red_g.copy_(torch.arange(num_redundant).view(-1, 1).float().cuda() + 10 * rank + 1)
+    grads = torch.ones(num_local, hidden, device='cuda')
+    ep.lb_reduce_grads(red_g, grads, mapping).current_stream_wait()
+    torch.cuda.synchronize()
+    for e in range(num_local):
+        expect = 1.0
+        for r in range(world):
+            for c in range(num_redundant):
+                if int(mapping[r, c]) == rank * num_local + e:
+                    expect += c + 10 * r + 1
+        assert torch.all(grads[e] == expect), f'expert {e}: {grads[e, 0].item()} != {expect}'
+    ep.destroy()
+
+
+@pytest.mark.gpu
+def test_lb_prefetch_and_reduce(master_port):
+    run_distributed(_lb_worker, _world(), master_port, 'nccl')
