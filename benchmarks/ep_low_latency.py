@@ -28,6 +28,7 @@ def main():
     p.add_argument('--num-experts', type=int, default=256)
     p.add_argument('--num-sms', type=int, nargs='+', default=[8, 16, 32])
     p.add_argument('--replays', type=int, default=100)
+    p.add_argument('--profile', action='store_true', help='print per-kernel device times of eager iterations (analysis only)')
     args = p.parse_args()
 
     rank, world = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1))
@@ -86,6 +87,19 @@ def main():
         num_recv = int(handle.psum_num_recv_tokens_per_rank[-1])
         results.append({'num_sms': num_sms, 'dispatch_us': round(t[0].item(), 2), 'combine_us': round(t[1].item(), 2),
                         'recv_tokens_rank0': num_recv})
+    if args.profile:
+        from deep_ep.utils.testing import bench_kineto
+        common = dict(num_experts=E, num_max_tokens_per_rank=T, expert_alignment=1, num_sms=args.num_sms[-1], do_expand=True,
+                      do_cpu_sync=False, async_with_compute_stream=True, defer_epilogue=True, fused_fp8_quant=True)
+
+        def eager():
+            (rx, rsf), _, rw, h = buffer.dispatch(x, topk_idx=topk_idx, topk_weights=topk_w, **common).current_stream_wait()
+            buffer.combine(y, h, topk_weights=rw, async_with_compute_stream=True, defer_epilogue=True).current_stream_wait()
+
+        profiles = bench_kineto(eager, return_all_kernels=True, num_tests=20, flush_l2=False, barrier_comm_profiling=True)
+        if rank == 0:
+            for name, prof in sorted(profiles.items(), key=lambda kv: -kv[1].dur_ns):
+                print(f'  {prof.dur_us:9.2f} us x{prof.num_calls}  {name[:100]}')
     if rank == 0:
         print(json.dumps({'bench': 'ep_low_latency_cuda_graph', 'n_gpus': world, 'tokens_per_rank': T, 'hidden': H,
                           'topk': K, 'experts': E, 'routing': 'skewed: N(0,1) logits + N(0,2) expert bias',
