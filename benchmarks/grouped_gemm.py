@@ -69,6 +69,7 @@ def main():
         'gemm2_forward': (lambda: gg.grouped_gemm_forward(act, w2, psum, count), lambda: torch_fwd(act, w2), 2 * useful * h * i),
         'gemm1_dgrad': (lambda: gg.grouped_gemm_dgrad(dy1, w1, psum, count),
                         lambda: [torch.mm(dy1[s:s + c], w1[e]) for e, (s, c) in enumerate(ranges)], 2 * useful * h * 2 * i),
+        'gemm1_wgrad_store': (lambda: gg.grouped_gemm_wgrad(dy1, x, dw1, psum, count, accumulate=False), None, 2 * useful * h * 2 * i),
         'gemm1_wgrad': (lambda: gg.grouped_gemm_wgrad(dy1, x, dw1, psum, count),
                         lambda: [torch.mm(dy1[s:s + c].t(), x[s:s + c]) for e, (s, c) in enumerate(ranges)], 2 * useful * h * 2 * i),
     }

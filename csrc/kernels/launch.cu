@@ -98,7 +98,8 @@ void combine(kernels::CombineArgs args, int num_sms, cudaStream_t stream) {
 }
 
 void combine_reduce(kernels::CombineReduceArgs args, int num_sms, cudaStream_t stream) {
-    launch_kernel(kernels::ep_combine_reduce_kernel, args, clamp_sms(num_sms), 256, 0, false, stream);
+    // not cooperative: oversubscribe the SMs so that enough loads are in flight
+    launch_kernel(kernels::ep_combine_reduce_kernel, args, clamp_sms(num_sms) * 4, 256, 0, false, stream);
 }
 
 namespace {

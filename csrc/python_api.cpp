@@ -92,9 +92,9 @@ void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::T
     launch::grouped_gemm(args, a.data_ptr(), rows, a.size(1), b.data_ptr(), b_rows, b_cols, num_sms, c10::cuda::getCurrentCUDAStream());
 }
 
-// d[g, m, n] (fp32) += a[rows_e, m]^T * b[rows_e, n] for every expert e; padding rows of `a` or `b` must be zero.
+// d[g, m, n] (fp32) (+)= a[rows_e, m]^T * b[rows_e, n] for every expert e; padding rows of `a` or `b` must be zero.
 void grouped_gemm_wgrad(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const torch::Tensor& psum,
-                        const torch::Tensor& count, int num_sms) {
+                        const torch::Tensor& count, int num_sms, bool accumulate) {
     using namespace kernels;
     EP_HOST_ASSERT(a.is_cuda() and b.is_cuda() and d.is_cuda() and a.is_contiguous() and b.is_contiguous() and d.is_contiguous());
     EP_HOST_ASSERT(a.scalar_type() == torch::kBFloat16 and b.scalar_type() == torch::kBFloat16 and a.dim() == 2 and b.dim() == 2);
@@ -102,6 +102,7 @@ void grouped_gemm_wgrad(const torch::Tensor& a, const torch::Tensor& b, const to
     EP_HOST_ASSERT(psum.scalar_type() == torch::kInt32 and count.scalar_type() == torch::kInt32 and psum.numel() == count.numel());
     GroupedGemmArgs args = {};
     args.mode = kModeWgrad, args.epilogue = kEpilogueStore, args.num_groups = static_cast<int>(psum.numel());
+    args.accumulate = accumulate;
     args.psum = psum.data_ptr<int>(), args.count = count.data_ptr<int>();
     args.m = static_cast<int>(a.size(1)), args.n = static_cast<int>(b.size(1)), args.k = 0;
     EP_HOST_ASSERT(d.size(0) == args.num_groups and d.size(1) == args.m and d.size(2) == args.n);
@@ -178,7 +179,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
           py::arg("mode"), py::arg("epilogue") = 0, py::arg("num_sms") = 0);
     m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
-          py::arg("num_sms") = 0);
+          py::arg("num_sms") = 0, py::arg("accumulate") = true);
 
     py::class_<BufferBase, std::shared_ptr<BufferBase>>(m, "BufferBase")
         .def_readonly("main_context", &BufferBase::main_context)

@@ -99,6 +99,38 @@ EP_DEVICE void reduce_rows(const uint8_t* x, int hidden_bytes, int chunks, int m
     }
 }
 
+// Owner-side reduction of one token: fp32 sum of bias_0, bias_1 and the partials in slot order, one rounding to
+// bf16. `kChunks` 16-byte chunks per lane are in flight before the first add.
+template <int kParts, int kChunks>
+EP_DEVICE void reduce_token(const uint8_t* const (&part)[kParts], const uint8_t* b0, const uint8_t* b1, uint8_t* out,
+                            int chunks, int lane) {
+    for (int c0 = lane; c0 < chunks; c0 += 32 * kChunks) {
+        int4 v[kChunks][kParts], vb0[kChunks], vb1[kChunks];
+        #pragma unroll
+        for (int i = 0; i < kChunks; ++i) {
+            const int c = c0 + 32 * i;
+            if (c >= chunks) continue;
+            if (b0 != nullptr) vb0[i] = ptx::ld_nc_v4(b0 + c * 16);
+            if (b1 != nullptr) vb1[i] = ptx::ld_nc_v4(b1 + c * 16);
+            #pragma unroll
+            for (int u = 0; u < kParts; ++u)
+                if (part[u] != nullptr) v[i][u] = ptx::ld_v4(part[u] + c * 16);
+        }
+        #pragma unroll
+        for (int i = 0; i < kChunks; ++i) {
+            const int c = c0 + 32 * i;
+            if (c >= chunks) continue;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (b0 != nullptr) accumulate(acc, vb0[i]);
+            if (b1 != nullptr) accumulate(acc, vb1[i]);
+            #pragma unroll
+            for (int u = 0; u < kParts; ++u)
+                if (part[u] != nullptr) accumulate(acc, v[i][u]);
+            ptx::st_na_v4(out + c * 16, pack(acc));
+        }
+    }
+}
+
 }  // namespace combine_detail
 
 __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_constant__ CombineArgs a) {
@@ -275,24 +307,26 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
             const int g = __shfl_sync(0xffffffffu, group, u < count ? nth_set_bit(masters, u) : 0);
             part[u] = u < count ? a.buffer + bl.offset(g, t) : nullptr;
         }
-        for (int c = lane; c < chunks; c += 32) {
-            int4 v[kUnroll], b0 = make_int4(0, 0, 0, 0), b1 = make_int4(0, 0, 0, 0);
-            if (a.bias_0 != nullptr) b0 = ptx::ld_nc_v4(a.bias_0 + int64_t(t) * a.hidden_bytes + c * 16);
-            if (a.bias_1 != nullptr) b1 = ptx::ld_nc_v4(a.bias_1 + int64_t(t) * a.hidden_bytes + c * 16);
-            #pragma unroll
-            for (int u = 0; u < kUnroll; ++u)
-                if (part[u] != nullptr) v[u] = ptx::ld_v4(part[u] + c * 16);
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (a.bias_0 != nullptr) accumulate(acc, b0);
-            if (a.bias_1 != nullptr) accumulate(acc, b1);
-            #pragma unroll
-            for (int u = 0; u < kUnroll; ++u)
-                if (part[u] != nullptr) accumulate(acc, v[u]);
-            for (int u = kUnroll; u < count; ++u) {
-                const int g = __shfl_sync(0xffffffffu, group, nth_set_bit(masters, u));
-                accumulate(acc, ptx::ld_v4(a.buffer + bl.offset(g, t) + c * 16));
+        const uint8_t* b0 = a.bias_0 != nullptr ? a.bias_0 + int64_t(t) * a.hidden_bytes : nullptr;
+        const uint8_t* b1 = a.bias_1 != nullptr ? a.bias_1 + int64_t(t) * a.hidden_bytes : nullptr;
+        uint8_t* out = a.combined_x + int64_t(t) * a.hidden_bytes;
+        if (count <= 4) {
+            const uint8_t* p4[4] = {part[0], part[1], part[2], part[3]};
+            reduce_token<4, 4>(p4, b0, b1, out, chunks, lane);
+        } else if (count <= kUnroll) {
+            reduce_token<kUnroll, 2>(part, b0, b1, out, chunks, lane);
+        } else {
+            for (int base = 0; base < chunks; base += 32) {      // warp-uniform trip count: shuffles inside
+                const int c = base + lane;
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (c < chunks and b0 != nullptr) accumulate(acc, ptx::ld_nc_v4(b0 + c * 16));
+                if (c < chunks and b1 != nullptr) accumulate(acc, ptx::ld_nc_v4(b1 + c * 16));
+                for (int u = 0; u < count; ++u) {
+                    const int g = __shfl_sync(0xffffffffu, group, nth_set_bit(masters, u));
+                    if (c < chunks) accumulate(acc, ptx::ld_v4(a.buffer + bl.offset(g, t) + c * 16));
+                }
+                if (c < chunks) ptx::st_na_v4(out + c * 16, pack(acc));
             }
-            ptx::st_na_v4(a.combined_x + int64_t(t) * a.hidden_bytes + c * 16, pack(acc));
         }
         if (a.combined_topk_weights != nullptr) {
             // position j reads its weight from the partial produced by the rank that owns expert j

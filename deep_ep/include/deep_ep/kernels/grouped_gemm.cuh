@@ -91,7 +91,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int tiles = 0;
             if (e < a.num_groups) {
                 const int count = a.count[e];
-                if (a.mode == kModeWgrad) tiles = count > 0 ? (a.m / kGemmBlockM) * (a.n / BN) : 0;
+                if (a.mode == kModeWgrad) tiles = (count > 0 or not a.accumulate) ? (a.m / kGemmBlockM) * (a.n / BN) : 0;
                 else tiles = math::ceil_div(count, kGemmBlockM) * (a.n_out / a.block_n_out);
             }
             int incl = tiles;
@@ -180,7 +180,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                     tc::commit(&empty_bar[s]);          // stage is free once these MMAs have read it
                 }
-                tc::commit(&tmem_full_bar[acc]);        // accumulator complete
+                if (t.num_k_blocks > 0) tc::commit(&tmem_full_bar[acc]);        // accumulator complete
+                else ptx::mbarrier_arrive(&tmem_full_bar[acc]);                 // nothing to wait for: the epilogue writes zeros
             }
         }
     } else {
@@ -199,14 +200,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 float* out = reinterpret_cast<float*>(a.d) + (size_t(t.expert) * a.m + t.m0 + row) * a.n + t.n0;
                 for (int c = 0; c < BN; c += 32) {
                     uint32_t r[32];
-                    tc::tmem_ld_32x32(taddr + c, r);
-                    tc::wait_ld();
+                    if (t.num_k_blocks > 0) {
+                        tc::tmem_ld_32x32(taddr + c, r);
+                        tc::wait_ld();
+                    } else {
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = 0;
+                    }
                     #pragma unroll
                     for (int v = 0; v < 8; ++v) {
-                        float4 old = *reinterpret_cast<float4*>(out + c + 4 * v);
-                        old.x += __uint_as_float(r[4 * v]), old.y += __uint_as_float(r[4 * v + 1]);
-                        old.z += __uint_as_float(r[4 * v + 2]), old.w += __uint_as_float(r[4 * v + 3]);
-                        *reinterpret_cast<float4*>(out + c + 4 * v) = old;
+                        float4 val = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                 __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                        if (a.accumulate) {
+                            const float4 old = *reinterpret_cast<float4*>(out + c + 4 * v);
+                            val.x += old.x, val.y += old.y, val.z += old.z, val.w += old.w;
+                        }
+                        *reinterpret_cast<float4*>(out + c + 4 * v) = val;
                     }
                 }
             } else if (a.epilogue == kEpilogueSwiGLU) {

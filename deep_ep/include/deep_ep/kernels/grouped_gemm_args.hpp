@@ -24,6 +24,7 @@ struct GroupedGemmArgs {
     int block_n;              // accumulator columns per tile (128 or 256)
     int block_n_out;          // output columns per tile
     int num_stages;
+    int accumulate;           // wgrad: 1 = add to the existing contents of d, 0 = overwrite (experts without rows get zeros)
     void* d;                  // bf16 [rows, n_out] (forward/dgrad) or fp32 [G, m, n] accumulated into (wgrad)
     int* status;              // set to 1 if a bounded wait ran out (may be nullptr)
 };

@@ -36,10 +36,11 @@ def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, co
 
 
 def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, dw: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
-                       num_sms: int = 0) -> torch.Tensor:
-    """`dw[e] += dy[rows_e].T @ x[rows_e]` accumulated in fp32 (`dw [G, N, K]` fp32). Padding rows of `dy` or `x`
-    up to the next multiple of 64 rows must be zero."""
-    _C.grouped_gemm_wgrad(dy, x, dw, psum, count, num_sms)
+                       num_sms: int = 0, accumulate: bool = True) -> torch.Tensor:
+    """`dw[e] += dy[rows_e].T @ x[rows_e]` in fp32 (`dw [G, N, K]` fp32); with `accumulate=False` the result
+    overwrites `dw` (experts without rows get zeros), which saves reading it. Padding rows of `dy` or `x` up to the
+    next multiple of 64 rows must be zero."""
+    _C.grouped_gemm_wgrad(dy, x, dw, psum, count, num_sms, accumulate)
     return dw
 
 
@@ -70,10 +71,11 @@ class GroupedLinear(torch.autograd.Function):
         dw = None
         if ctx.needs_input_grad[1]:
             main_grad = getattr(w, 'main_grad', None)
-            acc = main_grad if main_grad is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
             if ctx.alignment % 64 == 0:
-                grouped_gemm_wgrad(dy, x, acc, psum, count)
+                acc = main_grad if main_grad is not None else torch.empty(w.shape, dtype=torch.float32, device=w.device)
+                grouped_gemm_wgrad(dy, x, acc, psum, count, accumulate=main_grad is not None)
             else:
+                acc = main_grad if main_grad is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
                 for e, (start, c) in enumerate(_ranges(psum, count)):
                     if c:
                         acc[e].addmm_(dy[start:start + c].float().t(), x[start:start + c].float())

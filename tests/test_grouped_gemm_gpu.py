@@ -42,6 +42,10 @@ def test_grouped_forward_dgrad_wgrad(counts, alignment, k, n):
     if alignment % 64 == 0:
         gg.grouped_gemm_wgrad(dy, x, dw, psum, count)
         gg.grouped_gemm_wgrad(dy, x, dw, psum, count)      # accumulates
+        dw_store = torch.full((g, n, k), float('nan'), device=dev, dtype=torch.float32)
+        gg.grouped_gemm_wgrad(dy, x, dw_store, psum, count, accumulate=False)
+        torch.cuda.synchronize()
+        assert torch.allclose(dw_store * 2, dw, atol=1e-3, rtol=1e-4)
     torch.cuda.synchronize()
     for e, (s, c) in enumerate(zip(starts, counts)):
         if c == 0:
