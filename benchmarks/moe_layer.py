@@ -60,13 +60,13 @@ class BaselineMoELayer(nn.Module):
                                                 counts.reshape(-1))
         by_expert = torch.argsort(expert_of_row, stable=True)
         rows = recv[by_expert]
-        out = torch.empty_like(rows)
-        start = 0
+        outs, start = [], 0
         for e, c in enumerate(counts.sum(0).tolist()):
             if c:
                 g, u = F.linear(rows[start:start + c], self.w_gate_up[e]).chunk(2, dim=-1)
-                out[start:start + c] = F.linear(F.silu(g) * u, self.w_down[e])
+                outs.append(F.linear(F.silu(g) * u, self.w_down[e]))
             start += c
+        out = torch.cat(outs) if outs else torch.empty_like(rows)
         back_rows = torch.empty_like(out)
         back_rows[by_expert] = out
         back = dist_fn.all_to_all_single(torch.empty((sum(sc), x.size(1)), dtype=x.dtype, device=x.device), back_rows, sc, rc,

@@ -44,6 +44,10 @@ void dispatch_layout(const kernels::LayoutArgs& args, int num_sms, cudaStream_t 
 void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, int64_t a_cols,
                   const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream);
 
+// dh = d(silu(gate) * up * row_scale) / d[gate | up] for bf16 rows; `inter` must be a multiple of 8.
+void swiglu_backward(const void* h, const void* dact, const float* row_scale, void* dh, int64_t rows, int inter,
+                     cudaStream_t stream);
+
 // Test hook: a one-warp kernel that waits (bounded) for a flag nobody sets and records the status.
 void bounded_wait_probe(layout::CommonSignals* cs, layout::HostStatus* host_status, long long timeout_ns,
                         cudaStream_t stream);

@@ -32,7 +32,9 @@ void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, 
                   const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream) {
     using namespace kernels;
     EP_HOST_ASSERT(args.num_groups > 0 and args.num_groups <= kMaxLocalExperts);
-    if (args.epilogue == kEpilogueSwiGLU) {
+    // the driver call below needs a current context; autograd worker threads may not have touched the runtime yet
+    CUDA_CHECK(cudaFree(nullptr));
+    if (args.epilogue != kEpilogueStore) {
         EP_HOST_ASSERT(args.mode == kModeForward and args.n % 256 == 0);
         args.block_n = 256, args.block_n_out = 128, args.n_out = args.n / 2;
     } else {

@@ -4,6 +4,7 @@
 #include <string>
 
 #include <deep_ep/common/exception.hpp>
+#include <deep_ep/kernels/elementwise.cuh>
 #include <deep_ep/kernels/ep_combine.cuh>
 #include <deep_ep/kernels/ep_dispatch.cuh>
 #include <deep_ep/kernels/ep_expand.cuh>
@@ -125,15 +126,25 @@ void engram_fetch(const kernels::EngramFetchArgs& args, int num_sms, cudaStream_
 }
 
 void all_gather(const kernels::AllGatherArgs& args, int num_sms, cudaStream_t stream) {
-    launch_kernel(kernels::bucket_all_gather_kernel, args, clamp_sms(num_sms), 512, 0, true, stream);
+    launch_kernel(kernels::bucket_all_gather_kernel, args, clamp_sms(num_sms), 256, dev::bulk_copy_smem_bytes(8), true, stream);
 }
 
 void pp_send(const kernels::PPArgs& args, int num_sms, cudaStream_t stream) {
-    launch_kernel(kernels::pp_send_kernel, args, clamp_sms(num_sms), 512, 0, true, stream);
+    launch_kernel(kernels::pp_send_kernel, args, clamp_sms(num_sms), 256, dev::bulk_copy_smem_bytes(8), true, stream);
 }
 
 void pp_recv(const kernels::PPArgs& args, int num_sms, cudaStream_t stream) {
-    launch_kernel(kernels::pp_recv_kernel, args, clamp_sms(num_sms), 512, 0, true, stream);
+    launch_kernel(kernels::pp_recv_kernel, args, clamp_sms(num_sms), 256, dev::bulk_copy_smem_bytes(8), true, stream);
+}
+
+void swiglu_backward(const void* h, const void* dact, const float* row_scale, void* dh, int64_t rows, int inter,
+                     cudaStream_t stream) {
+    EP_HOST_ASSERT(inter % 8 == 0);
+    if (rows == 0) return;
+    const kernels::SwiGLUBackwardArgs args = {static_cast<const uint8_t*>(h), static_cast<const uint8_t*>(dact), row_scale,
+                                              static_cast<uint8_t*>(dh), rows, inter};
+    const int64_t blocks = std::min<int64_t>((rows * (inter / 8) + 255) / 256, 148 * 16);
+    launch_kernel(kernels::swiglu_backward_kernel, args, static_cast<int>(blocks), 256, 0, false, stream);
 }
 
 void lb_exchange(const kernels::LBArgs& args, int num_sms, cudaStream_t stream) {

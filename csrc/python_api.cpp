@@ -61,7 +61,8 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> get_dispatch_layout(cons
 // Grouped GEMM over the expanded layout. mode 0: d[rows, n_out] = a[rows, k] * b[g, n, k]^T (optionally SwiGLU);
 // mode 1: d[rows, n] = a[rows, k] * b[g, k, n]; mode 2: d[g, m, n] += a[rows, m]^T * b[rows, n] (fp32).
 void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const torch::Tensor& psum,
-                  const torch::Tensor& count, int mode, int epilogue, int num_sms) {
+                  const torch::Tensor& count, int mode, int epilogue, int num_sms, int alignment,
+                  const std::optional<torch::Tensor>& row_scale, const std::optional<torch::Tensor>& keep) {
     using namespace kernels;
     EP_HOST_ASSERT(a.is_cuda() and b.is_cuda() and d.is_cuda() and a.is_contiguous() and b.is_contiguous() and d.is_contiguous());
     EP_HOST_ASSERT(a.scalar_type() == torch::kBFloat16 and b.scalar_type() == torch::kBFloat16 and a.dim() == 2 and b.dim() == 3);
@@ -70,14 +71,24 @@ void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::T
     GroupedGemmArgs args = {};
     args.mode = mode, args.epilogue = epilogue, args.num_groups = static_cast<int>(psum.numel());
     args.psum = psum.data_ptr<int>(), args.count = count.data_ptr<int>();
-    args.d = d.data_ptr(), args.status = nullptr;
+    args.d = d.data_ptr(), args.status = nullptr, args.alignment = alignment;
     const int64_t rows = a.size(0), g = args.num_groups;
+    if (row_scale.has_value()) {
+        EP_HOST_ASSERT(epilogue != kEpilogueStore and row_scale->is_cuda() and row_scale->is_contiguous() and
+                       row_scale->scalar_type() == torch::kFloat32 and row_scale->numel() == rows);
+        args.row_scale = row_scale->data_ptr<float>();
+    }
+    if (epilogue == kEpilogueSwiGLUKeep) {
+        EP_HOST_ASSERT(keep.has_value() and keep->is_cuda() and keep->is_contiguous() and keep->scalar_type() == torch::kBFloat16 and
+                       keep->dim() == 2 and keep->size(0) == rows and keep->size(1) == b.size(1));
+        args.d2 = keep->data_ptr();
+    }
     int64_t b_rows, b_cols;
     if (mode == kModeForward) {
         EP_HOST_ASSERT(b.size(0) == g and b.size(2) == a.size(1));
         args.n = static_cast<int>(b.size(1)), args.k = static_cast<int>(a.size(1));
         b_rows = g * b.size(1), b_cols = b.size(2);
-        const int64_t n_out = epilogue == kEpilogueSwiGLU ? args.n / 2 : args.n;
+        const int64_t n_out = epilogue != kEpilogueStore ? args.n / 2 : args.n;
         EP_HOST_ASSERT(d.scalar_type() == torch::kBFloat16 and d.dim() == 2 and d.size(0) == rows and d.size(1) == n_out);
         EP_HOST_ASSERT(args.k % 8 == 0);
     } else if (mode == kModeDgrad) {
@@ -92,17 +103,31 @@ void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::T
     launch::grouped_gemm(args, a.data_ptr(), rows, a.size(1), b.data_ptr(), b_rows, b_cols, num_sms, c10::cuda::getCurrentCUDAStream());
 }
 
+torch::Tensor swiglu_backward(const torch::Tensor& h, const torch::Tensor& dact, const std::optional<torch::Tensor>& row_scale) {
+    EP_HOST_ASSERT(h.is_cuda() and h.is_contiguous() and h.scalar_type() == torch::kBFloat16 and h.dim() == 2);
+    EP_HOST_ASSERT(dact.is_cuda() and dact.is_contiguous() and dact.scalar_type() == torch::kBFloat16 and dact.dim() == 2);
+    EP_HOST_ASSERT(h.size(0) == dact.size(0) and h.size(1) == 2 * dact.size(1));
+    if (row_scale.has_value())
+        EP_HOST_ASSERT(row_scale->is_cuda() and row_scale->is_contiguous() and row_scale->scalar_type() == torch::kFloat32 and
+                       row_scale->numel() == h.size(0));
+    auto dh = torch::empty_like(h);
+    launch::swiglu_backward(h.data_ptr(), dact.data_ptr(), row_scale.has_value() ? row_scale->data_ptr<float>() : nullptr,
+                            dh.data_ptr(), h.size(0), static_cast<int>(dact.size(1)), c10::cuda::getCurrentCUDAStream());
+    return dh;
+}
+
 // d[g, m, n] (fp32) (+)= a[rows_e, m]^T * b[rows_e, n] for every expert e; padding rows of `a` or `b` must be zero.
 void grouped_gemm_wgrad(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const torch::Tensor& psum,
                         const torch::Tensor& count, int num_sms, bool accumulate) {
     using namespace kernels;
     EP_HOST_ASSERT(a.is_cuda() and b.is_cuda() and d.is_cuda() and a.is_contiguous() and b.is_contiguous() and d.is_contiguous());
     EP_HOST_ASSERT(a.scalar_type() == torch::kBFloat16 and b.scalar_type() == torch::kBFloat16 and a.dim() == 2 and b.dim() == 2);
-    EP_HOST_ASSERT(a.size(0) == b.size(0) and d.scalar_type() == torch::kFloat32 and d.dim() == 3);
+    EP_HOST_ASSERT(a.size(0) == b.size(0) and d.dim() == 3);
+    EP_HOST_ASSERT(d.scalar_type() == torch::kFloat32 or (d.scalar_type() == torch::kBFloat16 and not accumulate));
     EP_HOST_ASSERT(psum.scalar_type() == torch::kInt32 and count.scalar_type() == torch::kInt32 and psum.numel() == count.numel());
     GroupedGemmArgs args = {};
     args.mode = kModeWgrad, args.epilogue = kEpilogueStore, args.num_groups = static_cast<int>(psum.numel());
-    args.accumulate = accumulate;
+    args.accumulate = accumulate, args.out_bf16 = d.scalar_type() == torch::kBFloat16;
     args.psum = psum.data_ptr<int>(), args.count = count.data_ptr<int>();
     args.m = static_cast<int>(a.size(1)), args.n = static_cast<int>(b.size(1)), args.k = 0;
     EP_HOST_ASSERT(d.size(0) == args.num_groups and d.size(1) == args.m and d.size(2) == args.n);
@@ -177,7 +202,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("get_dispatch_layout", &get_dispatch_layout, py::arg("topk_idx"), py::arg("num_experts"), py::arg("num_ranks"),
           py::arg("num_sms") = 0);
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
-          py::arg("mode"), py::arg("epilogue") = 0, py::arg("num_sms") = 0);
+          py::arg("mode"), py::arg("epilogue") = 0, py::arg("num_sms") = 0, py::arg("alignment") = 1,
+          py::arg("row_scale") = py::none(), py::arg("keep") = py::none());
+    m.def("swiglu_backward", &swiglu_backward, py::arg("h"), py::arg("dact"), py::arg("row_scale") = py::none());
     m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
           py::arg("num_sms") = 0, py::arg("accumulate") = true);
 

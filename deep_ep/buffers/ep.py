@@ -155,6 +155,11 @@ class EPBuffer(BufferBase):
         if os.environ.get('EP_BUFFER_DEBUG', 0):
             print(f'Initializing EP buffer with {num_bytes} bytes at rank EP {self.rank_idx}/{self.num_ranks}')
 
+        # every rank must build the same buffer: a mismatch would corrupt peers' receive regions later
+        configs = [None] * self.num_ranks
+        dist.all_gather_object(configs, (num_bytes, num_lb_bytes, num_max_tokens_per_rank), group)
+        assert all(c == configs[0] for c in configs), f'EPBuffer arguments differ across ranks: {configs}'
+
         self.comm_handle = comm.get_comm_handle(group)
         super().__init__(explicitly_destroy)
         self.is_simulated = not torch.cuda.is_available()

@@ -49,6 +49,11 @@ EP_DEVICE void st_release_gpu(unsigned int* p, unsigned int v) {
 EP_DEVICE void st_relaxed_sys(unsigned long long* p, unsigned long long v) {
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+EP_DEVICE unsigned long long ld_relaxed_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
 EP_DEVICE void red_add_release_sys(int* p, int v) {
     asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

@@ -102,6 +102,7 @@ namespace expand_detail {
 EP_HOST_DEVICE int64_t smem_bytes(int num_warps, int num_stages, int num_topk, int num_local_experts, int token_bytes) {
     int64_t n = int64_t(num_warps) * num_stages * 8;
     n += int64_t(num_warps) * num_local_experts * 4 * 2;      // running bases + hit bitmaps
+    n += int64_t(num_local_experts) * 4 * 2;                  // expert region ends and per-CTA bases
     n += int64_t(num_warps) * 32 * (num_topk + 1) * 4;        // slots (+ source row index)
     n = math::align<int64_t>(n, 128);
     n += int64_t(num_warps) * num_stages * token_bytes;

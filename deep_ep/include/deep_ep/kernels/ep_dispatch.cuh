@@ -184,16 +184,26 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
     if (is_aux) {
         if (cta != 0 or a.cached) return;
         // rank counts -> peers
-        for (int r = lane; r < num_ranks; r += 32) {
+        for (int r0 = 0; r0 < num_ranks; r0 += 32) {
+            // per-rank totals over all CTAs: lanes split the CTAs of one rank at a time so that the loads overlap
             int total = 0;
-            for (int c = 0; c < num_ctas; ++c) total += __ldcg(&a.ws->cta_rank_count[c][r]);
-            ptx::st_release_sys(&a.peers.sym(&a.ws->recv_rank_count[rank], r)[0], layout::pack_tagged(epoch, total));
+            for (int rr = r0; rr < min(r0 + 32, num_ranks); ++rr) {
+                int partial = 0;
+                for (int c = lane; c < num_ctas; c += 32) partial += __ldcg(&a.ws->cta_rank_count[c][rr]);
+                #pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, o);
+                if (rr - r0 == lane) total = partial;
+            }
+            const int r = r0 + lane;
+            if (r >= num_ranks) continue;
+            // count words validate themselves through their epoch tag: no ordering against other stores is needed
+            ptx::st_relaxed_sys(&a.peers.sym(&a.ws->recv_rank_count[rank], r)[0], layout::pack_tagged(epoch, total));
         }
         // expert counts -> owners (and clean the local histogram for the next call)
         for (int e = lane; e < a.num_experts; e += 32) {
             const int v = __ldcg(&a.ws->send_expert_count[e]);
             a.ws->send_expert_count[e] = 0;
-            ptx::st_release_sys(a.peers.sym(&a.ws->recv_expert_count[rank][e % num_local_experts], e / num_local_experts),
+            ptx::st_relaxed_sys(a.peers.sym(&a.ws->recv_expert_count[rank][e % num_local_experts], e / num_local_experts),
                                 layout::pack_tagged(epoch, v));
         }
         // wait for every source's rank count, inclusive prefix
@@ -206,7 +216,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
             if (s < num_ranks) {
                 unsigned long long w = 0;
                 const bool got = dev::spin_until(deadline, [&]() {
-                    w = ptx::ld_acquire_sys(&a.ws->recv_rank_count[s]);
+                    w = ptx::ld_relaxed_sys(&a.ws->recv_rank_count[s]);
                     return layout::tagged_epoch(w) == epoch;
                 });
                 if (not got) dev::report_status(cs, hs, kStatusCountTimeout, rank, s, kSiteRankCount, epoch, layout::tagged_epoch(w));
@@ -232,7 +242,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
                 for (int s = 0; s < num_ranks; ++s) {
                     unsigned long long w = 0;
                     const bool got = dev::spin_until(deadline, [&]() {
-                        w = ptx::ld_acquire_sys(&a.ws->recv_expert_count[s][e]);
+                        w = ptx::ld_relaxed_sys(&a.ws->recv_expert_count[s][e]);
                         return layout::tagged_epoch(w) == epoch;
                     });
                     if (not got) dev::report_status(cs, hs, kStatusCountTimeout, rank, s, kSiteExpertCount, epoch, layout::tagged_epoch(w));
@@ -268,9 +278,18 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
     // ------------------------------------------------------------------ pusher warps
     // running slot base per (warp, rank): tokens of earlier CTAs + earlier warps of this CTA
     if (not a.cached) {
+        // tokens of earlier CTAs: one warp per rank, lanes split the CTAs so that the loads overlap
+        __shared__ int cta_base[kMaxRanks];
+        for (int r = warp; r < num_ranks; r += W) {
+            int partial = 0;
+            for (int c = lane; c < cta; c += 32) partial += __ldcg(&a.ws->cta_rank_count[c][r]);
+            #pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, o);
+            if (lane == 0) cta_base[r] = partial;
+        }
+        ptx::named_barrier(1, num_pushers);
         for (int r = threadIdx.x; r < num_ranks; r += num_pushers) {
-            int base = 0;
-            for (int c = 0; c < cta; ++c) base += __ldcg(&a.ws->cta_rank_count[c][r]);
+            int base = cta_base[r];
             for (int w = 0; w < W; ++w) {
                 const int cnt = sm.warp_rank[w * kMaxRanks + r];
                 sm.warp_rank[w * kMaxRanks + r] = base, base += cnt;

@@ -51,6 +51,10 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
     p += int64_t(W) * num_local_experts * 4;
     int* slots_all = reinterpret_cast<int*>(p);
     p += int64_t(W) * 32 * (k + 1) * 4;
+    int* psum_sm = reinterpret_cast<int*>(p);          // end of every local expert's rows
+    p += int64_t(num_local_experts) * 4;
+    int* base_sm = reinterpret_cast<int*>(p);          // first row this CTA writes for every local expert
+    p += int64_t(num_local_experts) * 4;
     p = base + math::align<int64_t>(p - base, 128);
     uint8_t* stages_all = p;
 
@@ -73,6 +77,7 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
         }
     }
     for (int s = threadIdx.x; s < a.num_ranks; s += blockDim.x) psum_rank_smem[s] = a.psum_rank[s];
+    for (int e = threadIdx.x; e < num_local_experts; e += blockDim.x) psum_sm[e] = a.psum_expert[e];
     __syncthreads();
     if (not dev::healthy(cs)) return;
 
@@ -107,9 +112,17 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
             a.ws->cta_expert_count[cta][e] = total;
         }
         if (not dev::grid_sync(cs, hs, num_ctas, a.timeout_ns, a.rank, kSiteGridSync)) return;
+        // rows written by earlier CTAs: one warp per expert, lanes split the CTAs so that the loads overlap
+        for (int e = warp; e < num_local_experts; e += W) {
+            int partial = 0;
+            for (int c = lane; c < cta; c += 32) partial += __ldcg(&a.ws->cta_expert_count[c][e]);
+            #pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, o);
+            if (lane == 0) base_sm[e] = psum_sm[e] - a.num_unaligned[e] + partial;     // aligned region start + earlier rows
+        }
+        __syncthreads();
         for (int e = threadIdx.x; e < num_local_experts; e += blockDim.x) {
-            int b = a.psum_expert[e] - a.num_unaligned[e];     // aligned start of the expert's region
-            for (int c = 0; c < cta; ++c) b += __ldcg(&a.ws->cta_expert_count[c][e]);
+            int b = base_sm[e];
             for (int w = 0; w < W; ++w) {
                 const int cnt = run_all[w * num_local_experts + e];
                 run_all[w * num_local_experts + e] = b, b += cnt;
@@ -238,7 +251,7 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
         const int gw = cta * W + warp, num_gw = num_ctas * W;
         const int4 zero = make_int4(0, 0, 0, 0);
         for (int e = 0; e < num_local_experts; ++e) {
-            const int end = a.psum_expert[e];
+            const int end = psum_sm[e];
             const int pad_end = min(math::align(end, a.expert_alignment), a.num_expanded_rows);
             for (int row = end + gw; row < pad_end; row += num_gw) {
                 for (int c = lane; c < a.hidden_bytes / 16; c += 32)

@@ -29,7 +29,7 @@ namespace gemm_detail {
 EP_DEVICE float silu(float x) { return x / (1.0f + __expf(-x)); }
 
 struct Tile {
-    int expert, m0, n0, row_base, rows_valid, num_k_blocks;
+    int expert, m0, n0, row_base, rows_valid, rows_written, num_k_blocks;
 };
 
 // tile index -> (expert, m block, n block). `prefix` holds the exclusive prefix of tiles per expert.
@@ -46,11 +46,13 @@ EP_DEVICE Tile locate_tile(const GroupedGemmArgs& a, const int* prefix, int tile
     if (a.mode == kModeWgrad) {
         const int m_tiles = a.m / kGemmBlockM;
         t.m0 = (local % m_tiles) * kGemmBlockM, t.n0 = (local / m_tiles) * a.block_n;
-        t.rows_valid = kGemmBlockM, t.num_k_blocks = math::ceil_div(count, kGemmBlockK);
+        t.rows_valid = t.rows_written = kGemmBlockM, t.num_k_blocks = math::ceil_div(count, kGemmBlockK);
     } else {
         const int m_tiles = math::ceil_div(count, kGemmBlockM);
         t.m0 = (local % m_tiles) * kGemmBlockM, t.n0 = (local / m_tiles) * a.block_n_out;
         t.rows_valid = min(kGemmBlockM, count - t.m0), t.num_k_blocks = math::ceil_div(a.k, kGemmBlockK);
+        // padding rows of the expert's aligned region that fall into this tile are written as zeros
+        t.rows_written = min(kGemmBlockM, math::align(count, max(a.alignment, 1)) - t.m0);
     }
     return t;
 }
@@ -135,7 +137,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         if (a.mode == kModeForward) {
                             // K-major weights [G * N, K]; with SwiGLU the tile pairs 128 gate rows with 128 up rows
                             const int row = t.expert * a.n;
-                            if (a.epilogue == kEpilogueSwiGLU) {
+                            if (a.epilogue != kEpilogueStore) {
                                 tc::tma_load_2d(sb, &map_b, k0, row + t.n0, &full_bar[s]);
                                 tc::tma_load_2d(sb + 128 * 128, &map_b, k0, row + a.n / 2 + t.n0, &full_bar[s]);
                             } else {
@@ -197,7 +199,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t taddr = tmem_base + acc * 256 + (uint32_t(quarter * 32) << 16);
             const bool valid = row < t.rows_valid;
             if (a.mode == kModeWgrad) {
-                float* out = reinterpret_cast<float*>(a.d) + (size_t(t.expert) * a.m + t.m0 + row) * a.n + t.n0;
+                const size_t out_index = (size_t(t.expert) * a.m + t.m0 + row) * a.n + t.n0;
+                float* out = reinterpret_cast<float*>(a.d) + out_index;
+                __nv_bfloat16* out16 = reinterpret_cast<__nv_bfloat16*>(a.d) + out_index;
                 for (int c = 0; c < BN; c += 32) {
                     uint32_t r[32];
                     if (t.num_k_blocks > 0) {
@@ -206,6 +210,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     } else {
                         #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = 0;
+                    }
+                    if (a.out_bf16) {
+                        #pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            int4 packed;
+                            uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+                            #pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                w[i] = ptx::float2_to_bf16x2(__uint_as_float(r[8 * v + 2 * i]), __uint_as_float(r[8 * v + 2 * i + 1]));
+                            *reinterpret_cast<int4*>(out16 + c + 8 * v) = packed;
+                        }
+                        continue;
                     }
                     #pragma unroll
                     for (int v = 0; v < 8; ++v) {
@@ -218,44 +234,55 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         *reinterpret_cast<float4*>(out + c + 4 * v) = val;
                     }
                 }
-            } else if (a.epilogue == kEpilogueSwiGLU) {
-                __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + size_t(t.row_base + t.m0 + row) * a.n_out + t.n0;
+            } else if (a.epilogue != kEpilogueStore) {
+                const size_t grow = size_t(t.row_base + t.m0 + row);
+                __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + grow * a.n_out + t.n0;
+                __nv_bfloat16* keep = a.epilogue == kEpilogueSwiGLUKeep ? reinterpret_cast<__nv_bfloat16*>(a.d2) + grow * a.n + t.n0 : nullptr;
+                const bool written = row < t.rows_written;
+                const float scale = (valid and a.row_scale != nullptr) ? a.row_scale[grow] : 1.0f;
                 for (int c = 0; c < 128; c += 32) {
                     uint32_t g[32], u[32];
                     tc::tmem_ld_32x32(taddr + c, g);
                     tc::tmem_ld_32x32(taddr + 128 + c, u);
                     tc::wait_ld();
-                    if (valid) {
+                    if (not written) continue;
+                    #pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        int4 packed, pg, pu;
+                        uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+                        uint32_t* wg = reinterpret_cast<uint32_t*>(&pg);
+                        uint32_t* wu = reinterpret_cast<uint32_t*>(&pu);
                         #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            int4 packed;
-                            uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
-                            #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int j = 8 * v + 2 * i;
-                                w[i] = ptx::float2_to_bf16x2(silu(__uint_as_float(g[j])) * __uint_as_float(u[j]),
-                                                             silu(__uint_as_float(g[j + 1])) * __uint_as_float(u[j + 1]));
-                            }
-                            *reinterpret_cast<int4*>(out + c + 8 * v) = packed;
+                        for (int i = 0; i < 4; ++i) {
+                            const int j = 8 * v + 2 * i;
+                            const float g0 = valid ? __uint_as_float(g[j]) : 0.f, g1 = valid ? __uint_as_float(g[j + 1]) : 0.f;
+                            const float u0 = valid ? __uint_as_float(u[j]) : 0.f, u1 = valid ? __uint_as_float(u[j + 1]) : 0.f;
+                            w[i] = ptx::float2_to_bf16x2(silu(g0) * u0 * scale, silu(g1) * u1 * scale);
+                            wg[i] = ptx::float2_to_bf16x2(g0, g1), wu[i] = ptx::float2_to_bf16x2(u0, u1);
+                        }
+                        *reinterpret_cast<int4*>(out + c + 8 * v) = packed;
+                        if (keep != nullptr) {
+                            *reinterpret_cast<int4*>(keep + c + 8 * v) = pg;
+                            *reinterpret_cast<int4*>(keep + a.n / 2 + c + 8 * v) = pu;
                         }
                     }
                 }
             } else {
                 __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + size_t(t.row_base + t.m0 + row) * a.n_out + t.n0;
+                const bool written = row < t.rows_written;
                 for (int c = 0; c < BN; c += 32) {
                     uint32_t r[32];
                     tc::tmem_ld_32x32(taddr + c, r);
                     tc::wait_ld();
-                    if (valid) {
+                    if (not written) continue;
+                    #pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        int4 packed;
+                        uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
                         #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            int4 packed;
-                            uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
-                            #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                w[i] = ptx::float2_to_bf16x2(__uint_as_float(r[8 * v + 2 * i]), __uint_as_float(r[8 * v + 2 * i + 1]));
-                            *reinterpret_cast<int4*>(out + c + 8 * v) = packed;
-                        }
+                        for (int i = 0; i < 4; ++i)
+                            w[i] = valid ? ptx::float2_to_bf16x2(__uint_as_float(r[8 * v + 2 * i]), __uint_as_float(r[8 * v + 2 * i + 1])) : 0u;
+                        *reinterpret_cast<int4*>(out + c + 8 * v) = packed;
                     }
                 }
             }

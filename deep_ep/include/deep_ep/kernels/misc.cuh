@@ -4,6 +4,7 @@
 // with ordinary peer loads/stores (or NVLS `multimem.st`) issued by the SMs over NVLink.
 #pragma once
 
+#include "../device/bulk_copy.cuh"
 #include "../device/sync.cuh"
 #include "misc_args.hpp"
 
@@ -81,7 +82,11 @@ EP_DEVICE void multimem_st_v4(void* mc_ptr, const int4& v) {
 // destination (peer order rotated by rank), or written once through the NVLS multicast mapping.
 __global__ void __launch_bounds__(512) bucket_all_gather_kernel(const __grid_constant__ AllGatherArgs a) {
     constexpr int64_t kTileBytes = 32 * 1024;
+    extern __shared__ uint8_t ag_smem[];
     const int rank = a.peers.rank, num_ranks = a.peers.num_ranks;
+    const int warp = threadIdx.x / 32, lane = ptx::lane_id(), warps_per_cta = blockDim.x / 32;
+    dev::WarpCopier copier;
+    copier.init(ag_smem, warps_per_cta, warp, lane);
 
     // "destinations have been consumed" barrier, then release the other CTAs
     if (not dev::healthy(a.cs)) return;
@@ -99,7 +104,16 @@ __global__ void __launch_bounds__(512) bucket_all_gather_kernel(const __grid_con
         const bool vec16 = (mis & 15) == 0;
         for (int64_t tile = (blockIdx.x + gridDim.x - tile_base % gridDim.x) % gridDim.x; tile < num_tiles; tile += gridDim.x) {
             const int64_t begin = tile * kTileBytes, end = min(begin + kTileBytes, bucket.num_bytes);
-            if (vec16) {
+            if (vec16 and not a.use_multicast) {
+                // read each 8 KiB chunk once into shared memory, store it to every destination with the TMA engine
+                for (int64_t o = begin + int64_t(warp) * dev::kCopyChunkBytes; o < end; o += int64_t(warps_per_cta) * dev::kCopyChunkBytes) {
+                    const int bytes = int(min(int64_t(dev::kCopyChunkBytes), end - o));
+                    const int num_dsts = a.skip_local ? num_ranks - 1 : num_ranks;
+                    copier.copy_chunk(bucket.src + o, bytes, num_dsts, [&](int i) {
+                        return a.peers.base[(rank + 1 + i) % num_ranks] + dst_off + o;      // rotation: the local rank comes last
+                    }, lane);
+                }
+            } else if (vec16) {
                 for (int64_t o = begin + threadIdx.x * 16; o < end; o += blockDim.x * 16) {
                     const int4 v = ptx::ld_nc_v4(bucket.src + o);
                     if (a.use_multicast) {
@@ -126,6 +140,8 @@ __global__ void __launch_bounds__(512) bucket_all_gather_kernel(const __grid_con
         }
         tile_base += num_tiles;
     }
+    copier.drain();
+    if (copier.failed and lane == 0) dev::report_status(a.cs, a.host_status, kStatusMbarrierTimeout, rank, -1, 42, 0, 0);
     __threadfence_system();
 }
 
@@ -180,9 +196,21 @@ __global__ void __launch_bounds__(512) lb_exchange_kernel(const __grid_constant_
 // ---------------------------------------------------------------------------------------- pipeline
 namespace pp_detail {
 
-EP_DEVICE void copy_bytes(uint8_t* dst, const uint8_t* src, int64_t n) {
+// Grid-wide copy. 16-byte aligned ranges go through the TMA ring of `copier`; the tail and unaligned ranges use
+// ordinary loads and stores.
+EP_DEVICE void copy_bytes(uint8_t* dst, const uint8_t* src, int64_t n, dev::WarpCopier& copier) {
     const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x, nthreads = int64_t(gridDim.x) * blockDim.x;
-    if (((reinterpret_cast<uint64_t>(dst) | reinterpret_cast<uint64_t>(src)) & 15) == 0) {
+    if (((reinterpret_cast<uint64_t>(dst) | reinterpret_cast<uint64_t>(src)) & 15) == 0 and n >= dev::kCopyChunkBytes) {
+        const int lane = ptx::lane_id();
+        const int64_t gw = tid / 32, num_gw = nthreads / 32;
+        const int64_t body = n / 16 * 16;
+        for (int64_t o = gw * dev::kCopyChunkBytes; o < body; o += num_gw * dev::kCopyChunkBytes) {
+            const int bytes = int(min(int64_t(dev::kCopyChunkBytes), body - o));
+            copier.copy_chunk(src + o, bytes, 1, [&](int) { return dst + o; }, lane);
+        }
+        copier.drain();
+        for (int64_t i = body + tid; i < n; i += nthreads) dst[i] = src[i];
+    } else if (((reinterpret_cast<uint64_t>(dst) | reinterpret_cast<uint64_t>(src)) & 15) == 0) {
         const int64_t nvec = n / 16;
         for (int64_t i = tid; i < nvec; i += nthreads) ptx::st_na_v4(dst + i * 16, ptx::ld_v4(src + i * 16));
         for (int64_t i = nvec * 16 + tid; i < n; i += nthreads) dst[i] = src[i];
@@ -209,8 +237,11 @@ EP_DEVICE bool last_cta(layout::CommonSignals* cs) {
 // Buffered send to a ring neighbour: wait for a free slot (credit), copy the tensor into the
 // neighbour's landing slot, then publish the arrival counter with release semantics.
 __global__ void __launch_bounds__(512) pp_send_kernel(const __grid_constant__ PPArgs a) {
+    extern __shared__ uint8_t pp_smem[];
     layout::CommonSignals* cs = &a.ws->common;
     if (not dev::healthy(cs)) return;
+    dev::WarpCopier copier;
+    copier.init(pp_smem, blockDim.x / 32, threadIdx.x / 32, ptx::lane_id());
     const int d = a.direction;
     const unsigned long long n = a.ws->send_count[d];
     __shared__ int ok_smem;
@@ -229,7 +260,8 @@ __global__ void __launch_bounds__(512) pp_send_kernel(const __grid_constant__ PP
     // the receiver sees data from its previous rank in region 1 and from its next rank in region 0
     const int region = 1 - d;
     uint8_t* slot = a.peers.base[a.peer] + a.storage_offset + (int64_t(region) * a.num_inflight + n % a.num_inflight) * a.slot_bytes;
-    pp_detail::copy_bytes(slot, a.x, a.num_bytes);
+    pp_detail::copy_bytes(slot, a.x, a.num_bytes, copier);
+    if (copier.failed and ptx::lane_id() == 0) dev::report_status(cs, a.host_status, kStatusMbarrierTimeout, a.peers.rank, a.peer, 52, 0, 0);
     if (pp_detail::last_cta(cs) and threadIdx.x == 0) {
         ptx::st_release_sys(a.peers.sym(&a.ws->arrival[region], a.peer), n + 1);
         a.ws->send_count[d] = n + 1;
@@ -238,8 +270,11 @@ __global__ void __launch_bounds__(512) pp_send_kernel(const __grid_constant__ PP
 
 // Matching receive: wait for the arrival counter, copy out of the landing slot, return the credit.
 __global__ void __launch_bounds__(512) pp_recv_kernel(const __grid_constant__ PPArgs a) {
+    extern __shared__ uint8_t pp_smem[];
     layout::CommonSignals* cs = &a.ws->common;
     if (not dev::healthy(cs)) return;
+    dev::WarpCopier copier;
+    copier.init(pp_smem, blockDim.x / 32, threadIdx.x / 32, ptx::lane_id());
     const int d = a.direction;            // region index == direction of the source
     const unsigned long long n = a.ws->recv_count[d];
     __shared__ int ok_smem;
@@ -253,7 +288,8 @@ __global__ void __launch_bounds__(512) pp_recv_kernel(const __grid_constant__ PP
     __syncthreads();
     if (not ok_smem) return;
     const uint8_t* slot = a.peers.base[a.peers.rank] + a.storage_offset + (int64_t(d) * a.num_inflight + n % a.num_inflight) * a.slot_bytes;
-    pp_detail::copy_bytes(a.x, slot, a.num_bytes);
+    pp_detail::copy_bytes(a.x, slot, a.num_bytes, copier);
+    if (copier.failed and ptx::lane_id() == 0) dev::report_status(cs, a.host_status, kStatusMbarrierTimeout, a.peers.rank, a.peer, 53, 0, 0);
     if (pp_detail::last_cta(cs) and threadIdx.x == 0) {
         // the sender addressed me through its direction 1 - d
         ptx::st_release_sys(a.peers.sym(&a.ws->release[1 - d], a.peer), n + 1);

@@ -103,18 +103,18 @@ class MoELayer(nn.Module):
         topk_weights = topk_weights / topk_weights.sum(dim=-1, keepdim=True)
         return topk_idx, topk_weights
 
-    def experts(self, recv_x: torch.Tensor, handle: EPHandle) -> torch.Tensor:
+    def experts(self, recv_x: torch.Tensor, recv_w: torch.Tensor, handle: EPHandle) -> torch.Tensor:
+        """Expert FFN on the expanded rows, already multiplied by each row's routing weight."""
         from ..ops.grouped_gemm import grouped_swiglu_ffn
         return grouped_swiglu_ffn(recv_x, self.w_gate_up, self.w_down, handle.psum_num_recv_tokens_per_expert,
                                   handle.num_unaligned_recv_tokens_per_expert, handle.num_recv_tokens_per_expert_list,
-                                  self.config.expert_alignment, backend=self.config.expert_backend)
+                                  self.config.expert_alignment, backend=self.config.expert_backend, row_scale=recv_w)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         topk_idx, topk_weights = self.route(x.detach())
         recv_x, recv_w = _Dispatch.apply(x, topk_idx, topk_weights.float().contiguous(), self)
         handle = self._handle
-        y = self.experts(recv_x, handle)
-        y = y * recv_w.unsqueeze(1).to(y.dtype)
+        y = self.experts(recv_x, recv_w, handle)
         out = _Combine.apply(y, self, handle)
         if self.config.num_shared_experts > 0:
             g, u = F.linear(x, self.shared_gate_up).chunk(2, dim=-1)

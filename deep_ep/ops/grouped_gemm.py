@@ -14,25 +14,76 @@ import torch.nn.functional as F
 from .._C_loader import _C
 
 MODE_FORWARD, MODE_DGRAD, MODE_WGRAD = 0, 1, 2
-EPILOGUE_STORE, EPILOGUE_SWIGLU = 0, 1
+EPILOGUE_STORE, EPILOGUE_SWIGLU, EPILOGUE_SWIGLU_KEEP = 0, 1, 2
 
 
 def grouped_gemm_forward(x: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
-                         swiglu: bool = False, num_sms: int = 0) -> torch.Tensor:
+                         swiglu: bool = False, num_sms: int = 0, alignment: int = 1,
+                         row_scale: Optional[torch.Tensor] = None, keep_preactivation: bool = False):
     """`y[rows_e] = x[rows_e] @ w[e].T` with `w [G, N, K]`; with `swiglu`, `w[e] = [gate; up]` and
-    `y = silu(x @ gate.T) * (x @ up.T)` (`[rows, N / 2]`). Rows outside every expert's range are left untouched."""
+    `y = silu(x @ gate.T) * (x @ up.T) * row_scale` (`[rows, N / 2]`); `keep_preactivation` also returns the bf16
+    `[gate | up]` matrix. Padding rows inside an expert's aligned region are written as zeros; rows that belong to no
+    region are left untouched."""
     n_out = w.size(1) // 2 if swiglu else w.size(1)
     y = torch.empty((x.size(0), n_out), dtype=torch.bfloat16, device=x.device)
-    _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_SWIGLU if swiglu else EPILOGUE_STORE, num_sms)
-    return y
+    if not swiglu:
+        assert row_scale is None and not keep_preactivation
+        _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_STORE, num_sms, alignment)
+        return y
+    keep = torch.empty((x.size(0), w.size(1)), dtype=torch.bfloat16, device=x.device) if keep_preactivation else None
+    _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_SWIGLU_KEEP if keep_preactivation else EPILOGUE_SWIGLU,
+                    num_sms, alignment, row_scale, keep)
+    return (y, keep) if keep_preactivation else y
 
 
 def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
-                       num_sms: int = 0) -> torch.Tensor:
+                       num_sms: int = 0, alignment: int = 1) -> torch.Tensor:
     """`dx[rows_e] = dy[rows_e] @ w[e]` with `w [G, N, K]` read as stored (no transpose copy)."""
     dx = torch.empty((dy.size(0), w.size(2)), dtype=torch.bfloat16, device=dy.device)
-    _C.grouped_gemm(dy, w, dx, psum, count, MODE_DGRAD, EPILOGUE_STORE, num_sms)
+    _C.grouped_gemm(dy, w, dx, psum, count, MODE_DGRAD, EPILOGUE_STORE, num_sms, alignment)
     return dx
+
+
+def _wgrad(dy, x, w, psum, count, alignment):
+    """Weight gradient of one grouped linear layer, honouring a persistent fp32 `main_grad` buffer on the parameter."""
+    main_grad = getattr(w, 'main_grad', None)
+    if alignment % 64 == 0:
+        acc = main_grad if main_grad is not None else torch.empty(w.shape, dtype=w.dtype, device=w.device)
+        grouped_gemm_wgrad(dy, x, acc, psum, count, accumulate=main_grad is not None)
+    else:
+        acc = main_grad if main_grad is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        for e, (start, c) in enumerate(_ranges(psum, count)):
+            if c:
+                acc[e].addmm_(dy[start:start + c].float().t(), x[start:start + c].float())
+    return None if main_grad is not None else (acc if acc.dtype == w.dtype else acc.to(w.dtype))
+
+
+class GroupedSwiGLUFFN(torch.autograd.Function):
+    """Whole expert FFN as one autograd node: `y = (silu(x Wg^T) * (x Wu^T) * row_scale) Wd^T` per expert.
+
+    Forward: GEMM1 with the SwiGLU (and row-scale) epilogue that also keeps the pre-activation, then GEMM2.
+    Backward: dgrad and wgrad of GEMM2, one elementwise SwiGLU-backward kernel, dgrad and wgrad of GEMM1.
+    Requires the expert alignment to be a multiple of 128 (every padding row is then written as zero by a tile)."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate_up, w_down, row_scale, psum, count, alignment):
+        act, h = grouped_gemm_forward(x, w_gate_up, psum, count, swiglu=True, alignment=alignment, row_scale=row_scale,
+                                      keep_preactivation=True)
+        y = grouped_gemm_forward(act, w_down, psum, count, alignment=alignment)
+        ctx.save_for_backward(x, w_gate_up, w_down, row_scale, psum, count, h, act)
+        ctx.alignment = alignment
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w_gate_up, w_down, row_scale, psum, count, h, act = ctx.saved_tensors
+        dy = dy.contiguous()
+        dact = grouped_gemm_dgrad(dy, w_down, psum, count, alignment=ctx.alignment)
+        dw_down = _wgrad(dy, act, w_down, psum, count, ctx.alignment) if ctx.needs_input_grad[2] else None
+        dh = _C.swiglu_backward(h, dact, row_scale)
+        dx = grouped_gemm_dgrad(dh, w_gate_up, psum, count, alignment=ctx.alignment) if ctx.needs_input_grad[0] else None
+        dw_gate_up = _wgrad(dh, x, w_gate_up, psum, count, ctx.alignment) if ctx.needs_input_grad[1] else None
+        return dx, dw_gate_up, dw_down, None, None, None, None
 
 
 def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, dw: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
@@ -72,14 +123,16 @@ class GroupedLinear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             main_grad = getattr(w, 'main_grad', None)
             if ctx.alignment % 64 == 0:
-                acc = main_grad if main_grad is not None else torch.empty(w.shape, dtype=torch.float32, device=w.device)
+                # fp32 accumulation happens in tensor memory; without a persistent fp32 buffer the result is rounded
+                # once and stored in the parameter's dtype, which avoids materialising an fp32 copy of every expert
+                acc = main_grad if main_grad is not None else torch.empty(w.shape, dtype=w.dtype, device=w.device)
                 grouped_gemm_wgrad(dy, x, acc, psum, count, accumulate=main_grad is not None)
             else:
                 acc = main_grad if main_grad is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
                 for e, (start, c) in enumerate(_ranges(psum, count)):
                     if c:
                         acc[e].addmm_(dy[start:start + c].float().t(), x[start:start + c].float())
-            dw = None if main_grad is not None else acc.to(w.dtype)
+            dw = None if main_grad is not None else (acc if acc.dtype == w.dtype else acc.to(w.dtype))
         if dx is not None:
             # rows that belong to no expert (alignment padding) carry no gradient
             pass
@@ -99,14 +152,21 @@ def _torch_ffn(x, w_gate_up, w_down, psum, count):
 
 def grouped_swiglu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, psum: torch.Tensor,
                        unaligned: torch.Tensor, per_expert_list: Optional[List[int]], alignment: int,
-                       backend: str = 'grouped') -> torch.Tensor:
+                       backend: str = 'grouped', row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """SwiGLU FFN of every local expert on its rows. `w_gate_up [G, 2I, H]` (gate rows first), `w_down [G, H, I]`.
 
     Padding rows of the result are zero. In inference mode the SwiGLU is fused into the first GEMM's epilogue;
     under autograd the pre-activation is kept for the backward pass.
     """
     if backend == 'torch' or not (_supported(x, w_gate_up) and _supported(x, w_down)):
-        return _torch_ffn(x, w_gate_up, w_down, psum, unaligned)
+        y = _torch_ffn(x, w_gate_up, w_down, psum, unaligned)
+        return y if row_scale is None else y * row_scale.unsqueeze(1).to(y.dtype)
+    if alignment % 128 == 0 and w_gate_up.size(1) % 256 == 0:
+        # fused path: no elementwise passes, padding rows come out as zeros
+        return GroupedSwiGLUFFN.apply(x, w_gate_up, w_down, row_scale, psum, unaligned, alignment)
+    if row_scale is not None:
+        y = grouped_swiglu_ffn(x, w_gate_up, w_down, psum, unaligned, per_expert_list, alignment, backend)
+        return y * row_scale.unsqueeze(1).to(y.dtype)
     if not torch.is_grad_enabled() or not (x.requires_grad or w_gate_up.requires_grad or w_down.requires_grad):
         if w_gate_up.size(1) % 256 == 0:
             act = grouped_gemm_forward(x, w_gate_up, psum, unaligned, swiglu=True)

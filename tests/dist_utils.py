@@ -10,7 +10,7 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world_size, port, backend, fn, args):
+def _worker(rank, world_size, port, backend, fn, args, timeout_s=None):
     import faulthandler
     faulthandler.enable()
     if ROOT not in sys.path:
@@ -18,6 +18,9 @@ def _worker(rank, world_size, port, backend, fn, args):
     os.environ['MASTER_ADDR'] = '127.0.0.1'
     os.environ['MASTER_PORT'] = str(port)
     kwargs = dict(backend=backend, init_method=f'tcp://127.0.0.1:{port}', world_size=world_size, rank=rank)
+    if timeout_s is not None:
+        import datetime
+        kwargs['timeout'] = datetime.timedelta(seconds=timeout_s)
     if backend == 'nccl':
         torch.cuda.set_device(rank)
         kwargs['device_id'] = torch.device('cuda', rank)
@@ -34,6 +37,6 @@ def _worker(rank, world_size, port, backend, fn, args):
             pass
 
 
-def run_distributed(fn, world_size, port, backend='gloo', args=()):
+def run_distributed(fn, world_size, port, backend='gloo', args=(), timeout_s=None):
     """Run `fn(rank, world_size, *args)` in `world_size` processes; raises if any of them fails."""
-    mp.spawn(_worker, args=(world_size, port, backend, fn, args), nprocs=world_size, join=True)
+    mp.spawn(_worker, args=(world_size, port, backend, fn, args, timeout_s), nprocs=world_size, join=True)

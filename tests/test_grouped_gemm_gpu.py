@@ -46,6 +46,10 @@ def test_grouped_forward_dgrad_wgrad(counts, alignment, k, n):
         gg.grouped_gemm_wgrad(dy, x, dw_store, psum, count, accumulate=False)
         torch.cuda.synchronize()
         assert torch.allclose(dw_store * 2, dw, atol=1e-3, rtol=1e-4)
+        dw_bf16 = torch.full((g, n, k), float('nan'), device=dev, dtype=torch.bfloat16)
+        gg.grouped_gemm_wgrad(dy, x, dw_bf16, psum, count, accumulate=False)
+        torch.cuda.synchronize()
+        assert torch.equal(dw_bf16, dw_store.to(torch.bfloat16))
     torch.cuda.synchronize()
     for e, (s, c) in enumerate(zip(starts, counts)):
         if c == 0:
@@ -93,3 +97,33 @@ def test_grouped_swiglu_ffn_matches_torch():
     assert rel_err(xs[0].grad[valid], xs[1].grad[valid]) < 3e-2
     assert rel_err(w1s[0].grad, w1s[1].grad) < 3e-2
     assert rel_err(w2s[0].grad, w2s[1].grad) < 3e-2
+
+
+@pytest.mark.gpu
+def test_fused_ffn_row_scale_and_zero_padding():
+    """The fused FFN node: routing weights applied in the GEMM1 epilogue, padding rows exactly zero, gradients right."""
+    from deep_ep.ops import grouped_gemm as gg
+    torch.manual_seed(2)
+    dev = torch.device('cuda')
+    counts, alignment, h, inter = [130, 1, 0, 255], 128, 256, 128
+    psum, count, rows, starts = make_layout(counts, alignment, dev)
+    valid = torch.zeros(rows, dtype=torch.bool, device=dev)
+    for s, c in zip(starts, counts):
+        valid[s:s + c] = True
+    x = torch.randn(rows, h, device=dev, dtype=torch.bfloat16) * valid.unsqueeze(1)
+    scale = torch.rand(rows, device=dev) * valid
+    w1 = (torch.randn(len(counts), 2 * inter, h, device=dev) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(len(counts), h, inter, device=dev) * 0.05).to(torch.bfloat16)
+    params = [[t.clone().requires_grad_() for t in (x, w1, w2)] for _ in range(2)]
+    outs = [gg.grouped_swiglu_ffn(p[0], p[1], p[2], psum, count, None, alignment, backend=b, row_scale=scale)
+            for p, b in zip(params, ('grouped', 'torch'))]
+    assert torch.count_nonzero(outs[0][~valid]).item() == 0
+    grad = torch.randn_like(outs[0]) * valid.unsqueeze(1)
+    for o in outs:
+        o.backward(grad)
+
+    def rel_err(a, b):
+        return ((a.float() - b.float()).norm() / b.float().norm().clamp(min=1e-6)).item()
+    assert rel_err(outs[0][valid], outs[1][valid]) < 2e-2
+    for a, b in zip(params[0], params[1]):
+        assert rel_err(a.grad, b.grad) < 3e-2
