@@ -61,10 +61,13 @@ class BaselineMoELayer(nn.Module):
         by_expert = torch.argsort(expert_of_row, stable=True)
         rows = recv[by_expert]
         outs, start = [], 0
+        # unbind once: indexing the stacked parameter per expert would make autograd materialise a full-size
+        # gradient of all experts for every expert
+        w1s, w2s = self.w_gate_up.unbind(0), self.w_down.unbind(0)
         for e, c in enumerate(counts.sum(0).tolist()):
             if c:
-                g, u = F.linear(rows[start:start + c], self.w_gate_up[e]).chunk(2, dim=-1)
-                outs.append(F.linear(F.silu(g) * u, self.w_down[e]))
+                g, u = F.linear(rows[start:start + c], w1s[e]).chunk(2, dim=-1)
+                outs.append(F.linear(F.silu(g) * u, w2s[e]))
             start += c
         out = torch.cat(outs) if outs else torch.empty_like(rows)
         back_rows = torch.empty_like(out)

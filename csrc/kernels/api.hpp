@@ -40,9 +40,10 @@ void lb_exchange(const kernels::LBArgs& args, int num_sms, cudaStream_t stream);
 void dispatch_layout(const kernels::LayoutArgs& args, int num_sms, cudaStream_t stream);
 
 // Grouped BF16 GEMM on tcgen05 tensor cores over the expanded layout. `a`/`b` are row-major bf16 matrices
-// ([a_rows, a_cols], [b_rows, b_cols]); their roles depend on `args.mode` (see grouped_gemm.cuh).
+// ([a_rows, a_cols], [b_rows, b_cols]); their roles depend on `args.mode` (see grouped_gemm.cuh). `use_pairs` selects
+// the CTA-pair kernel (`cta_group::2`, 256 x 256 tiles) when the shape allows it.
 void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, int64_t a_cols,
-                  const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream);
+                  const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream, bool use_pairs = false);
 
 // dh = d(silu(gate) * up * row_scale) / d[gate | up] for bf16 rows; `inter` must be a multiple of 8.
 void swiglu_backward(const void* h, const void* dact, const float* row_scale, void* dh, int64_t rows, int inter,

@@ -4,6 +4,7 @@
 
 #include <deep_ep/common/exception.hpp>
 #include <deep_ep/kernels/grouped_gemm.cuh>
+#include <deep_ep/kernels/grouped_gemm2.cuh>
 
 #include "../runtime/driver.hpp"
 #include "api.hpp"
@@ -29,7 +30,7 @@ CUtensorMap make_map_2d(const void* base, int64_t rows, int64_t cols, int box_co
 }  // namespace
 
 void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, int64_t a_cols,
-                  const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream) {
+                  const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream, bool use_pairs) {
     using namespace kernels;
     EP_HOST_ASSERT(args.num_groups > 0 and args.num_groups <= kMaxLocalExperts);
     // the driver call below needs a current context; autograd worker threads may not have touched the runtime yet
@@ -43,19 +44,33 @@ void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, 
         args.block_n_out = args.block_n, args.n_out = args.n;
     }
     if (args.mode == kModeWgrad) EP_HOST_ASSERT(args.m % kGemmBlockM == 0);
-    const int64_t budget = 200 * 1024;
-    args.num_stages = static_cast<int>(std::min<int64_t>(kGemmMaxStages, (budget - 1024) / ((kGemmBlockM + args.block_n) * kGemmBlockK * 2)));
-    EP_HOST_ASSERT(args.num_stages >= 2);
-
-    // A: K-major activations (box 64 x 128) or, for wgrad, MN-major (box 64 x 64)
-    const CUtensorMap map_a = args.mode == kModeWgrad ? make_map_2d(a, a_rows, a_cols, 64, 64) : make_map_2d(a, a_rows, a_cols, 64, 128);
-    // B: K-major weights (box 64 x 128) for forward, MN-major (box 64 x 64) otherwise
-    const CUtensorMap map_b = args.mode == kModeForward ? make_map_2d(b, b_rows, b_cols, 64, 128) : make_map_2d(b, b_rows, b_cols, 64, 64);
 
     int device = 0, sms = 0;
     CUDA_CHECK(cudaGetDevice(&device));
     CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-    const int grid = num_sms > 0 ? std::min(num_sms, sms) : sms;
+    int grid = num_sms > 0 ? std::min(num_sms, sms) : sms;
+    const int64_t budget = 200 * 1024;
+
+    // CTA pairs (256 x 256 tiles) whenever the shape allows it; the single-CTA kernel covers the rest
+    const bool pair = use_pairs and args.block_n == 256 and grid >= 2 and (args.mode != kModeWgrad or args.m % 256 == 0);
+    if (pair) {
+        grid -= grid % 2;
+        args.num_stages = static_cast<int>(std::min<int64_t>(kGemmMaxStages, (budget - 1024) / (2 * 128 * kGemmBlockK * 2)));
+        const CUtensorMap map_a = args.mode == kModeWgrad ? make_map_2d(a, a_rows, a_cols, 64, 64) : make_map_2d(a, a_rows, a_cols, 64, 128);
+        const CUtensorMap map_b = args.mode == kModeForward ? make_map_2d(b, b_rows, b_cols, 64, 128) : make_map_2d(b, b_rows, b_cols, 64, 64);
+        const auto smem = int64_t(args.num_stages) * 2 * 128 * kGemmBlockK * 2 + 1024;
+        CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        grouped_gemm_pair_kernel<<<grid, 192, smem, stream>>>(map_a, map_b, args);
+        CUDA_CHECK(cudaGetLastError());
+        return;
+    }
+
+    args.num_stages = static_cast<int>(std::min<int64_t>(kGemmMaxStages, (budget - 1024) / ((kGemmBlockM + args.block_n) * kGemmBlockK * 2)));
+    EP_HOST_ASSERT(args.num_stages >= 2);
+    // A: K-major activations (box 64 x 128) or, for wgrad, MN-major (box 64 x 64)
+    const CUtensorMap map_a = args.mode == kModeWgrad ? make_map_2d(a, a_rows, a_cols, 64, 64) : make_map_2d(a, a_rows, a_cols, 64, 128);
+    // B: K-major weights (box 64 x 128) for forward, MN-major (box 64 x 64) otherwise
+    const CUtensorMap map_b = args.mode == kModeForward ? make_map_2d(b, b_rows, b_cols, 64, 128) : make_map_2d(b, b_rows, b_cols, 64, 64);
     const auto smem = grouped_gemm_smem_bytes(args.block_n, args.num_stages);
     CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     grouped_gemm_kernel<<<grid, 192, smem, stream>>>(map_a, map_b, args);

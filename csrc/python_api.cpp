@@ -62,7 +62,7 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> get_dispatch_layout(cons
 // mode 1: d[rows, n] = a[rows, k] * b[g, k, n]; mode 2: d[g, m, n] += a[rows, m]^T * b[rows, n] (fp32).
 void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const torch::Tensor& psum,
                   const torch::Tensor& count, int mode, int epilogue, int num_sms, int alignment,
-                  const std::optional<torch::Tensor>& row_scale, const std::optional<torch::Tensor>& keep) {
+                  const std::optional<torch::Tensor>& row_scale, const std::optional<torch::Tensor>& keep, bool use_pairs) {
     using namespace kernels;
     EP_HOST_ASSERT(a.is_cuda() and b.is_cuda() and d.is_cuda() and a.is_contiguous() and b.is_contiguous() and d.is_contiguous());
     EP_HOST_ASSERT(a.scalar_type() == torch::kBFloat16 and b.scalar_type() == torch::kBFloat16 and a.dim() == 2 and b.dim() == 3);
@@ -100,7 +100,8 @@ void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::T
     } else {
         EP_HOST_UNREACHABLE("use grouped_gemm_wgrad for mode 2");
     }
-    launch::grouped_gemm(args, a.data_ptr(), rows, a.size(1), b.data_ptr(), b_rows, b_cols, num_sms, c10::cuda::getCurrentCUDAStream());
+    launch::grouped_gemm(args, a.data_ptr(), rows, a.size(1), b.data_ptr(), b_rows, b_cols, num_sms, c10::cuda::getCurrentCUDAStream(),
+                         use_pairs);
 }
 
 torch::Tensor swiglu_backward(const torch::Tensor& h, const torch::Tensor& dact, const std::optional<torch::Tensor>& row_scale) {
@@ -118,7 +119,7 @@ torch::Tensor swiglu_backward(const torch::Tensor& h, const torch::Tensor& dact,
 
 // d[g, m, n] (fp32) (+)= a[rows_e, m]^T * b[rows_e, n] for every expert e; padding rows of `a` or `b` must be zero.
 void grouped_gemm_wgrad(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const torch::Tensor& psum,
-                        const torch::Tensor& count, int num_sms, bool accumulate) {
+                        const torch::Tensor& count, int num_sms, bool accumulate, bool use_pairs) {
     using namespace kernels;
     EP_HOST_ASSERT(a.is_cuda() and b.is_cuda() and d.is_cuda() and a.is_contiguous() and b.is_contiguous() and d.is_contiguous());
     EP_HOST_ASSERT(a.scalar_type() == torch::kBFloat16 and b.scalar_type() == torch::kBFloat16 and a.dim() == 2 and b.dim() == 2);
@@ -133,7 +134,7 @@ void grouped_gemm_wgrad(const torch::Tensor& a, const torch::Tensor& b, const to
     EP_HOST_ASSERT(d.size(0) == args.num_groups and d.size(1) == args.m and d.size(2) == args.n);
     args.d = d.data_ptr(), args.status = nullptr;
     launch::grouped_gemm(args, a.data_ptr(), a.size(0), a.size(1), b.data_ptr(), b.size(0), b.size(1), num_sms,
-                         c10::cuda::getCurrentCUDAStream());
+                         c10::cuda::getCurrentCUDAStream(), use_pairs);
 }
 
 }  // namespace
@@ -203,10 +204,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("num_sms") = 0);
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
           py::arg("mode"), py::arg("epilogue") = 0, py::arg("num_sms") = 0, py::arg("alignment") = 1,
-          py::arg("row_scale") = py::none(), py::arg("keep") = py::none());
+          py::arg("row_scale") = py::none(), py::arg("keep") = py::none(), py::arg("use_pairs") = false);
     m.def("swiglu_backward", &swiglu_backward, py::arg("h"), py::arg("dact"), py::arg("row_scale") = py::none());
     m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
-          py::arg("num_sms") = 0, py::arg("accumulate") = true);
+          py::arg("num_sms") = 0, py::arg("accumulate") = true, py::arg("use_pairs") = false);
 
     py::class_<BufferBase, std::shared_ptr<BufferBase>>(m, "BufferBase")
         .def_readonly("main_context", &BufferBase::main_context)

@@ -93,4 +93,54 @@ EP_DEVICE void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
+// ---------------------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster (ranks 2i and 2i + 1) share one MMA: the even CTA issues it, each CTA supplies its half of
+// A (128 of the 256 rows) and its half of B (128 of the 256 columns) from its own shared memory at identical offsets,
+// and each CTA's tensor memory receives its 128 rows of the accumulator.
+EP_DEVICE uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+EP_DEVICE void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local_ptr`'s counterpart in CTA `rank` of this cluster
+EP_DEVICE uint32_t map_to_cta(const void* local_ptr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(ptx::smem_addr(local_ptr)), "r"(rank));
+    return out;
+}
+EP_DEVICE void mbarrier_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+EP_DEVICE void tmem_alloc_pair(uint32_t* smem_slot, uint32_t num_columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(ptx::smem_addr(smem_slot)), "r"(num_columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+EP_DEVICE void tmem_dealloc_pair(uint32_t tmem_base, uint32_t num_columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(num_columns) : "memory");
+}
+EP_DEVICE void mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(uint32_t(accumulate)) : "memory");
+}
+// One arrival on the mbarrier at the same shared-memory offset in BOTH CTAs of the pair when all MMAs issued so far
+// have completed (the commit, not a load, is what is multicast here).
+EP_DEVICE void commit_pair(uint64_t* bar) {
+    const uint16_t mask = 0x3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(ptx::smem_addr(bar)), "h"(mask) : "memory");
+}
+// Tiled 2-D load whose completion bytes are counted on the mbarrier of the pair's even CTA (`leader_bar_addr` is a
+// shared::cluster address). The data lands in the executing CTA's own shared memory; nothing is multicast.
+EP_DEVICE void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(ptx::smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(leader_bar_addr) : "memory");
+}
+
 }  // namespace deep_ep::tc

@@ -118,7 +118,8 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
             for (int c = lane; c < cta; c += 32) partial += __ldcg(&a.ws->cta_expert_count[c][e]);
             #pragma unroll
             for (int o = 16; o >= 1; o >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, o);
-            if (lane == 0) base_sm[e] = psum_sm[e] - a.num_unaligned[e] + partial;     // aligned region start + earlier rows
+            // aligned start of the expert's region (previous expert's end, rounded up) + rows of earlier CTAs
+            if (lane == 0) base_sm[e] = (e == 0 ? 0 : math::align(psum_sm[e - 1], a.expert_alignment)) + partial;
         }
         __syncthreads();
         for (int e = threadIdx.x; e < num_local_experts; e += blockDim.x) {

@@ -6,12 +6,17 @@ synchronisation is needed to launch). Three kernels modes cover a linear layer's
 weight gradient; `GroupedLinear` ties them into autograd and `grouped_swiglu_ffn` builds the SwiGLU FFN.
 Backend `'torch'` is the library-GEMM loop used as the comparison baseline and as the oracle in tests.
 """
+import os
 from typing import List, Optional
 
 import torch
 import torch.nn.functional as F
 
 from .._C_loader import _C
+
+# CTA-pair kernels (`tcgen05.mma.cta_group::2`, 256 x 256 tiles) are used whenever the shape allows; EP_GEMM_PAIRS=0
+# selects the single-CTA kernels everywhere.
+USE_PAIRS = os.environ.get('EP_GEMM_PAIRS', '1') == '1'
 
 MODE_FORWARD, MODE_DGRAD, MODE_WGRAD = 0, 1, 2
 EPILOGUE_STORE, EPILOGUE_SWIGLU, EPILOGUE_SWIGLU_KEEP = 0, 1, 2
@@ -28,11 +33,11 @@ def grouped_gemm_forward(x: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, c
     y = torch.empty((x.size(0), n_out), dtype=torch.bfloat16, device=x.device)
     if not swiglu:
         assert row_scale is None and not keep_preactivation
-        _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_STORE, num_sms, alignment)
+        _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_STORE, num_sms, alignment, None, None, USE_PAIRS)
         return y
     keep = torch.empty((x.size(0), w.size(1)), dtype=torch.bfloat16, device=x.device) if keep_preactivation else None
     _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_SWIGLU_KEEP if keep_preactivation else EPILOGUE_SWIGLU,
-                    num_sms, alignment, row_scale, keep)
+                    num_sms, alignment, row_scale, keep, USE_PAIRS)
     return (y, keep) if keep_preactivation else y
 
 
@@ -40,7 +45,7 @@ def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, co
                        num_sms: int = 0, alignment: int = 1) -> torch.Tensor:
     """`dx[rows_e] = dy[rows_e] @ w[e]` with `w [G, N, K]` read as stored (no transpose copy)."""
     dx = torch.empty((dy.size(0), w.size(2)), dtype=torch.bfloat16, device=dy.device)
-    _C.grouped_gemm(dy, w, dx, psum, count, MODE_DGRAD, EPILOGUE_STORE, num_sms, alignment)
+    _C.grouped_gemm(dy, w, dx, psum, count, MODE_DGRAD, EPILOGUE_STORE, num_sms, alignment, None, None, USE_PAIRS)
     return dx
 
 
@@ -91,7 +96,7 @@ def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, dw: torch.Tensor, psum
     """`dw[e] += dy[rows_e].T @ x[rows_e]` in fp32 (`dw [G, N, K]` fp32); with `accumulate=False` the result
     overwrites `dw` (experts without rows get zeros), which saves reading it. Padding rows of `dy` or `x` up to the
     next multiple of 64 rows must be zero."""
-    _C.grouped_gemm_wgrad(dy, x, dw, psum, count, num_sms, accumulate)
+    _C.grouped_gemm_wgrad(dy, x, dw, psum, count, num_sms, accumulate, USE_PAIRS)
     return dw
 
 
@@ -140,14 +145,19 @@ class GroupedLinear(torch.autograd.Function):
 
 
 def _torch_ffn(x, w_gate_up, w_down, psum, count):
-    out = torch.zeros((x.size(0), w_down.size(1)), dtype=x.dtype, device=x.device)
+    pieces, cursor = [], 0
+    w1s, w2s = w_gate_up.unbind(0), w_down.unbind(0)
     for e, (start, c) in enumerate(_ranges(psum, count)):
         if c == 0:
             continue
-        rows = x[start:start + c]
-        g, u = F.linear(rows, w_gate_up[e]).chunk(2, dim=-1)
-        out[start:start + c] = F.linear(F.silu(g) * u, w_down[e])
-    return out
+        if start > cursor:
+            pieces.append(x.new_zeros((start - cursor, w_down.size(1))))
+        g, u = F.linear(x[start:start + c], w1s[e]).chunk(2, dim=-1)
+        pieces.append(F.linear(F.silu(g) * u, w2s[e]))
+        cursor = start + c
+    if cursor < x.size(0):
+        pieces.append(x.new_zeros((x.size(0) - cursor, w_down.size(1))))
+    return torch.cat(pieces)
 
 
 def grouped_swiglu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, psum: torch.Tensor,

@@ -18,9 +18,17 @@ CASES = [
 ]
 
 
+@pytest.fixture(params=[False, True], ids=['single_cta', 'cta_pairs'])
+def pairs(request):
+    from deep_ep.ops import grouped_gemm as gg
+    saved, gg.USE_PAIRS = gg.USE_PAIRS, request.param
+    yield request.param
+    gg.USE_PAIRS = saved
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize('counts,alignment,k,n', CASES)
-def test_grouped_forward_dgrad_wgrad(counts, alignment, k, n):
+def test_grouped_forward_dgrad_wgrad(counts, alignment, k, n, pairs):
     from deep_ep.ops import grouped_gemm as gg
     torch.manual_seed(0)
     dev = torch.device('cuda')
@@ -64,7 +72,7 @@ def test_grouped_forward_dgrad_wgrad(counts, alignment, k, n):
 
 
 @pytest.mark.gpu
-def test_grouped_swiglu_ffn_matches_torch():
+def test_grouped_swiglu_ffn_matches_torch(pairs):
     from deep_ep.ops import grouped_gemm as gg
     torch.manual_seed(1)
     dev = torch.device('cuda')
@@ -100,7 +108,7 @@ def test_grouped_swiglu_ffn_matches_torch():
 
 
 @pytest.mark.gpu
-def test_fused_ffn_row_scale_and_zero_padding():
+def test_fused_ffn_row_scale_and_zero_padding(pairs):
     """The fused FFN node: routing weights applied in the GEMM1 epilogue, padding rows exactly zero, gradients right."""
     from deep_ep.ops import grouped_gemm as gg
     torch.manual_seed(2)
