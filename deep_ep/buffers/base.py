@@ -1,9 +1,12 @@
 """Lifecycle shared by all communication buffers (reference: `deep_ep/buffers/base.py:4-27`)."""
+import os
 from abc import ABC, abstractmethod
 from typing import List
 
 import torch
 import torch.distributed as dist
+
+from .._C_loader import _C
 
 
 class BufferBase(ABC):
@@ -41,7 +44,15 @@ def connect_peers(context, group: dist.ProcessGroup) -> None:
     if group.size() == 1 or context.peers_ready:
         return
     handles: List[bytes] = [b''] * group.size()
-    dist.all_gather_object(handles, context.get_local_handle(), group)
+    device = torch.cuda.current_device()
+    exchanged = [None] * group.size()
+    dist.all_gather_object(exchanged, (context.get_local_handle(), device, os.uname().nodename), group)
+    # one NVLink domain: every peer must be another GPU of this node that this GPU can address directly
+    for rank, (_, peer_device, node) in enumerate(exchanged):
+        assert node == os.uname().nodename, f'rank {rank} runs on another node ({node}); only one NVLink domain is supported'
+        if peer_device != device:
+            assert _C.check_peer_access(device, peer_device), f'GPU {device} cannot access GPU {peer_device} (rank {rank}) directly'
+    handles = [h for h, _, _ in exchanged]
     context.set_peer_handles(handles)
 
 

@@ -116,12 +116,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int it = 0;       // k-block counter over all tiles of this CTA (ring position)
+            // ring position: stage index and phase bit, advanced without divisions (this loop is one thread's
+            // critical path: it must stay shorter than the 512 cycles a K block occupies the tensor core)
+            int s = 0;
+            uint32_t phase = 0;
             for (int tile = blockIdx.x; tile < num_tiles and not error_flag; tile += gridDim.x) {
                 const Tile t = locate_tile(a, tile_prefix, tile);
-                for (int kb = 0; kb < t.num_k_blocks; ++kb, ++it) {
-                    const int s = it % S;
-                    if (not ptx::mbarrier_wait(&empty_bar[s], ((it / S) & 1) ^ 1)) { error_flag = 1; break; }
+                for (int kb = 0; kb < t.num_k_blocks; ++kb, s = (s + 1 == S ? 0 : s + 1), phase ^= (s == 0)) {
+                    if (not ptx::mbarrier_wait(&empty_bar[s], phase ^ 1)) { error_flag = 1; break; }
                     ptx::mbarrier_arrive_expect_tx(&full_bar[s], a_bytes + b_bytes);
                     uint8_t* sa = smem_a + size_t(s) * a_bytes;
                     uint8_t* sb = smem_b + size_t(s) * b_bytes;
@@ -161,25 +163,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // descriptor strides: K-major -> 8-row groups 1024 B apart; MN-major -> K atoms 1024 B apart, 64-wide blocks 8192 B apart
             const uint32_t a_lead = a_mn ? 8192 : 16, b_lead = b_mn ? 8192 : 16;
             const uint32_t a_kstep = a_mn ? 2048 : 32, b_kstep = b_mn ? 2048 : 32;     // bytes per K = 16
-            int it = 0, local_tile = 0;
+            // descriptors of stage 0; other stages and K steps differ only in the 14-bit address field (units of 16 bytes)
+            const uint64_t desc_a0 = tc::make_smem_desc(smem_a, a_lead, 1024), desc_b0 = tc::make_smem_desc(smem_b, b_lead, 1024);
+            const uint32_t a_stage_step = a_bytes >> 4, b_stage_step = b_bytes >> 4;
+            const uint32_t a_k = a_kstep >> 4, b_k = b_kstep >> 4;
+            int s = 0, local_tile = 0;
+            uint32_t phase = 0;
             for (int tile = blockIdx.x; tile < num_tiles and not error_flag; tile += gridDim.x, ++local_tile) {
                 const Tile t = locate_tile(a, tile_prefix, tile);
                 const int acc = local_tile & 1, use = local_tile >> 1;
                 if (not ptx::mbarrier_wait(&tmem_empty_bar[acc], (use & 1) ^ 1)) { error_flag = 1; break; }
                 tc::fence_after_thread_sync();
                 const uint32_t tmem_d = tmem_base + acc * 256;
-                for (int kb = 0; kb < t.num_k_blocks; ++kb, ++it) {
-                    const int s = it % S;
-                    if (not ptx::mbarrier_wait(&full_bar[s], (it / S) & 1)) { error_flag = 1; break; }
+                for (int kb = 0; kb < t.num_k_blocks; ++kb, s = (s + 1 == S ? 0 : s + 1), phase ^= (s == 0)) {
+                    if (not ptx::mbarrier_wait(&full_bar[s], phase)) { error_flag = 1; break; }
                     tc::fence_after_thread_sync();
-                    const uint8_t* sa = smem_a + size_t(s) * a_bytes;
-                    const uint8_t* sb = smem_b + size_t(s) * b_bytes;
+                    const uint64_t da = desc_a0 + uint64_t(s * a_stage_step), db = desc_b0 + uint64_t(s * b_stage_step);
                     #pragma unroll
-                    for (int k = 0; k < kGemmBlockK / 16; ++k) {
-                        const uint64_t da = tc::make_smem_desc(sa + k * a_kstep, a_lead, 1024);
-                        const uint64_t db = tc::make_smem_desc(sb + k * b_kstep, b_lead, 1024);
-                        tc::mma_f16(tmem_d, da, db, idesc, kb > 0 or k > 0);
-                    }
+                    for (int k = 0; k < kGemmBlockK / 16; ++k)
+                        tc::mma_f16(tmem_d, da + uint64_t(k * a_k), db + uint64_t(k * b_k), idesc, kb > 0 or k > 0);
                     tc::commit(&empty_bar[s]);          // stage is free once these MMAs have read it
                 }
                 if (t.num_k_blocks > 0) tc::commit(&tmem_full_bar[acc]);        // accumulator complete

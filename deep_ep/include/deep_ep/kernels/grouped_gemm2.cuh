@@ -112,12 +112,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
         if (lane == 0) {
-            int it = 0;
+            int s = 0;
+            uint32_t phase = 0;
             for (int tile = pair; tile < num_tiles and not error_flag; tile += num_pairs) {
                 const Tile t = locate_tile(a, tile_prefix, tile);
-                for (int kb = 0; kb < t.num_k_blocks; ++kb, ++it) {
-                    const int s = it % S;
-                    if (not ptx::mbarrier_wait(&empty_bar[s], ((it / S) & 1) ^ 1)) { error_flag = 1; break; }
+                for (int kb = 0; kb < t.num_k_blocks; ++kb, s = (s + 1 == S ? 0 : s + 1), phase ^= (s == 0)) {
+                    if (not ptx::mbarrier_wait(&empty_bar[s], phase ^ 1)) { error_flag = 1; break; }
                     // the bytes of both CTAs are counted on the even CTA's barrier
                     const uint32_t bar = tc::map_to_cta(&full_bar[s], 0);
                     if (leader) ptx::mbarrier_arrive_expect_tx(&full_bar[s], 4 * kHalfBytes);
@@ -156,27 +156,24 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const uint32_t idesc = tc::make_idesc(tc::kFormatBF16, kPairM, kPairN, a_mn, b_mn);
             const uint32_t a_lead = a_mn ? 8192 : 16, b_lead = b_mn ? 8192 : 16;
             const uint32_t a_kstep = a_mn ? 2048 : 32, b_kstep = b_mn ? 2048 : 32;
-            int it = 0, local_tile = 0;
+            const uint64_t desc_a0 = tc::make_smem_desc(smem_a, a_lead, 1024), desc_b0 = tc::make_smem_desc(smem_b, b_lead, 1024);
+            const uint32_t stage_step = kHalfBytes >> 4, a_k = a_kstep >> 4, b_k = b_kstep >> 4;
+            int s = 0, local_tile = 0;
+            uint32_t phase = 0;
             for (int tile = pair; tile < num_tiles and not error_flag; tile += num_pairs, ++local_tile) {
                 const Tile t = locate_tile(a, tile_prefix, tile);
                 const int acc = local_tile & 1, use = local_tile >> 1;
                 if (not ptx::mbarrier_wait(&tmem_empty_bar[acc], (use & 1) ^ 1)) { error_flag = 1; break; }
                 tc::fence_after_thread_sync();
                 const uint32_t tmem_d = tmem_base + acc * 256;
-                for (int kb = 0; kb < t.num_k_blocks; ++kb, ++it) {
-                    const int s = it % S;
-                    if (not ptx::mbarrier_wait(&full_bar[s], (it / S) & 1)) { error_flag = 1; break; }
+                for (int kb = 0; kb < t.num_k_blocks; ++kb, s = (s + 1 == S ? 0 : s + 1), phase ^= (s == 0)) {
+                    if (not ptx::mbarrier_wait(&full_bar[s], phase)) { error_flag = 1; break; }
                     tc::fence_after_thread_sync();
-                    const uint8_t* sa = smem_a + size_t(s) * kHalfBytes;
-                    const uint8_t* sb = smem_b + size_t(s) * kHalfBytes;
+                    const uint64_t da = desc_a0 + uint64_t(s * stage_step), db = desc_b0 + uint64_t(s * stage_step);
                     #pragma unroll
-                    for (int k = 0; k < kGemmBlockK / 16; ++k) {
-                        const uint64_t da = tc::make_smem_desc(sa + k * a_kstep, a_lead, 1024);
-                        const uint64_t db = tc::make_smem_desc(sb + k * b_kstep, b_lead, 1024);
-                        tc::mma_f16_pair(tmem_d, da, db, idesc, kb > 0 or k > 0);
-                    }
-                    // the stage is free in both CTAs once these MMAs have read it
-                    tc::commit_pair(&empty_bar[s]);
+                    for (int k = 0; k < kGemmBlockK / 16; ++k)
+                        tc::mma_f16_pair(tmem_d, da + uint64_t(k * a_k), db + uint64_t(k * b_k), idesc, kb > 0 or k > 0);
+                    tc::commit_pair(&empty_bar[s]);      // the stage is free in both CTAs once these MMAs have read it
                 }
                 if (t.num_k_blocks > 0) {
                     tc::commit_pair(&tmem_full_bar[acc]);

@@ -14,11 +14,18 @@ import torch.nn.functional as F
 
 from .._C_loader import _C
 
-# CTA-pair kernels (`tcgen05.mma.cta_group::2`, 256 x 256 tiles) are used whenever the shape allows; EP_GEMM_PAIRS=0
-# selects the single-CTA kernels everywhere.
-USE_PAIRS = os.environ.get('EP_GEMM_PAIRS', '1') == '1'
-
 MODE_FORWARD, MODE_DGRAD, MODE_WGRAD = 0, 1, 2
+
+# Which kernel runs a GEMM: CTA pairs (`tcgen05.mma.cta_group::2`, 256 x 256 tiles) or one CTA per 128 x 256 tile.
+# Measured on B200: the single-CTA kernel is ahead for the forward GEMMs (K-major weights, one TMA box per operand),
+# the pair kernel for data and weight gradients (MN-major operands, where a pair halves the TMA boxes per CTA).
+# EP_GEMM_PAIRS=1 / 0 forces one of them everywhere; the default 'auto' picks per mode.
+USE_PAIRS = {'0': False, '1': True}.get(os.environ.get('EP_GEMM_PAIRS', 'auto'), None)
+
+
+def _pairs(mode: int) -> bool:
+    return (mode != MODE_FORWARD) if USE_PAIRS is None else USE_PAIRS
+
 EPILOGUE_STORE, EPILOGUE_SWIGLU, EPILOGUE_SWIGLU_KEEP = 0, 1, 2
 
 
@@ -33,11 +40,11 @@ def grouped_gemm_forward(x: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, c
     y = torch.empty((x.size(0), n_out), dtype=torch.bfloat16, device=x.device)
     if not swiglu:
         assert row_scale is None and not keep_preactivation
-        _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_STORE, num_sms, alignment, None, None, USE_PAIRS)
+        _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_STORE, num_sms, alignment, None, None, _pairs(MODE_FORWARD))
         return y
     keep = torch.empty((x.size(0), w.size(1)), dtype=torch.bfloat16, device=x.device) if keep_preactivation else None
     _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_SWIGLU_KEEP if keep_preactivation else EPILOGUE_SWIGLU,
-                    num_sms, alignment, row_scale, keep, USE_PAIRS)
+                    num_sms, alignment, row_scale, keep, _pairs(MODE_FORWARD))
     return (y, keep) if keep_preactivation else y
 
 
@@ -45,7 +52,7 @@ def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, co
                        num_sms: int = 0, alignment: int = 1) -> torch.Tensor:
     """`dx[rows_e] = dy[rows_e] @ w[e]` with `w [G, N, K]` read as stored (no transpose copy)."""
     dx = torch.empty((dy.size(0), w.size(2)), dtype=torch.bfloat16, device=dy.device)
-    _C.grouped_gemm(dy, w, dx, psum, count, MODE_DGRAD, EPILOGUE_STORE, num_sms, alignment, None, None, USE_PAIRS)
+    _C.grouped_gemm(dy, w, dx, psum, count, MODE_DGRAD, EPILOGUE_STORE, num_sms, alignment, None, None, _pairs(MODE_DGRAD))
     return dx
 
 
@@ -96,7 +103,7 @@ def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, dw: torch.Tensor, psum
     """`dw[e] += dy[rows_e].T @ x[rows_e]` in fp32 (`dw [G, N, K]` fp32); with `accumulate=False` the result
     overwrites `dw` (experts without rows get zeros), which saves reading it. Padding rows of `dy` or `x` up to the
     next multiple of 64 rows must be zero."""
-    _C.grouped_gemm_wgrad(dy, x, dw, psum, count, num_sms, accumulate, USE_PAIRS)
+    _C.grouped_gemm_wgrad(dy, x, dw, psum, count, num_sms, accumulate, _pairs(MODE_WGRAD))
     return dw
 
 
