@@ -69,6 +69,7 @@ public:
     std::shared_ptr<comm::Context> context;
     int64_t num_bytes, num_lb_bytes;
     torch::Tensor lb_storage;
+    torch::Tensor gsge_constant;      // all -1, shape of the last dispatch's `dst_gsge_idx`
 
     EPBuffer(int rank_idx, int num_ranks, const std::string& comm_name, int64_t num_bytes, int64_t num_lb_bytes,
              bool use_huge1g_page, int num_cpu_timeout_secs, int num_gpu_timeout_secs, bool explicitly_destroy)
@@ -210,8 +211,11 @@ public:
         auto num_unaligned = cached_mode ? *cached_num_unaligned_recv_tokens_per_expert : torch::empty({num_local_experts}, int_options);
         auto dst_buffer_slot_idx = cached_mode ? *cached_dst_buffer_slot_idx : torch::empty({num_tokens, num_topk}, int_options);
         // no scatter-gather bookkeeping exists on NVLink; the tensor is kept (all -1) for API shape
-        auto dst_gsge_idx = cached_mode and cached_dst_gsge_idx.has_value() ? *cached_dst_gsge_idx
-                                                                              : torch::full({num_tokens, num_topk}, -1, int_options);
+        // (the tensor is never written, so one instance per shape is shared by all handles)
+        if (not cached_mode and (not gsge_constant.defined() or gsge_constant.size(0) != num_tokens or
+                                 gsge_constant.size(1) != num_topk or gsge_constant.device() != device))
+            gsge_constant = torch::full({num_tokens, num_topk}, -1, int_options);
+        auto dst_gsge_idx = cached_mode and cached_dst_gsge_idx.has_value() ? *cached_dst_gsge_idx : gsge_constant;
         if (cached_mode) {
             EP_HOST_ASSERT(dst_buffer_slot_idx.size(0) == num_tokens and dst_buffer_slot_idx.size(1) == num_topk and
                            dst_buffer_slot_idx.is_contiguous() and dst_buffer_slot_idx.scalar_type() == torch::kInt32);

@@ -187,7 +187,9 @@ def _all_gather_worker(rank, world):
         outs = handle.wait()
         torch.cuda.synchronize()
         for i, o in enumerate(outs):
-            assert torch.equal(o.view(size, -1)[:, 0].float(), torch.arange(size, device='cuda').float() * 100 + i)
+            # (values beyond 256 are not exact in bf16: round the expectation the same way)
+            expect = (torch.arange(size, device='cuda').float() * 100 + i).to(torch.bfloat16).float()
+            assert torch.equal(o.view(size, -1)[:, 0].float(), expect)
         bucket.barrier(**kw)
     for c in bucket.contexts:
         assert c.status_code() == 0
