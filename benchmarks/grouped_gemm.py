@@ -38,6 +38,8 @@ def main():
     p.add_argument('--inter', type=int, default=2048)
     p.add_argument('--iters', type=int, default=10)
     p.add_argument('--skip-torch', action='store_true')
+    p.add_argument('--skip-fp8', action='store_true')
+    p.add_argument('--only', type=str, default='', help='comma-separated case names to run')
     args = p.parse_args()
     dev = torch.device('cuda')
     torch.manual_seed(0)
@@ -73,9 +75,24 @@ def main():
         'gemm1_wgrad': (lambda: gg.grouped_gemm_wgrad(dy1, x, dw1, psum, count),
                         lambda: [torch.mm(dy1[s:s + c].t(), x[s:s + c]) for e, (s, c) in enumerate(ranges)], 2 * useful * h * 2 * i),
     }
+    if not args.skip_fp8:
+        # FP8 forward path: e4m3 rows with 1 x 128 scales (what the FP8 dispatch delivers), weights with 128 x 128 scales
+        from deep_ep.ops.quant import per_token_cast_to_fp8
+        x8, x8_sf = per_token_cast_to_fp8(x)
+        a8, a8_sf = per_token_cast_to_fp8(act)
+        w1_8, w1_sf = gg.per_block_cast_to_fp8(w1)
+        w2_8, w2_sf = gg.per_block_cast_to_fp8(w2)
+        cases.update({
+            'fp8_gemm1_forward': (lambda: gg.grouped_gemm_fp8_forward(x8, x8_sf, w1_8, w1_sf, psum, count), None, 2 * useful * h * 2 * i),
+            'fp8_gemm1_forward_swiglu_quant': (lambda: gg.grouped_gemm_fp8_forward(x8, x8_sf, w1_8, w1_sf, psum, count, swiglu=True,
+                                                                                   quantize_output=True), None, 2 * useful * h * 2 * i),
+            'fp8_gemm2_forward': (lambda: gg.grouped_gemm_fp8_forward(a8, a8_sf, w2_8, w2_sf, psum, count), None, 2 * useful * h * i),
+        })
     out = {'bench': 'grouped_gemm', 'experts': g, 'rows_total': rows, 'rows_useful': useful, 'hidden': h, 'inter': i,
            'peak_tflops_measured': peak, 'results': {}}
     for name, (ours, ref, flops) in cases.items():
+        if args.only and name not in args.only.split(','):
+            continue
         t_min, t_avg = bench(ours, args.iters)
         entry = {'ours_ms': round(t_avg, 4), 'ours_tflops': round(flops / (t_avg * 1e-3) / 1e12, 1),
                  'ours_frac_of_measured_peak': round(flops / (t_avg * 1e-3) / 1e12 / peak, 3)}

@@ -102,6 +102,24 @@ def time_layer(layer, x, steps, warmup):
     return t.item()
 
 
+def time_forward(fn, x, steps, warmup):
+    """Inference forward only (no autograd), device-timed, maximum over ranks."""
+    with torch.no_grad():
+        for _ in range(warmup):
+            fn(x)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for a, b in ev:
+            a.record()
+            fn(x)
+            b.record()
+        torch.cuda.synchronize()
+    t = torch.tensor([sum(a.elapsed_time(b) for a, b in ev) / steps], device=x.device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
 def main():
     p = argparse.ArgumentParser()
     p.add_argument('--num-tokens', type=int, default=4096)
@@ -112,6 +130,8 @@ def main():
     p.add_argument('--steps', type=int, default=10)
     p.add_argument('--warmup', type=int, default=3)
     p.add_argument('--skip-baseline', action='store_true')
+    p.add_argument('--forward-fp8', action='store_true',
+                   help='also time the inference forward: BF16 path against the FP8 path (e4m3 dispatch + block-scaled FP8 GEMMs)')
     args = p.parse_args()
     rank, world = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1))
     local_rank = int(os.environ.get('LOCAL_RANK', 0))
@@ -143,6 +163,13 @@ def main():
     flops = 3 * 2 * rows * args.hidden * args.intermediate * 3
     result['ours_tflops_per_gpu'] = round(flops / (result['ours_ms'] * 1e-3) / 1e12, 1)
     result['tokens_per_s_total'] = round(args.num_tokens * world / (result['ours_ms'] * 1e-3))
+    if args.forward_fp8:
+        ours.quantize_weights()
+        with torch.no_grad():
+            y16, y8 = ours(x), ours.forward_fp8(x)
+        result['fp8_forward_rel_diff_vs_bf16'] = round(((y8.float() - y16.float()).norm() / y16.float().norm()).item(), 5)
+        result['forward_bf16_ms'] = round(time_forward(ours, x, args.steps, args.warmup), 3)
+        result['forward_fp8_ms'] = round(time_forward(ours.forward_fp8, x, args.steps, args.warmup), 3)
     if 'baseline_ms' in result:
         result['speedup'] = round(result['baseline_ms'] / result['ours_ms'], 3)
     if rank == 0:

@@ -45,6 +45,11 @@ void dispatch_layout(const kernels::LayoutArgs& args, int num_sms, cudaStream_t 
 void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, int64_t a_cols,
                   const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream, bool use_pairs = false);
 
+// Grouped FP8 (e4m3) forward GEMM with fp32 block scales (1 x 128 for `a`, 128 x 128 for `b`), see grouped_gemm_fp8.cuh.
+// `a` is [a_rows, args.k] bytes, `b` is [b_rows = G * args.n, args.k] bytes.
+void grouped_gemm_fp8(kernels::GroupedGemmFp8Args args, const void* a, int64_t a_rows, const void* b, int64_t b_rows,
+                      int num_sms, cudaStream_t stream);
+
 // dh = d(silu(gate) * up * row_scale) / d[gate | up] for bf16 rows; `inter` must be a multiple of 8.
 void swiglu_backward(const void* h, const void* dact, const float* row_scale, void* dh, int64_t rows, int inter,
                      cudaStream_t stream);

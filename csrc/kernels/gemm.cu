@@ -5,6 +5,7 @@
 #include <deep_ep/common/exception.hpp>
 #include <deep_ep/kernels/grouped_gemm.cuh>
 #include <deep_ep/kernels/grouped_gemm2.cuh>
+#include <deep_ep/kernels/grouped_gemm_fp8.cuh>
 
 #include "../runtime/driver.hpp"
 #include "api.hpp"
@@ -27,7 +28,50 @@ CUtensorMap make_map_2d(const void* base, int64_t rows, int64_t cols, int box_co
     return map;
 }
 
+// 2-D byte tensor map (e4m3 operands) over a row-major [rows, cols] matrix with a {128, box_rows} box.
+CUtensorMap make_map_2d_u8(const void* base, int64_t rows, int64_t cols, int box_rows) {
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols)};
+    const cuuint32_t box[2] = {128, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    EP_HOST_ASSERT(reinterpret_cast<uintptr_t>(base) % 16 == 0 and cols % 16 == 0);
+    DRV_CHECK(driver::cuTensorMapEncodeTiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+                                               box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+    return map;
+}
+
 }  // namespace
+
+void grouped_gemm_fp8(kernels::GroupedGemmFp8Args args, const void* a, int64_t a_rows, const void* b, int64_t b_rows,
+                      int num_sms, cudaStream_t stream) {
+    using namespace kernels;
+    EP_HOST_ASSERT(args.num_groups > 0 and args.num_groups <= kMaxLocalExperts);
+    EP_HOST_ASSERT_MSG(args.k > 0 and args.k % kFp8BlockK == 0, "K must be a multiple of 128");
+    EP_HOST_ASSERT(a_rows > 0);
+    CUDA_CHECK(cudaFree(nullptr));       // the driver call below needs a current context
+    if (args.epilogue != kEpilogueStore) {
+        EP_HOST_ASSERT_MSG(args.epilogue == kEpilogueSwiGLU and args.n % 256 == 0, "SwiGLU needs N (gate + up) to be a multiple of 256");
+        args.n_out = args.n / 2;
+    } else {
+        EP_HOST_ASSERT_MSG(args.n % kFp8BlockN == 0, "N must be a multiple of 256");
+        args.n_out = args.n;
+    }
+    args.total_rows = static_cast<int>(a_rows);
+    int device = 0, sms = 0;
+    CUDA_CHECK(cudaGetDevice(&device));
+    CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const int grid = num_sms > 0 ? std::min(num_sms, sms) : sms;
+    const int64_t budget = 200 * 1024;
+    args.num_stages = static_cast<int>(std::min<int64_t>(kGemmMaxStages, (budget - 1024) / ((kGemmBlockM + kFp8BlockN) * kFp8BlockK)));
+    const CUtensorMap map_a = make_map_2d_u8(a, a_rows, args.k, 128);
+    const CUtensorMap map_b = make_map_2d_u8(b, b_rows, args.k, 128);
+    const auto smem = grouped_gemm_fp8_smem_bytes(args.num_stages);
+    CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    grouped_gemm_fp8_kernel<<<grid, kFp8Threads, smem, stream>>>(map_a, map_b, args);
+    CUDA_CHECK(cudaGetLastError());
+}
 
 void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, int64_t a_cols,
                   const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream, bool use_pairs) {

@@ -104,6 +104,47 @@ void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::T
                          use_pairs);
 }
 
+// d = (a * a_sf) x (b * b_sf)^T per expert with e4m3 operands: a [rows, k] + a_sf [rows, k / 128], b [g, n, k] + b_sf [g, n / 128, k / 128].
+// epilogue 0: d bf16 [rows, n]. epilogue 1 (SwiGLU over [gate | up] = n columns): d bf16 [rows, n / 2], or, when `d_sf` is
+// given, d e4m3 [rows, n / 2] with d_sf fp32 [rows, n / 256] (re-quantised for the next GEMM).
+void grouped_gemm_fp8(const torch::Tensor& a, const torch::Tensor& a_sf, const torch::Tensor& b, const torch::Tensor& b_sf,
+                      const torch::Tensor& d, const torch::Tensor& psum, const torch::Tensor& count, int epilogue, int num_sms,
+                      int alignment, const std::optional<torch::Tensor>& row_scale, const std::optional<torch::Tensor>& d_sf) {
+    using namespace kernels;
+    for (const auto* t : {&a, &a_sf, &b, &b_sf, &d, &psum, &count}) EP_HOST_ASSERT(t->is_cuda() and t->is_contiguous());
+    EP_HOST_ASSERT(a.scalar_type() == torch::kFloat8_e4m3fn and b.scalar_type() == torch::kFloat8_e4m3fn and a.dim() == 2 and b.dim() == 3);
+    EP_HOST_ASSERT(a_sf.scalar_type() == torch::kFloat32 and b_sf.scalar_type() == torch::kFloat32);
+    EP_HOST_ASSERT(psum.scalar_type() == torch::kInt32 and count.scalar_type() == torch::kInt32 and psum.numel() == count.numel());
+    EP_HOST_ASSERT(epilogue == kEpilogueStore or epilogue == kEpilogueSwiGLU);
+    const int64_t rows = a.size(0), k = a.size(1), g = psum.numel(), n = b.size(1);
+    EP_HOST_ASSERT(b.size(0) == g and b.size(2) == k and k % kFp8BlockK == 0 and n % 128 == 0);
+    EP_HOST_ASSERT(a_sf.dim() == 2 and a_sf.size(0) == rows and a_sf.size(1) == k / 128);
+    EP_HOST_ASSERT(b_sf.dim() == 3 and b_sf.size(0) == g and b_sf.size(1) == n / 128 and b_sf.size(2) == k / 128);
+    if (rows == 0) return;
+    GroupedGemmFp8Args args = {};
+    args.epilogue = epilogue, args.num_groups = static_cast<int>(g);
+    args.psum = psum.data_ptr<int>(), args.count = count.data_ptr<int>();
+    args.n = static_cast<int>(n), args.k = static_cast<int>(k), args.alignment = alignment;
+    args.sf_a = a_sf.data_ptr<float>(), args.sf_b = b_sf.data_ptr<float>();
+    args.d = d.data_ptr(), args.status = nullptr;
+    const int64_t n_out = epilogue == kEpilogueStore ? n : n / 2;
+    EP_HOST_ASSERT(d.dim() == 2 and d.size(0) == rows and d.size(1) == n_out);
+    if (d_sf.has_value()) {
+        EP_HOST_ASSERT(epilogue == kEpilogueSwiGLU and d.scalar_type() == torch::kFloat8_e4m3fn);
+        EP_HOST_ASSERT(d_sf->is_cuda() and d_sf->is_contiguous() and d_sf->scalar_type() == torch::kFloat32 and d_sf->dim() == 2 and
+                       d_sf->size(0) == rows and d_sf->size(1) == n_out / 128);
+        args.out_fp8 = 1, args.d_sf = d_sf->data_ptr<float>();
+    } else {
+        EP_HOST_ASSERT(d.scalar_type() == torch::kBFloat16);
+    }
+    if (row_scale.has_value()) {
+        EP_HOST_ASSERT(epilogue == kEpilogueSwiGLU and row_scale->is_cuda() and row_scale->is_contiguous() and
+                       row_scale->scalar_type() == torch::kFloat32 and row_scale->numel() == rows);
+        args.row_scale = row_scale->data_ptr<float>();
+    }
+    launch::grouped_gemm_fp8(args, a.data_ptr(), rows, b.data_ptr(), g * n, num_sms, c10::cuda::getCurrentCUDAStream());
+}
+
 torch::Tensor swiglu_backward(const torch::Tensor& h, const torch::Tensor& dact, const std::optional<torch::Tensor>& row_scale) {
     EP_HOST_ASSERT(h.is_cuda() and h.is_contiguous() and h.scalar_type() == torch::kBFloat16 and h.dim() == 2);
     EP_HOST_ASSERT(dact.is_cuda() and dact.is_contiguous() and dact.scalar_type() == torch::kBFloat16 and dact.dim() == 2);
@@ -205,6 +246,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
           py::arg("mode"), py::arg("epilogue") = 0, py::arg("num_sms") = 0, py::arg("alignment") = 1,
           py::arg("row_scale") = py::none(), py::arg("keep") = py::none(), py::arg("use_pairs") = false);
+    m.def("grouped_gemm_fp8", &grouped_gemm_fp8, py::arg("a"), py::arg("a_sf"), py::arg("b"), py::arg("b_sf"), py::arg("d"),
+          py::arg("psum"), py::arg("count"), py::arg("epilogue") = 0, py::arg("num_sms") = 0, py::arg("alignment") = 1,
+          py::arg("row_scale") = py::none(), py::arg("d_sf") = py::none());
     m.def("swiglu_backward", &swiglu_backward, py::arg("h"), py::arg("dact"), py::arg("row_scale") = py::none());
     m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
           py::arg("num_sms") = 0, py::arg("accumulate") = true, py::arg("use_pairs") = false);

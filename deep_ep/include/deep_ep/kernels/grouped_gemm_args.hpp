@@ -39,4 +39,34 @@ EP_HOST_DEVICE int64_t grouped_gemm_smem_bytes(int block_n, int num_stages) {
     return int64_t(num_stages) * (kGemmBlockM + block_n) * kGemmBlockK * 2 + 1024;
 }
 
+// ---------------------------------------------------------------- FP8 (e4m3) block-scaled forward GEMM
+// A: e4m3 [rows, k] with one fp32 scale per row and 128 columns (the format the FP8 dispatch delivers);
+// B: e4m3 [G, n, k] with one fp32 scale per 128 x 128 block. K blocks of 128 are multiplied on the tensor cores
+// and promoted into fp32 registers with `sf_a[row, kb] * sf_b[g, n / 128, kb]`.
+constexpr int kFp8BlockK = 128;        // 128 e4m3 = one 128-byte swizzle row = one scale block
+constexpr int kFp8BlockN = 256;        // accumulator columns per tile
+constexpr int kFp8Threads = 320;       // producer warp, MMA warp, eight promotion/epilogue warps
+
+struct GroupedGemmFp8Args {
+    int epilogue;             // kEpilogueStore: d = bf16 [rows, n]; kEpilogueSwiGLU: d = silu(gate) * up (* row_scale), [rows, n / 2]
+    int out_fp8;              // SwiGLU only: 1 = d is e4m3 [rows, n / 2] and d_sf receives fp32 [rows, n / 256] scales
+    int num_groups;
+    const int* psum;          // [G] end (exclusive) of each expert's rows; start = psum - count
+    const int* count;         // [G] exact rows per expert
+    int total_rows;           // rows of A (scale reads are clamped to it)
+    int n, k, n_out;
+    int num_stages;
+    const float* sf_a;        // [rows, k / 128]
+    const float* sf_b;        // [G, n / 128, k / 128]
+    void* d;
+    float* d_sf;
+    const float* row_scale;   // optional fp32 [rows] factor applied by the SwiGLU epilogue
+    int alignment;            // rows in [count, align(count)) of a tile are written as zeros
+    int* status;              // set to 1 if a bounded wait ran out (may be nullptr)
+};
+
+EP_HOST_DEVICE int64_t grouped_gemm_fp8_smem_bytes(int num_stages) {
+    return int64_t(num_stages) * (kGemmBlockM + kFp8BlockN) * kFp8BlockK + 1024;
+}
+
 }  // namespace deep_ep::kernels

@@ -24,7 +24,8 @@ class MoEConfig:
     num_shared_experts: int = 0
     num_max_tokens_per_rank: int = 4096
     expert_alignment: int = 128
-    fp8_dispatch: bool = False          # quantise to e4m3 (1x128 scales) inside the dispatch kernel
+    fp8_dispatch: bool = False          # inference (`forward_fp8`): e4m3 dispatch (1x128 scales, quantised inside the
+                                        # dispatch kernel) feeding block-scaled FP8 expert GEMMs
     expert_backend: str = 'grouped'     # 'grouped': hand-written grouped GEMM kernels, 'torch': per-expert torch.mm
     num_sms: int = 0
     init_std: float = 0.02
@@ -109,6 +110,38 @@ class MoELayer(nn.Module):
         return grouped_swiglu_ffn(recv_x, self.w_gate_up, self.w_down, handle.psum_num_recv_tokens_per_expert,
                                   handle.num_unaligned_recv_tokens_per_expert, handle.num_recv_tokens_per_expert_list,
                                   self.config.expert_alignment, backend=self.config.expert_backend, row_scale=recv_w)
+
+    # ------------------------------------------------------------------------------------------ FP8 inference
+    def quantize_weights(self) -> None:
+        """Store the routed experts' weights as e4m3 with one fp32 scale per 128 x 128 block (used by `forward_fp8`)."""
+        from ..ops.grouped_gemm import per_block_cast_to_fp8
+        with torch.no_grad():
+            self._w1_fp8, self._w1_sf = per_block_cast_to_fp8(self.w_gate_up)
+            self._w2_fp8, self._w2_sf = per_block_cast_to_fp8(self.w_down)
+
+    @torch.no_grad()
+    def forward_fp8(self, x: torch.Tensor) -> torch.Tensor:
+        """Forward pass for inference with FP8 on the wire and on the tensor cores: the dispatch kernel quantises the
+        bf16 tokens to e4m3 (fp32 1 x 128 scales), GEMM1 consumes the received rows as they are and re-quantises the
+        SwiGLU output in its epilogue, GEMM2 writes bf16 for the combine. Needs `quantize_weights()` once."""
+        from ..ops.grouped_gemm import grouped_swiglu_ffn_fp8
+        cfg = self.config
+        assert cfg.expert_alignment % 128 == 0, 'the FP8 path needs an expert alignment that is a multiple of 128'
+        if getattr(self, '_w1_fp8', None) is None:
+            self.quantize_weights()
+        topk_idx, topk_weights = self.route(x)
+        (recv_x, recv_sf), _, recv_w, handle, _ = self.buffer.dispatch(
+            x, topk_idx=topk_idx, topk_weights=topk_weights.float().contiguous(), num_experts=cfg.num_experts,
+            expert_alignment=cfg.expert_alignment, num_sms=cfg.num_sms, do_expand=True, do_zero_padding=True,
+            do_cpu_sync=True, fused_fp8_quant=True)
+        y = grouped_swiglu_ffn_fp8(recv_x, recv_sf, self._w1_fp8, self._w1_sf, self._w2_fp8, self._w2_sf,
+                                   handle.psum_num_recv_tokens_per_expert, handle.num_unaligned_recv_tokens_per_expert,
+                                   alignment=cfg.expert_alignment, row_scale=recv_w)
+        out, _, _ = self.buffer.combine(y, handle)
+        if cfg.num_shared_experts > 0:
+            g, u = F.linear(x, self.shared_gate_up).chunk(2, dim=-1)
+            out = out + F.linear(F.silu(g) * u, self.shared_down)
+        return out
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         topk_idx, topk_weights = self.route(x.detach())

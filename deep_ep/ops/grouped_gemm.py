@@ -151,6 +151,59 @@ class GroupedLinear(torch.autograd.Function):
         return dx, dw, None, None, None
 
 
+# ---------------------------------------------------------------------------------------------- FP8 forward path
+def per_block_cast_to_fp8(w: torch.Tensor):
+    """Quantise weights `[..., n, k]` to e4m3 with one fp32 scale per 128 x 128 block (`n`, `k` multiples of 128).
+    Returns `(w_fp8 [..., n, k], scales [..., n / 128, k / 128])`; `w ~= w_fp8 * scales` expanded over the blocks."""
+    *lead, n, k = w.shape
+    assert n % 128 == 0 and k % 128 == 0
+    blocks = w.float().reshape(*lead, n // 128, 128, k // 128, 128)
+    amax = blocks.abs().amax(dim=(-3, -1), keepdim=True).clamp(min=1e-4)
+    q = (blocks * (448.0 / amax)).to(torch.float8_e4m3fn).reshape(*lead, n, k)
+    return q.contiguous(), (amax / 448.0).reshape(*lead, n // 128, k // 128).contiguous()
+
+
+def per_block_cast_back(w_fp8: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """fp32 `[..., n, k]` from `per_block_cast_to_fp8` output."""
+    return w_fp8.float() * scales.repeat_interleave(128, dim=-2).repeat_interleave(128, dim=-1)
+
+
+def grouped_gemm_fp8_forward(x_fp8: torch.Tensor, x_sf: torch.Tensor, w_fp8: torch.Tensor, w_sf: torch.Tensor,
+                             psum: torch.Tensor, count: torch.Tensor, swiglu: bool = False, quantize_output: bool = False,
+                             num_sms: int = 0, alignment: int = 1, row_scale: Optional[torch.Tensor] = None):
+    """`y[rows_e] = (x_fp8 * x_sf)[rows_e] @ (w_fp8[e] * w_sf[e]).T` on the FP8 tensor cores.
+
+    `x_fp8 [rows, K]` e4m3 with `x_sf [rows, K / 128]` fp32 (what an FP8 dispatch returns), `w_fp8 [G, N, K]` e4m3 with
+    `w_sf [G, N / 128, K / 128]`. Result: bf16 `[rows, N]`; with `swiglu` (`w[e] = [gate; up]`) bf16 `[rows, N / 2]`, or
+    with `quantize_output` the pair `(e4m3 [rows, N / 2], fp32 [rows, N / 256])` ready to feed the next FP8 GEMM.
+    Padding rows inside an expert's aligned region are written as zeros."""
+    rows, n = x_fp8.size(0), w_fp8.size(1)
+    if not swiglu:
+        assert not quantize_output and row_scale is None
+        y = torch.empty((rows, n), dtype=torch.bfloat16, device=x_fp8.device)
+        _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_STORE, num_sms, alignment, None, None)
+        return y
+    if quantize_output:
+        y = torch.empty((rows, n // 2), dtype=torch.float8_e4m3fn, device=x_fp8.device)
+        y_sf = torch.empty((rows, n // 256), dtype=torch.float32, device=x_fp8.device)
+        _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_SWIGLU, num_sms, alignment, row_scale, y_sf)
+        return y, y_sf
+    y = torch.empty((rows, n // 2), dtype=torch.bfloat16, device=x_fp8.device)
+    _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_SWIGLU, num_sms, alignment, row_scale, None)
+    return y
+
+
+def grouped_swiglu_ffn_fp8(x_fp8: torch.Tensor, x_sf: torch.Tensor, w_gate_up: torch.Tensor, w_gate_up_sf: torch.Tensor,
+                           w_down: torch.Tensor, w_down_sf: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
+                           alignment: int = 128, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Forward-only FP8 expert FFN over dispatched FP8 rows: GEMM1 with the SwiGLU epilogue re-quantises its output per
+    row and 128 columns, GEMM2 consumes that directly; the result is bf16 `[rows, H]`. No elementwise pass touches
+    global memory between the dispatch and the combine."""
+    act, act_sf = grouped_gemm_fp8_forward(x_fp8, x_sf, w_gate_up, w_gate_up_sf, psum, count, swiglu=True,
+                                           quantize_output=True, alignment=alignment, row_scale=row_scale)
+    return grouped_gemm_fp8_forward(act, act_sf, w_down, w_down_sf, psum, count, alignment=alignment)
+
+
 def _torch_ffn(x, w_gate_up, w_down, psum, count):
     pieces, cursor = [], 0
     w1s, w2s = w_gate_up.unbind(0), w_down.unbind(0)

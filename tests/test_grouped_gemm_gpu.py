@@ -135,3 +135,86 @@ def test_fused_ffn_row_scale_and_zero_padding(pairs):
     assert rel_err(outs[0][valid], outs[1][valid]) < 2e-2
     for a, b in zip(params[0], params[1]):
         assert rel_err(a.grad, b.grad) < 3e-2
+
+
+FP8_CASES = [
+    # counts per expert, alignment, K, N
+    ([128, 0, 37, 256, 1, 300], 128, 256, 256),
+    ([77, 130, 5, 64], 64, 512, 512),
+    ([500, 12, 0, 0, 129, 128, 127, 1000], 128, 1024, 768),
+]
+
+
+def _fp8_inputs(counts, alignment, k, n, dev):
+    from deep_ep.ops import grouped_gemm as gg
+    from deep_ep.utils.math import per_token_cast_to_fp8
+    psum, count, rows, starts = make_layout(counts, alignment, dev)
+    x = torch.randn(rows, k, device=dev, dtype=torch.bfloat16)
+    # uneven magnitudes per 128-column block and per weight block, so that a wrong scale index shows
+    x = x * (1 + torch.arange(k, device=dev) // 128).to(torch.bfloat16)
+    w = torch.randn(len(counts), n, k, device=dev) * 0.05
+    w = w * (1 + (torch.arange(n, device=dev) // 128).float()).view(1, n, 1) * (1 + (torch.arange(k, device=dev) // 128).float() * 0.5)
+    x_fp8, x_sf = per_token_cast_to_fp8(x)
+    w_fp8, w_sf = gg.per_block_cast_to_fp8(w)
+    x_deq = x_fp8.float() * x_sf.repeat_interleave(128, dim=1)
+    w_deq = gg.per_block_cast_back(w_fp8, w_sf)
+    return psum, count, rows, starts, x_fp8, x_sf, w_fp8, w_sf, x_deq, w_deq
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('counts,alignment,k,n', FP8_CASES)
+def test_grouped_fp8_forward(counts, alignment, k, n):
+    """Block-scaled e4m3 GEMM against fp32 PyTorch on the de-quantised operands."""
+    from deep_ep.ops import grouped_gemm as gg
+    torch.manual_seed(2)
+    dev = torch.device('cuda')
+    psum, count, rows, starts, x_fp8, x_sf, w_fp8, w_sf, x_deq, w_deq = _fp8_inputs(counts, alignment, k, n, dev)
+    out = gg.grouped_gemm_fp8_forward(x_fp8, x_sf, w_fp8, w_sf, psum, count, alignment=alignment)
+    torch.cuda.synchronize()
+    for e, (s, c) in enumerate(zip(starts, counts)):
+        if c == 0:
+            continue
+        ref = x_deq[s:s + c] @ w_deq[e].t()
+        got = out[s:s + c].float()
+        assert torch.allclose(got, ref, atol=1e-2 * ref.abs().max().item(), rtol=1e-2), f'expert {e}: {(got - ref).abs().max()}'
+        pad = (c + alignment - 1) // alignment * alignment
+        if pad > c:
+            assert out[s + c:s + pad].abs().max().item() == 0
+
+
+@pytest.mark.gpu
+def test_grouped_fp8_swiglu_and_ffn():
+    """SwiGLU epilogue (bf16 and re-quantised e4m3 output) and the two-GEMM FP8 FFN against fp32 PyTorch."""
+    from deep_ep.ops import grouped_gemm as gg
+    import torch.nn.functional as F
+    torch.manual_seed(3)
+    dev = torch.device('cuda')
+    counts, alignment, h, inter = [200, 0, 129, 64, 511], 128, 512, 256
+    psum, count, rows, starts, x_fp8, x_sf, w1_fp8, w1_sf, x_deq, w1_deq = _fp8_inputs(counts, alignment, h, 2 * inter, dev)
+    w2 = torch.randn(len(counts), h, inter, device=dev) * 0.05
+    w2_fp8, w2_sf = gg.per_block_cast_to_fp8(w2)
+    w2_deq = gg.per_block_cast_back(w2_fp8, w2_sf)
+    row_scale = torch.rand(rows, device=dev) + 0.5
+
+    act = gg.grouped_gemm_fp8_forward(x_fp8, x_sf, w1_fp8, w1_sf, psum, count, swiglu=True, alignment=alignment, row_scale=row_scale)
+    act_q, act_sf = gg.grouped_gemm_fp8_forward(x_fp8, x_sf, w1_fp8, w1_sf, psum, count, swiglu=True, quantize_output=True,
+                                                alignment=alignment, row_scale=row_scale)
+    y = gg.grouped_swiglu_ffn_fp8(x_fp8, x_sf, w1_fp8, w1_sf, w2_fp8, w2_sf, psum, count, alignment=alignment, row_scale=row_scale)
+    torch.cuda.synchronize()
+    act_deq = act_q.float() * act_sf.repeat_interleave(128, dim=1)
+    for e, (s, c) in enumerate(zip(starts, counts)):
+        if c == 0:
+            continue
+        g, u = (x_deq[s:s + c] @ w1_deq[e].t()).chunk(2, dim=-1)
+        ref_act = F.silu(g) * u * row_scale[s:s + c].unsqueeze(1)
+        scale = ref_act.abs().max().item()
+        assert torch.allclose(act[s:s + c].float(), ref_act, atol=1e-2 * scale, rtol=1e-2), f'swiglu expert {e}'
+        # e4m3 has 3 mantissa bits: relative error up to 2^-4 of each row block's maximum
+        err = (act_deq[s:s + c] - ref_act).abs().max().item()
+        assert err <= 0.07 * scale, f'quantised swiglu expert {e}: {err} vs {scale}'
+        # the FFN result against the same math on what the second GEMM actually consumed
+        ref_y = act_deq[s:s + c] @ w2_deq[e].t()
+        assert torch.allclose(y[s:s + c].float(), ref_y, atol=1e-2 * ref_y.abs().max().item(), rtol=1e-2), f'ffn expert {e}'
+        pad = (c + alignment - 1) // alignment * alignment
+        if pad > c:
+            assert y[s + c:s + pad].abs().max().item() == 0 and act[s + c:s + pad].abs().max().item() == 0

@@ -1,0 +1,85 @@
+"""The expert-parallel MoE layer (dispatch -> grouped tcgen05 GEMMs -> combine) against a dense fp32 PyTorch
+computation of the same layer, forward and backward, and the FP8 inference path against the BF16 one."""
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+
+def _dense_reference(x, gate, w_gate_up, w_down, num_topk):
+    """fp32 MoE FFN with every expert available locally: `sum_k weight_k * FFN_{expert_k}(x)`."""
+    import torch.nn.functional as F
+    scores = torch.softmax(F.linear(x.detach().float(), gate.float()), dim=-1)     # routing carries no gradient
+    topk_w, topk_idx = scores.topk(num_topk, dim=-1)
+    topk_w = topk_w / topk_w.sum(dim=-1, keepdim=True)
+    out = torch.zeros_like(x, dtype=torch.float32)
+    for e in range(w_gate_up.size(0)):
+        hit = (topk_idx == e)
+        rows = hit.any(dim=1).nonzero().squeeze(1)
+        if rows.numel() == 0:
+            continue
+        weight = (topk_w * hit)[rows].sum(dim=1, keepdim=True)
+        g, u = F.linear(x[rows].float(), w_gate_up[e].float()).chunk(2, dim=-1)
+        out.index_add_(0, rows, F.linear(F.silu(g) * u, w_down[e].float()) * weight)
+    return out
+
+
+def _moe_worker(rank, world_size, num_tokens, hidden, inter, num_experts, num_topk):
+    import torch.distributed as dist
+    from deep_ep.models.moe_layer import MoEConfig, MoELayer
+    torch.manual_seed(5)                       # same parameters on every rank, sliced per rank below
+    dev = torch.device('cuda')
+    cfg = MoEConfig(hidden=hidden, intermediate=inter, num_experts=num_experts, num_topk=num_topk,
+                    num_max_tokens_per_rank=num_tokens, expert_alignment=128)
+    gate = torch.randn(num_experts, hidden) * 0.5
+    w1 = (torch.randn(num_experts, 2 * inter, hidden) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(num_experts, hidden, inter) * 0.05).to(torch.bfloat16)
+    layer = MoELayer(dist.group.WORLD, cfg).to(dev)
+    local = num_experts // world_size
+    with torch.no_grad():
+        layer.gate.copy_(gate)
+        layer.w_gate_up.copy_(w1[rank * local:(rank + 1) * local])
+        layer.w_down.copy_(w2[rank * local:(rank + 1) * local])
+    torch.manual_seed(100 + rank)
+    x = torch.randn(num_tokens, hidden, device=dev, dtype=torch.bfloat16).requires_grad_()
+    dy = torch.randn(num_tokens, hidden, device=dev, dtype=torch.bfloat16)
+
+    y = layer(x)
+    y.backward(dy)
+    torch.cuda.synchronize()
+
+    xr = x.detach().clone().requires_grad_()
+    w1r, w2r = w1.to(dev).requires_grad_(), w2.to(dev).requires_grad_()
+    ref = _dense_reference(xr, gate.to(dev), w1r, w2r, num_topk)
+    ref.backward(dy.float())
+    scale = ref.abs().max().item()
+    assert torch.allclose(y.float(), ref, atol=2e-2 * scale, rtol=2e-2), f'forward: {(y.float() - ref).abs().max()} of {scale}'
+    gscale = xr.grad.abs().max().item()
+    assert torch.allclose(x.grad.float(), xr.grad.float(), atol=3e-2 * gscale, rtol=3e-2), 'input gradient'
+    # weight gradients: this rank's experts receive contributions from every rank's tokens
+    g1, g2 = w1r.grad.float(), w2r.grad.float()
+    dist.all_reduce(g1), dist.all_reduce(g2)
+    sl = slice(rank * local, (rank + 1) * local)
+    assert torch.allclose(layer.w_gate_up.grad.float(), g1[sl], atol=3e-2 * g1[sl].abs().max().item(), rtol=3e-2), 'gate/up gradient'
+    assert torch.allclose(layer.w_down.grad.float(), g2[sl], atol=3e-2 * g2[sl].abs().max().item(), rtol=3e-2), 'down gradient'
+
+    # FP8 inference path: e4m3 on the wire and in both GEMMs; compared as a whole-tensor relative difference
+    y8 = layer.forward_fp8(x.detach())
+    torch.cuda.synchronize()
+    a, b = y8.float(), ref.detach()
+    diff = 1 - 2 * (a * b).sum() / ((a * a).sum() + (b * b).sum())
+    assert diff.item() < 5e-3, f'fp8 forward differs: {diff.item()}'
+    layer.destroy()
+
+
+@pytest.mark.gpu
+def test_moe_layer_single_gpu(master_port):
+    run_distributed(_moe_worker, 1, master_port, 'nccl', (300, 512, 256, 8, 2))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_moe_layer_multi_gpu(master_port):
+    world = min(torch.cuda.device_count(), 8)
+    world -= world % 2
+    run_distributed(_moe_worker, world, master_port, 'nccl', (300, 512, 256, 16, 4))
