@@ -120,6 +120,52 @@ public:
         };
         return pybind11::make_tuple(event, epilogue, num_sms);
     }
+
+    // In-place batched reduce-scatter (`all_reduce == false`) or all-reduce of registered tensors. Every rank passes
+    // tensors at the same storage offsets; tensor i is cut into `num_ranks` equal shards and rank r reduces shard r.
+    // Returns `(results, event, num_sms)`: for a reduce-scatter `results[i]` is this rank's reduced shard (a view of
+    // `srcs[i]`), for an all-reduce it is `srcs[i]` itself. The kernel runs on the communication stream and contains
+    // both rank barriers, so the event marks completion on every rank's data.
+    // (The reference declares both without an implementation: `csrc/buffers/bucket.hpp:66-75`.)
+    pybind11::tuple reduce(const std::vector<torch::Tensor>& srcs, int context_idx, int num_sms, float scale, bool all_reduce) const {
+        EP_HOST_ASSERT(not destroyed);
+        EP_HOST_ASSERT(context_idx >= 0 and context_idx < static_cast<int>(contexts.size()));
+        EP_HOST_ASSERT(not srcs.empty() and static_cast<int>(srcs.size()) <= kMaxBuckets);
+        const auto& context = contexts[context_idx];
+        EP_HOST_ASSERT(context->peers_ready);
+        const int rank = context->rank_idx, num_ranks = context->num_ranks;
+
+        kernels::BucketReduceArgs args = {};
+        args.peers = context->peers, args.cs = context->common_signals, args.host_status = context->host_status_device;
+        args.timeout_ns = context->num_gpu_timeout_ns, args.scale = scale, args.all_reduce = all_reduce;
+        args.list.num_buckets = static_cast<int>(srcs.size());
+        std::vector<torch::Tensor> results;
+        const auto storage_ptr = reinterpret_cast<int64_t>(storage.data_ptr());
+        for (size_t i = 0; i < srcs.size(); ++i) {
+            const auto& src = srcs[i];
+            EP_HOST_ASSERT(src.is_cuda() and src.is_contiguous() and src.numel() > 0);
+            const auto bytes = static_cast<int64_t>(src.nbytes());
+            const auto offset = reinterpret_cast<int64_t>(src.data_ptr()) - storage_ptr;
+            EP_HOST_ASSERT_MSG(offset >= 0 and offset + bytes <= num_storage_bytes, "reduced tensors must belong to this BucketBuffer");
+            EP_HOST_ASSERT_MSG(offset % 16 == 0 and bytes % (int64_t(num_ranks) * 16) == 0,
+                               "reduced tensors must start on a 16-byte boundary and split into 16-byte aligned shards");
+            switch (src.scalar_type()) {
+                case torch::kBFloat16: args.dtype[i] = kernels::kReduceBF16; break;
+                case torch::kFloat32: args.dtype[i] = kernels::kReduceFP32; break;
+                case torch::kFloat16: args.dtype[i] = kernels::kReduceFP16; break;
+                default: EP_HOST_UNREACHABLE("reduce-scatter / all-reduce support bf16, fp16 and fp32 tensors");
+            }
+            args.list.buckets[i] = {context->num_workspace_bytes + offset, bytes, nullptr};
+            const auto shard_numel = src.numel() / num_ranks;
+            results.push_back(all_reduce ? src : src.view(-1).narrow(0, rank * shard_numel, shard_numel));
+        }
+        const auto compute_stream = c10::cuda::getCurrentCUDAStream();
+        const auto comm_stream = comm::get_comm_stream();
+        comm::stream_wait(comm_stream, compute_stream);
+        if (num_sms <= 0) num_sms = Runtime::get().get_num_sms();
+        launch::bucket_reduce(args, num_sms, comm_stream);
+        return pybind11::make_tuple(results, EventHandle(comm_stream), num_sms);
+    }
 };
 
 }  // namespace deep_ep

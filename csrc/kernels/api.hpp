@@ -31,6 +31,8 @@ void combine_reduce(kernels::CombineReduceArgs args, int num_sms, cudaStream_t s
 void barrier(const kernels::BarrierArgs& args, cudaStream_t stream);
 void engram_fetch(const kernels::EngramFetchArgs& args, int num_sms, cudaStream_t stream);
 void all_gather(const kernels::AllGatherArgs& args, int num_sms, cudaStream_t stream);
+// Batched in-place reduce-scatter (`args.all_reduce == 0`) or all-reduce over symmetric tensors.
+void bucket_reduce(const kernels::BucketReduceArgs& args, int num_sms, cudaStream_t stream);
 void pp_send(const kernels::PPArgs& args, int num_sms, cudaStream_t stream);
 void pp_recv(const kernels::PPArgs& args, int num_sms, cudaStream_t stream);
 void lb_exchange(const kernels::LBArgs& args, int num_sms, cudaStream_t stream);

@@ -129,6 +129,10 @@ void all_gather(const kernels::AllGatherArgs& args, int num_sms, cudaStream_t st
     launch_kernel(kernels::bucket_all_gather_kernel, args, clamp_sms(num_sms), 256, dev::bulk_copy_smem_bytes(8), true, stream);
 }
 
+void bucket_reduce(const kernels::BucketReduceArgs& args, int num_sms, cudaStream_t stream) {
+    launch_kernel(kernels::bucket_reduce_kernel, args, clamp_sms(num_sms), 512, 0, true, stream);
+}
+
 void pp_send(const kernels::PPArgs& args, int num_sms, cudaStream_t stream) {
     launch_kernel(kernels::pp_send_kernel, args, clamp_sms(num_sms), 256, dev::bulk_copy_smem_bytes(8), true, stream);
 }

@@ -287,5 +287,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def(py::init<const std::vector<int>&, const std::vector<int>&, const std::vector<std::string>&, int64_t, bool, int, bool>())
         .def_readonly("contexts", &BucketBuffer::contexts)
         .def_readonly("storage", &BucketBuffer::storage)
-        .def("all_gather", &BucketBuffer::all_gather);
+        .def("all_gather", &BucketBuffer::all_gather)
+        .def("reduce", &BucketBuffer::reduce, py::arg("srcs"), py::arg("context_idx"), py::arg("num_sms"), py::arg("scale"),
+             py::arg("all_reduce"));
 }

@@ -188,15 +188,39 @@ class BucketBuffer(BufferBase):
         """Device barrier over the selected group."""
         comm.barrier(self, wait_comm_stream, with_cpu_sync, sequential, self.get_context_idx(group))
 
+    def _reduce(self, srcs, scale: float, group: Optional[dist.ProcessGroup], num_sms: Optional[int], all_reduce: bool) -> EventOverlap:
+        is_packed, srcs = self._pack_tensors(srcs)
+        context_idx = self.get_context_idx(group)
+        assert num_sms in (None, 0) or num_sms > 0
+        results, event, used_sms = self.runtime.reduce(srcs, context_idx, 0 if num_sms is None else num_sms, float(scale), all_reduce)
+        handle = EventOverlap(event, extra_tensors=tuple(srcs) + (self.storage,))
+        handle.register_hook_after_wait(lambda: results[0] if is_packed else results)
+        setattr(handle, 'num_sms', used_sms)
+        return handle
+
     def reduce_scatter(self, srcs, comm_precision: str = 'fp32', scale: float = 1.0,
                        group: Optional[dist.ProcessGroup] = None, num_sms: Optional[int] = None) -> EventOverlap:
-        """Batched reduce-scatter (API of the reference, whose native kernel is also absent)."""
-        raise NotImplementedError('BucketBuffer.reduce_scatter is not implemented')
+        """Launch a batched in-place reduce-scatter of up to 64 registered tensors on the communication stream.
+
+        Every rank passes tensors at the same storage offsets (bf16, fp16 or fp32); tensor i is cut into `group.size()`
+        equal shards and this rank's shard receives `scale * sum over ranks`, accumulated in fp32 in rank order.
+        `handle.wait()` returns this rank's reduced shards (1-D views into `srcs`); the other shards of `srcs` keep
+        their contents. `comm_precision` names the accumulation precision and must be 'fp32': shards cross NVLink in
+        the tensors' own dtype because the owner pulls them straight from its peers' memory.
+        (The reference declares this method without a kernel behind it, `deep_ep/buffers/bucket.py:266-285`.)
+        """
+        assert comm_precision == 'fp32', 'sums are accumulated in fp32; other precisions are not offered'
+        return self._reduce(srcs, scale, group, num_sms, all_reduce=False)
 
     def all_reduce(self, srcs, scale: float = 1.0, group: Optional[dist.ProcessGroup] = None,
                    num_sms: Optional[int] = None) -> EventOverlap:
-        """Batched in-place all-reduce (API of the reference, whose native kernel is also absent)."""
-        raise NotImplementedError('BucketBuffer.all_reduce is not implemented')
+        """Launch a batched in-place all-reduce of up to 64 registered tensors on the communication stream.
+
+        One kernel: rank r pulls shard r of every tensor from all ranks, sums in fp32, scales, and stores the result to
+        every rank, so all ranks end with bitwise identical tensors. `handle.wait()` returns `srcs`.
+        (The reference declares this method without a kernel behind it, `deep_ep/buffers/bucket.py:287-305`.)
+        """
+        return self._reduce(srcs, scale, group, num_sms, all_reduce=True)
 
     def all_gather(self, srcs: Union[torch.Tensor, Sequence[torch.Tensor]],
                    dsts: Optional[Union[torch.Tensor, Sequence[torch.Tensor]]] = None,

@@ -4,6 +4,8 @@
 // with ordinary peer loads/stores (or NVLS `multimem.st`) issued by the SMs over NVLink.
 #pragma once
 
+#include <cuda_fp16.h>
+
 #include "../device/bulk_copy.cuh"
 #include "../device/sync.cuh"
 #include "misc_args.hpp"
@@ -143,6 +145,109 @@ __global__ void __launch_bounds__(512) bucket_all_gather_kernel(const __grid_con
     copier.drain();
     if (copier.failed and lane == 0) dev::report_status(a.cs, a.host_status, kStatusMbarrierTimeout, rank, -1, 42, 0, 0);
     __threadfence_system();
+}
+
+// ---------------------------------------------------------------------------------------- reduce-scatter / all-reduce
+// One pass over this rank's shard of every tensor: each 16-byte vector is pulled from all ranks (plain peer loads,
+// all in flight together), summed in fp32 in rank order (so the result does not depend on who reduces), scaled,
+// rounded to the tensor's dtype and stored in place on the owner; for an all-reduce the same registers are then stored
+// to the shard's position on every peer. Nobody else reads or writes shard `rank` positions, so the operation is in
+// place without staging. It starts with a rank barrier (every source is complete) and ends with one (every read and
+// write has been performed), so sources may be reused as soon as the kernel has completed.
+// The reference declares these two collectives without a kernel (`csrc/buffers/bucket.hpp:66-75`).
+namespace reduce_detail {
+
+template <int kDtype>
+EP_DEVICE void accumulate(float (&acc)[8], const int4& v) {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+    if constexpr (kDtype == kReduceFP32) {
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] += __uint_as_float(w[i]);
+    } else if constexpr (kDtype == kReduceBF16) {
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = ptx::bf16x2_to_float2(w[i]);
+            acc[2 * i] += f.x, acc[2 * i + 1] += f.y;
+        }
+    } else {
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            acc[2 * i] += f.x, acc[2 * i + 1] += f.y;
+        }
+    }
+}
+
+template <int kDtype>
+EP_DEVICE int4 finish(const float (&acc)[8], float scale) {
+    int4 out;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&out);
+    if constexpr (kDtype == kReduceFP32) {
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = __float_as_uint(acc[i] * scale);
+    } else if constexpr (kDtype == kReduceBF16) {
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = ptx::float2_to_bf16x2(acc[2 * i] * scale, acc[2 * i + 1] * scale);
+    } else {
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 h = __floats2half2_rn(acc[2 * i] * scale, acc[2 * i + 1] * scale);
+            w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+    }
+    return out;
+}
+
+template <int kDtype>
+EP_DEVICE void reduce_bucket(const BucketReduceArgs& a, const layout::Bucket& bucket, int64_t& tile_base) {
+    constexpr int64_t kTileBytes = 16 * 1024;
+    constexpr int kPeersPerRound = 8;
+    const int rank = a.peers.rank, num_ranks = a.peers.num_ranks;
+    const int64_t shard_bytes = bucket.num_bytes / num_ranks;
+    const int64_t base_off = bucket.dst_offset + int64_t(rank) * shard_bytes;
+    const int64_t num_tiles = math::ceil_div(shard_bytes, kTileBytes);
+    for (int64_t tile = (blockIdx.x + gridDim.x - tile_base % gridDim.x) % gridDim.x; tile < num_tiles; tile += gridDim.x) {
+        const int64_t begin = tile * kTileBytes, end = min(begin + kTileBytes, shard_bytes);
+        for (int64_t o = begin + threadIdx.x * 16; o < end; o += blockDim.x * 16) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int p0 = 0; p0 < num_ranks; p0 += kPeersPerRound) {
+                int4 v[kPeersPerRound];
+                #pragma unroll
+                for (int i = 0; i < kPeersPerRound; ++i)
+                    if (p0 + i < num_ranks) v[i] = ptx::ld_v4(a.peers.base[p0 + i] + base_off + o);
+                #pragma unroll
+                for (int i = 0; i < kPeersPerRound; ++i)
+                    if (p0 + i < num_ranks) accumulate<kDtype>(acc, v[i]);
+            }
+            const int4 out = finish<kDtype>(acc, a.scale);
+            if (a.all_reduce) {
+                for (int i = 0; i < num_ranks; ++i)
+                    ptx::st_na_v4(a.peers.base[(rank + 1 + i) % num_ranks] + base_off + o, out);     // the local copy comes last
+            } else {
+                ptx::st_v4(a.peers.base[rank] + base_off + o, out);
+            }
+        }
+    }
+    tile_base += num_tiles;
+}
+
+}  // namespace reduce_detail
+
+__global__ void __launch_bounds__(512) bucket_reduce_kernel(const __grid_constant__ BucketReduceArgs a) {
+    const int rank = a.peers.rank;
+    if (not dev::healthy(a.cs)) return;
+    if (blockIdx.x == 0 and threadIdx.x < 32) dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, /*where=*/44);
+    if (not dev::grid_sync(a.cs, a.host_status, gridDim.x, a.timeout_ns, rank, /*where=*/45)) return;
+    int64_t tile_base = 0;
+    for (int b = 0; b < a.list.num_buckets; ++b) {
+        const layout::Bucket& bucket = a.list.buckets[b];
+        if (a.dtype[b] == kReduceFP32) reduce_detail::reduce_bucket<kReduceFP32>(a, bucket, tile_base);
+        else if (a.dtype[b] == kReduceBF16) reduce_detail::reduce_bucket<kReduceBF16>(a, bucket, tile_base);
+        else reduce_detail::reduce_bucket<kReduceFP16>(a, bucket, tile_base);
+    }
+    __threadfence_system();
+    if (not dev::grid_sync(a.cs, a.host_status, gridDim.x, a.timeout_ns, rank, /*where=*/46)) return;
+    if (blockIdx.x == 0 and threadIdx.x < 32) dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, /*where=*/47);
 }
 
 // ---------------------------------------------------------------------------------------- load balancing

@@ -36,6 +36,21 @@ struct AllGatherArgs {
     int skip_local;                   // 1: the local shard is already in place
 };
 
+// Batched reduce-scatter / all-reduce over tensors that live at the same offset of every rank's symmetric allocation.
+// `list.buckets[i] = {offset of the whole tensor, bytes of the whole tensor, unused}`; rank r owns the r-th of
+// `num_ranks` equal shards of every tensor.
+enum ReduceDtype : int { kReduceBF16 = 0, kReduceFP32 = 1, kReduceFP16 = 2 };
+struct BucketReduceArgs {
+    layout::PeerTable peers;
+    layout::BucketList list;
+    layout::CommonSignals* cs;
+    layout::HostStatus* host_status;
+    long long timeout_ns;
+    int dtype[kMaxBuckets];           // ReduceDtype per bucket
+    float scale;                      // applied to the fp32 sum before it is rounded to the tensor's dtype
+    int all_reduce;                   // 0: the reduced shard stays on its owner; 1: it is also stored to every peer
+};
+
 struct PPArgs {
     layout::PeerTable peers;
     layout::PPSignals* ws;

@@ -261,6 +261,64 @@ def test_bucket_sessions(master_port):
 
 
 # ---------------------------------------------------------------------------------------------------- pipeline
+def _reduce_worker(rank, world):
+    import torch.distributed as dist
+    import deep_ep
+    group = dist.group.WORLD
+    bucket = deep_ep.BucketBuffer(group, 64 << 20, explicitly_destroy=True, num_gpu_timeout_secs=10)
+
+    def data(r, n, dtype):                       # what rank r holds: reproducible on every rank
+        g = torch.Generator(device='cuda').manual_seed(1000 + r)
+        return torch.randn(n, device='cuda', generator=g).to(dtype)
+
+    def expected(n, dtype, scale):               # fp32 sum in rank order, scaled, rounded once
+        acc = torch.zeros(n, device='cuda')
+        for r in range(world):
+            acc += data(r, n, dtype).float()
+        return (acc * scale).to(dtype)
+
+    with bucket.session() as session:
+        specs = [(world * 8 * 1000, torch.bfloat16), (world * 4 * 33, torch.float32), (world * 8 * 4096, torch.float16),
+                 (world * 8 * 70001, torch.bfloat16)]
+        tensors = [session.allocate((n,), dt) for n, dt in specs]
+        # ---- all-reduce: every rank ends with the same bits
+        for t, (n, dt) in zip(tensors, specs):
+            t.copy_(data(rank, n, dt))
+        out = bucket.all_reduce(tensors, scale=0.5).wait()
+        for o, t, (n, dt) in zip(out, tensors, specs):
+            assert o.data_ptr() == t.data_ptr()
+            assert torch.equal(o, expected(n, dt, 0.5)), f'all_reduce {dt} {n}'
+        # ---- reduce-scatter: my shard is reduced, the rest of my tensor is untouched
+        for t, (n, dt) in zip(tensors, specs):
+            t.copy_(data(rank, n, dt))
+        shards = bucket.reduce_scatter(tensors).wait()
+        for sh, t, (n, dt) in zip(shards, tensors, specs):
+            m = n // world
+            assert sh.numel() == m and sh.data_ptr() == t.data_ptr() + rank * m * t.element_size()
+            assert torch.equal(sh, expected(n, dt, 1.0)[rank * m:(rank + 1) * m]), f'reduce_scatter {dt} {n}'
+            mine = data(rank, n, dt)
+            keep = torch.ones(n, dtype=torch.bool, device='cuda')
+            keep[rank * m:(rank + 1) * m] = False
+            assert torch.equal(t[keep], mine[keep])
+        # ---- a single tensor comes back as a tensor; misaligned sizes are rejected
+        tensors[1].copy_(data(rank, specs[1][0], specs[1][1]))
+        single = bucket.all_reduce(tensors[1]).wait()
+        assert isinstance(single, torch.Tensor) and torch.equal(single, expected(specs[1][0], specs[1][1], 1.0))
+        odd = session.allocate((world * 4 + 1,), torch.float32)
+        with pytest.raises(deep_ep.EPException):
+            bucket.all_reduce(odd)
+        outside = torch.zeros(world * 16, device='cuda')
+        with pytest.raises(deep_ep.EPException):
+            bucket.reduce_scatter(outside)
+    torch.cuda.synchronize()
+    bucket.destroy()
+
+
+@pytest.mark.gpu
+def test_bucket_reduce_scatter_all_reduce(master_port):
+    run_distributed(_reduce_worker, _world(), master_port, 'nccl')
+
+
 def _pp_worker(rank, world):
     import random
     import torch.distributed as dist
