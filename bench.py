@@ -310,32 +310,48 @@ def main():
     e2e_ms, h2d_bytes, d2h_bytes = None, 0, 0
     if not args.skip_e2e:
         deep_ep._C.set_barrier_in_prologue(False)
-        x_dev, idx_dev, w_dev = torch.empty_like(x), torch.empty_like(topk_idx), torch.empty_like(topk_w)
+        # Input pipeline as a training or serving loop would run it: two device-side input sets; the copy of step i + 1
+        # (pinned host memory -> device, on a copy stream) overlaps the kernels of step i. Every step's copy and every
+        # step's device -> host read of the result happen inside the timed region.
+        dev_inputs = [(torch.empty_like(x), torch.empty_like(topk_idx), torch.empty_like(topk_w)) for _ in range(2)]
         result_host = torch.empty(2, dtype=torch.float32).pin_memory()
         h2d_bytes = x_host.nbytes + topk_idx_host.nbytes + topk_w_host.nbytes
         d2h_bytes = result_host.nbytes
+        copy_stream = torch.cuda.Stream()
+        copy_done = [torch.cuda.Event() for _ in range(2)]
+        inputs_free = [torch.cuda.Event() for _ in range(2)]
 
-        def e2e_step():
-            x_dev.copy_(x_host, non_blocking=True)
-            idx_dev.copy_(topk_idx_host, non_blocking=True)
-            w_dev.copy_(topk_w_host, non_blocking=True)
-            ev_d = buffer.dispatch(x_dev, topk_idx=idx_dev, topk_weights=w_dev, fused_fp8_quant=True, **common)
-            (rx, rsf), _, w_out, h = ev_d.current_stream_wait()
-            ev_c = buffer.combine(y[:rx.size(0)], h, topk_weights=w_out, num_sms=num_sms, async_with_compute_stream=True,
-                                  defer_epilogue=True)
-            combined, combined_w = ev_c.current_stream_wait()
-            result = torch.stack([combined[:, :8].float().sum(), combined_w.sum()])
-            result_host.copy_(result, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            return result_host
+        def issue_copy(i):
+            b = i % 2
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(inputs_free[b])          # the step that last read this set has finished
+                for dst, src in zip(dev_inputs[b], (x_host, topk_idx_host, topk_w_host)):
+                    dst.copy_(src, non_blocking=True)
+                copy_done[b].record(copy_stream)
 
-        for _ in range(3):
-            e2e_step()
+        def e2e_loop(steps):
+            issue_copy(0)
+            for i in range(steps):
+                b = i % 2
+                x_dev, idx_dev, w_dev = dev_inputs[b]
+                torch.cuda.current_stream().wait_event(copy_done[b])
+                if i + 1 < steps:
+                    issue_copy(i + 1)
+                ev_d = buffer.dispatch(x_dev, topk_idx=idx_dev, topk_weights=w_dev, fused_fp8_quant=True, **common)
+                (rx, rsf), _, w_out, h = ev_d.current_stream_wait()
+                ev_c = buffer.combine(y[:rx.size(0)], h, topk_weights=w_out, num_sms=num_sms, async_with_compute_stream=True,
+                                      defer_epilogue=True)
+                combined, combined_w = ev_c.current_stream_wait()
+                inputs_free[b].record()
+                result = torch.stack([combined[:, :8].float().sum(), combined_w.sum()])
+                result_host.copy_(result, non_blocking=True)
+                torch.cuda.current_stream().synchronize()      # the step's result is on the host
+
+        e2e_loop(3)
         dist.barrier()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        for _ in range(args.steps):
-            e2e_step()
+        e2e_loop(args.steps)
         torch.cuda.synchronize()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
 

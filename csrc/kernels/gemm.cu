@@ -68,8 +68,13 @@ void grouped_gemm_fp8(kernels::GroupedGemmFp8Args args, const void* a, int64_t a
     const CUtensorMap map_a = make_map_2d_u8(a, a_rows, args.k, 128);
     const CUtensorMap map_b = make_map_2d_u8(b, b_rows, args.k, 128);
     const auto smem = grouped_gemm_fp8_smem_bytes(args.num_stages);
-    CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    grouped_gemm_fp8_kernel<<<grid, kFp8Threads, smem, stream>>>(map_a, map_b, args);
+    if (args.reg_split) {
+        CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        grouped_gemm_fp8_kernel<true><<<grid, kFp8ThreadsRegSplit, smem, stream>>>(map_a, map_b, args);
+    } else {
+        CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        grouped_gemm_fp8_kernel<false><<<grid, kFp8Threads, smem, stream>>>(map_a, map_b, args);
+    }
     CUDA_CHECK(cudaGetLastError());
 }
 

@@ -109,7 +109,8 @@ void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::T
 // given, d e4m3 [rows, n / 2] with d_sf fp32 [rows, n / 256] (re-quantised for the next GEMM).
 void grouped_gemm_fp8(const torch::Tensor& a, const torch::Tensor& a_sf, const torch::Tensor& b, const torch::Tensor& b_sf,
                       const torch::Tensor& d, const torch::Tensor& psum, const torch::Tensor& count, int epilogue, int num_sms,
-                      int alignment, const std::optional<torch::Tensor>& row_scale, const std::optional<torch::Tensor>& d_sf) {
+                      int alignment, const std::optional<torch::Tensor>& row_scale, const std::optional<torch::Tensor>& d_sf,
+                      bool reg_split) {
     using namespace kernels;
     for (const auto* t : {&a, &a_sf, &b, &b_sf, &d, &psum, &count}) EP_HOST_ASSERT(t->is_cuda() and t->is_contiguous());
     EP_HOST_ASSERT(a.scalar_type() == torch::kFloat8_e4m3fn and b.scalar_type() == torch::kFloat8_e4m3fn and a.dim() == 2 and b.dim() == 3);
@@ -126,7 +127,7 @@ void grouped_gemm_fp8(const torch::Tensor& a, const torch::Tensor& a_sf, const t
     args.psum = psum.data_ptr<int>(), args.count = count.data_ptr<int>();
     args.n = static_cast<int>(n), args.k = static_cast<int>(k), args.alignment = alignment;
     args.sf_a = a_sf.data_ptr<float>(), args.sf_b = b_sf.data_ptr<float>();
-    args.d = d.data_ptr(), args.status = nullptr;
+    args.d = d.data_ptr(), args.status = nullptr, args.reg_split = reg_split;
     const int64_t n_out = epilogue == kEpilogueStore ? n : n / 2;
     EP_HOST_ASSERT(d.dim() == 2 and d.size(0) == rows and d.size(1) == n_out);
     if (d_sf.has_value()) {
@@ -248,7 +249,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("row_scale") = py::none(), py::arg("keep") = py::none(), py::arg("use_pairs") = false);
     m.def("grouped_gemm_fp8", &grouped_gemm_fp8, py::arg("a"), py::arg("a_sf"), py::arg("b"), py::arg("b_sf"), py::arg("d"),
           py::arg("psum"), py::arg("count"), py::arg("epilogue") = 0, py::arg("num_sms") = 0, py::arg("alignment") = 1,
-          py::arg("row_scale") = py::none(), py::arg("d_sf") = py::none());
+          py::arg("row_scale") = py::none(), py::arg("d_sf") = py::none(), py::arg("reg_split") = true);
     m.def("swiglu_backward", &swiglu_backward, py::arg("h"), py::arg("dact"), py::arg("row_scale") = py::none());
     m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
           py::arg("num_sms") = 0, py::arg("accumulate") = true, py::arg("use_pairs") = false);

@@ -131,11 +131,20 @@ EP_DEVICE bool mbarrier_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: false if the phase did not complete within `max_polls` polls (each poll itself
-// blocks for a hardware-defined short interval).
-EP_DEVICE bool mbarrier_wait(uint64_t* bar, uint32_t parity, int max_polls = 1 << 20) {
-    for (int i = 0; i < max_polls; ++i)
+// Bounded wait: false if the phase did not complete within `max_polls` polls or within `max_ns` of wall time,
+// whichever comes first (each poll itself blocks for a hardware-defined short interval, so the poll count alone
+// does not bound the time).
+EP_DEVICE bool mbarrier_wait(uint64_t* bar, uint32_t parity, int max_polls = 1 << 20, unsigned long long max_ns = 10000000000ull) {
+    unsigned long long start = 0;
+    for (int i = 0; i < max_polls; ++i) {
         if (mbarrier_try_wait(bar, parity)) return true;
+        if ((i & 63) == 63) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            else if (now - start > max_ns) return false;
+        }
+    }
     return false;
 }
 

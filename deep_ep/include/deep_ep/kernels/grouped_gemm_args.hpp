@@ -46,6 +46,7 @@ EP_HOST_DEVICE int64_t grouped_gemm_smem_bytes(int block_n, int num_stages) {
 constexpr int kFp8BlockK = 128;        // 128 e4m3 = one 128-byte swizzle row = one scale block
 constexpr int kFp8BlockN = 256;        // accumulator columns per tile
 constexpr int kFp8Threads = 320;       // producer warp, MMA warp, eight promotion/epilogue warps
+constexpr int kFp8ThreadsRegSplit = 384;   // the same plus two idle warps: three warpgroups that re-split the register file
 
 struct GroupedGemmFp8Args {
     int epilogue;             // kEpilogueStore: d = bf16 [rows, n]; kEpilogueSwiGLU: d = silu(gate) * up (* row_scale), [rows, n / 2]
@@ -63,6 +64,7 @@ struct GroupedGemmFp8Args {
     const float* row_scale;   // optional fp32 [rows] factor applied by the SwiGLU epilogue
     int alignment;            // rows in [count, align(count)) of a tile are written as zeros
     int* status;              // set to 1 if a bounded wait ran out (may be nullptr)
+    int reg_split;            // 1: 384-thread kernel that moves registers to the promotion warps (`setmaxnreg`)
 };
 
 EP_HOST_DEVICE int64_t grouped_gemm_fp8_smem_bytes(int num_stages) {

@@ -10,11 +10,13 @@
 // `tcgen05.ld` and add `sf_a[row, kb] * sf_b[block, kb] * partial` into fp32 registers while the tensor core
 // already works on the next K block in the second buffer.
 //
-// 320 threads per CTA:
-//   warp 0     TMA producer (tiled `cp.async.bulk.tensor`, 128-byte swizzle, CTA-local)
-//   warp 1     MMA issuer (one thread)
-//   warps 2-9  promotion + epilogue; warp w owns tensor-memory lanes 32 * (w % 4) .. +32 (one row per thread) and
-//              two 64-column segments of the 256-column tile
+// Roles (kRegSplit = true, 384 threads; the variant without the register split has 320 and no idle warps):
+//   warp 0      TMA producer (tiled `cp.async.bulk.tensor`, 128-byte swizzle, CTA-local)
+//   warp 1      MMA issuer (one thread)
+//   warps 2-3   idle: they complete the first warpgroup, which hands most of its registers to the other two
+//               (`setmaxnreg`), so that a promotion thread can hold 128 accumulators plus 64 values in flight
+//   warps 4-11  promotion + epilogue; warp w owns tensor-memory lanes 32 * (w % 4) .. +32 (one row per thread) and
+//               two 64-column segments of the 256-column tile
 // Epilogues: bf16 store, or SwiGLU (gate and up columns paired in one tile) with bf16 output or with e4m3 output
 // re-quantised per row and 128 columns, so that the second FFN GEMM consumes it without another pass.
 // The reference contains no matrix math; this kernel exists for the fused MoE layer the library is benchmarked in.
@@ -51,7 +53,8 @@ EP_DEVICE Fp8Tile locate_fp8_tile(const GroupedGemmFp8Args& a, const int* prefix
 
 }  // namespace gemm_detail
 
-__global__ void __launch_bounds__(kFp8Threads, 1)
+template <bool kRegSplit>
+__global__ void __launch_bounds__(kRegSplit ? kFp8ThreadsRegSplit : kFp8Threads, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ GroupedGemmFp8Args a) {
     using namespace gemm_detail;
@@ -103,7 +106,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     tc::fence_after_thread_sync();
     const uint32_t tmem_base = tmem_base_slot;
     const int num_tiles = tile_prefix[a.num_groups];
+    constexpr int kFirstEpilogueWarp = kRegSplit ? 4 : 2;
 
+    if (warp < kFirstEpilogueWarp) {
+    // The CTA's register pool is what the launch allocated: 384 threads x 168 registers = 64512. `setmaxnreg.inc` blocks
+    // until the pool has room, so the split must fit it exactly or below: 128 x 40 + 256 x 232 = 64512.
+    if constexpr (kRegSplit) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -149,10 +157,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 }
             }
         }
+    }
     } else {
-        // ------------------------------------------------------------------ promotion + epilogue (warps 2..9)
+        // ------------------------------------------------------------------ promotion + epilogue (eight warps)
+        if constexpr (kRegSplit) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
         const int quarter = warp & 3;                    // tensor-memory lane quarter this warp may access
-        const int half = (warp - 2) >> 2;                // which two 64-column segments
+        const int half = (warp - kFirstEpilogueWarp) >> 2;   // which two 64-column segments
         const int row = quarter * 32 + lane;
         // tensor-memory columns of the two segments: plain store -> 128 consecutive columns; SwiGLU -> 64 gate
         // columns and the 64 up columns that pair with them
@@ -183,20 +193,43 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 if (not ptx::mbarrier_wait(&tmem_full_bar[buf], use & 1)) { error_flag = 1; ok = false; break; }
                 tc::fence_after_thread_sync();
                 const uint32_t taddr = tmem_base + buf * kFp8BlockN + (uint32_t(quarter * 32) << 16);
-                #pragma unroll
-                for (int seg = 0; seg < 4; ++seg) {
-                    uint32_t r[32];
-                    tc::tmem_ld_32x32(taddr + (seg < 2 ? col_a + 32 * seg : col_b + 32 * (seg - 2)), r);
-                    tc::wait_ld();
-                    if (seg == 3) {
-                        // every value of this buffer is in registers: hand it back before the last multiply-adds
-                        tc::fence_before_thread_sync();
-                        __syncwarp();
-                        if (lane == 0) ptx::mbarrier_arrive(&tmem_empty_bar[buf]);
-                    }
-                    const float f = seg < 2 ? fa : fb;
+                if constexpr (kRegSplit) {
+                    // two round trips to tensor memory per K block, 64 columns each
                     #pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[32 * seg + i] = fmaf(f, __uint_as_float(r[i]), acc[32 * seg + i]);
+                    for (int seg = 0; seg < 2; ++seg) {
+                        uint32_t r0[32], r1[32];
+                        const int col = seg == 0 ? col_a : col_b;
+                        tc::tmem_ld_32x32(taddr + col, r0);
+                        tc::tmem_ld_32x32(taddr + col + 32, r1);
+                        tc::wait_ld();
+                        if (seg == 1) {
+                            // every value of this buffer is in registers: hand it back before the last multiply-adds
+                            tc::fence_before_thread_sync();
+                            __syncwarp();
+                            if (lane == 0) ptx::mbarrier_arrive(&tmem_empty_bar[buf]);
+                        }
+                        const float f = seg == 0 ? fa : fb;
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            acc[64 * seg + i] = fmaf(f, __uint_as_float(r0[i]), acc[64 * seg + i]);
+                            acc[64 * seg + 32 + i] = fmaf(f, __uint_as_float(r1[i]), acc[64 * seg + 32 + i]);
+                        }
+                    }
+                } else {
+                    #pragma unroll
+                    for (int seg = 0; seg < 4; ++seg) {
+                        uint32_t r[32];
+                        tc::tmem_ld_32x32(taddr + (seg < 2 ? col_a + 32 * seg : col_b + 32 * (seg - 2)), r);
+                        tc::wait_ld();
+                        if (seg == 3) {
+                            tc::fence_before_thread_sync();
+                            __syncwarp();
+                            if (lane == 0) ptx::mbarrier_arrive(&tmem_empty_bar[buf]);
+                        }
+                        const float f = seg < 2 ? fa : fb;
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[32 * seg + i] = fmaf(f, __uint_as_float(r[i]), acc[32 * seg + i]);
+                    }
                 }
             }
             if (not ok) break;

@@ -152,6 +152,9 @@ class GroupedLinear(torch.autograd.Function):
 
 
 # ---------------------------------------------------------------------------------------------- FP8 forward path
+# EP_FP8_REG_SPLIT=0 selects the 320-thread kernel without the `setmaxnreg` register split (kept for comparison).
+FP8_REG_SPLIT = os.environ.get('EP_FP8_REG_SPLIT', '1') != '0'
+
 def per_block_cast_to_fp8(w: torch.Tensor):
     """Quantise weights `[..., n, k]` to e4m3 with one fp32 scale per 128 x 128 block (`n`, `k` multiples of 128).
     Returns `(w_fp8 [..., n, k], scales [..., n / 128, k / 128])`; `w ~= w_fp8 * scales` expanded over the blocks."""
@@ -181,15 +184,15 @@ def grouped_gemm_fp8_forward(x_fp8: torch.Tensor, x_sf: torch.Tensor, w_fp8: tor
     if not swiglu:
         assert not quantize_output and row_scale is None
         y = torch.empty((rows, n), dtype=torch.bfloat16, device=x_fp8.device)
-        _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_STORE, num_sms, alignment, None, None)
+        _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_STORE, num_sms, alignment, None, None, FP8_REG_SPLIT)
         return y
     if quantize_output:
         y = torch.empty((rows, n // 2), dtype=torch.float8_e4m3fn, device=x_fp8.device)
         y_sf = torch.empty((rows, n // 256), dtype=torch.float32, device=x_fp8.device)
-        _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_SWIGLU, num_sms, alignment, row_scale, y_sf)
+        _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_SWIGLU, num_sms, alignment, row_scale, y_sf, FP8_REG_SPLIT)
         return y, y_sf
     y = torch.empty((rows, n // 2), dtype=torch.bfloat16, device=x_fp8.device)
-    _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_SWIGLU, num_sms, alignment, row_scale, None)
+    _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_SWIGLU, num_sms, alignment, row_scale, None, FP8_REG_SPLIT)
     return y
 
 

@@ -105,3 +105,17 @@ def test_random_gate_direction():
     scores = get_unbalanced_scores(2048, 64, 8, 6, 2.0, False, device=torch.device('cpu'))
     hits = torch.nn.functional.one_hot(scores.topk(6, dim=-1).indices // 8, 8).any(dim=1).float().sum(0)
     assert 1.5 < (hits[0] / hits[1:].mean()).item() < 2.6
+
+
+def test_per_block_fp8_cast_roundtrip():
+    """128 x 128 block quantisation of expert weights: shapes, scale definition and reconstruction error."""
+    from deep_ep.ops.grouped_gemm import per_block_cast_back, per_block_cast_to_fp8
+    torch.manual_seed(0)
+    w = torch.randn(3, 256, 384) * torch.tensor([0.01, 1.0, 30.0]).view(3, 1, 1)
+    q, sf = per_block_cast_to_fp8(w)
+    assert q.shape == w.shape and q.dtype == torch.float8_e4m3fn and sf.shape == (3, 2, 3) and sf.dtype == torch.float32
+    blocks = w.reshape(3, 2, 128, 3, 128).abs().amax(dim=(2, 4))
+    assert torch.allclose(sf, blocks / 448.0)
+    back = per_block_cast_back(q, sf)
+    # e4m3 keeps 3 mantissa bits: the error of an element is at most 1/16 of its block's maximum
+    assert ((back - w).abs() <= blocks.repeat_interleave(128, 1).repeat_interleave(128, 2) / 16 + 1e-12).all()
