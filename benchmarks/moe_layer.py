@@ -143,7 +143,7 @@ def main():
     torch.manual_seed(7 + rank)
     cfg = MoEConfig(hidden=args.hidden, intermediate=args.intermediate, num_experts=args.num_experts, num_topk=args.num_topk,
                     num_shared_experts=1, num_max_tokens_per_rank=args.num_tokens, expert_alignment=128)
-    ours = MoELayer(dist.group.WORLD, cfg).to(dev)
+    ours = MoELayer(dist.group.WORLD, cfg, device=dev)
     x = torch.randn(args.num_tokens, args.hidden, device=dev, dtype=torch.bfloat16, requires_grad=True)
 
     result = {'bench': 'moe_layer_fwd_bwd', 'n_gpus': world, 'tokens_per_rank': args.num_tokens, 'hidden': args.hidden,

@@ -30,6 +30,15 @@ namespace deep_ep::kernels {
 
 namespace gemm_detail {
 
+// acc{0,1} += f * {a0, a1} as one packed fp32x2 instruction (sm_100 issues two fp32 FMAs per slot this way).
+EP_DEVICE void fma2(float& acc0, float& acc1, uint32_t a0, uint32_t a1, float f) {
+    asm("{\n .reg .b64 va, vf, vc;\n"
+        " mov.b64 va, {%2, %3};\n mov.b64 vf, {%4, %4};\n mov.b64 vc, {%0, %1};\n"
+        " fma.rn.f32x2 vc, va, vf, vc;\n"
+        " mov.b64 {%0, %1}, vc;\n}\n"
+        : "+f"(acc0), "+f"(acc1) : "r"(a0), "r"(a1), "f"(f));
+}
+
 struct Fp8Tile {
     int expert, m0, n0, row_base, rows_valid, rows_written;
 };
@@ -210,9 +219,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         }
                         const float f = seg == 0 ? fa : fb;
                         #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            acc[64 * seg + i] = fmaf(f, __uint_as_float(r0[i]), acc[64 * seg + i]);
-                            acc[64 * seg + 32 + i] = fmaf(f, __uint_as_float(r1[i]), acc[64 * seg + 32 + i]);
+                        for (int i = 0; i < 32; i += 2) {
+                            fma2(acc[64 * seg + i], acc[64 * seg + i + 1], r0[i], r0[i + 1], f);
+                            fma2(acc[64 * seg + 32 + i], acc[64 * seg + 32 + i + 1], r1[i], r1[i + 1], f);
                         }
                     }
                 } else {

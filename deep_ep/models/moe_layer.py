@@ -71,7 +71,10 @@ class _Combine(torch.autograd.Function):
 class MoELayer(nn.Module):
     """Expert-parallel MoE FFN. Experts `[rank * E_local, (rank + 1) * E_local)` live on this rank."""
 
-    def __init__(self, group: dist.ProcessGroup, config: MoEConfig, buffer: Optional[EPBuffer] = None):
+    def __init__(self, group: dist.ProcessGroup, config: MoEConfig, buffer: Optional[EPBuffer] = None,
+                 device: Optional[torch.device] = None):
+        """`device`: where the parameters are created (default: CPU, to be moved with `.to()`); creating them on the GPU
+        avoids generating gigabytes of random numbers on the host for layers with many local experts."""
         super().__init__()
         self.group, self.config = group, config
         self.num_ranks, self.rank = group.size(), group.rank()
@@ -79,13 +82,13 @@ class MoELayer(nn.Module):
         self.num_local_experts = config.num_experts // self.num_ranks
         h, i, e = config.hidden, config.intermediate, self.num_local_experts
         std = config.init_std
-        self.gate = nn.Parameter(torch.randn(config.num_experts, h, dtype=torch.float32) * std)
-        self.w_gate_up = nn.Parameter(torch.randn(e, 2 * i, h, dtype=torch.bfloat16) * std)   # [gate; up] rows
-        self.w_down = nn.Parameter(torch.randn(e, h, i, dtype=torch.bfloat16) * std)
+        self.gate = nn.Parameter(torch.randn(config.num_experts, h, dtype=torch.float32, device=device) * std)
+        self.w_gate_up = nn.Parameter(torch.randn(e, 2 * i, h, dtype=torch.bfloat16, device=device) * std)   # [gate; up] rows
+        self.w_down = nn.Parameter(torch.randn(e, h, i, dtype=torch.bfloat16, device=device) * std)
         if config.num_shared_experts > 0:
             si = i * config.num_shared_experts
-            self.shared_gate_up = nn.Parameter(torch.randn(2 * si, h, dtype=torch.bfloat16) * std)
-            self.shared_down = nn.Parameter(torch.randn(h, si, dtype=torch.bfloat16) * std)
+            self.shared_gate_up = nn.Parameter(torch.randn(2 * si, h, dtype=torch.bfloat16, device=device) * std)
+            self.shared_down = nn.Parameter(torch.randn(h, si, dtype=torch.bfloat16, device=device) * std)
         self._own_buffer = buffer is None
         self.buffer = buffer if buffer is not None else EPBuffer(
             group, num_max_tokens_per_rank=config.num_max_tokens_per_rank, hidden=h, num_topk=config.num_topk,

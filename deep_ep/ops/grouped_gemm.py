@@ -160,6 +160,10 @@ def per_block_cast_to_fp8(w: torch.Tensor):
     Returns `(w_fp8 [..., n, k], scales [..., n / 128, k / 128])`; `w ~= w_fp8 * scales` expanded over the blocks."""
     *lead, n, k = w.shape
     assert n % 128 == 0 and k % 128 == 0
+    if lead and w.numel() > (1 << 28):
+        # one leading slice at a time: the fp32 temporaries of a whole expert stack would be several times its size
+        parts = [per_block_cast_to_fp8(w[i]) for i in range(w.size(0))]
+        return torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts])
     blocks = w.float().reshape(*lead, n // 128, 128, k // 128, 128)
     amax = blocks.abs().amax(dim=(-3, -1), keepdim=True).clamp(min=1e-4)
     q = (blocks * (448.0 / amax)).to(torch.float8_e4m3fn).reshape(*lead, n, k)
