@@ -104,7 +104,7 @@ class ClockSampler:
 
 def reference_arm(args):
     """The reference is Ascend C + CANN/HCCL: it has no CUDA path and cannot be installed or run on a B200 box."""
-    why = 'reference needs Ascend CANN/Bisheng/torch_npu and Ascend 950 hardware; pip install of /root/reference fails (see DESIGN.md)'
+    why = 'reference needs Ascend CANN/Bisheng/torch_npu and Ascend 950 hardware; its pip install fails at `import torch_npu`'
     marker = os.path.join(ROOT, 'baseline', 'reference_install.txt')
     if os.path.exists(marker):
         with open(marker) as f:

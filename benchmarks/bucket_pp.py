@@ -1,4 +1,4 @@
-"""Batched all-gather through `BucketBuffer` and pipeline send/recv through `PPBuffer`, the latter overlapped with a GEMM.
+"""Batched all-gather and all-reduce through `BucketBuffer` and pipeline send/recv through `PPBuffer`, the latter overlapped with a GEMM.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 benchmarks/bucket_pp.py
 
@@ -85,6 +85,33 @@ def main():
               'all_gather': {'ours_ms': round(ours_ms, 3), 'nccl_ms': round(nccl_ms, 3),
                              'ours_recv_gbs': round(recv_bytes / ours_ms / 1e6, 1), 'nccl_recv_gbs': round(recv_bytes / nccl_ms / 1e6, 1),
                              'ours_bus_gbs': round(recv_bytes * (world - 1) / world / ours_ms / 1e6, 1)}}
+
+    # ---- batched in-place all-reduce of the same 64 registered tensors (the reference declares it without a kernel)
+    def ours_ar():
+        bucket.all_reduce(dsts, group=group_a).wait()
+
+    def nccl_ar():
+        for o in nccl_out:
+            dist.all_reduce(o)
+
+    for d in dsts:
+        d.normal_()
+    check = [d.float().clone() for d in dsts[:2]]
+    for c in check:
+        dist.all_reduce(c)                           # fp32 reference of the first two tensors
+    ours_ar()
+    torch.cuda.synchronize()
+    for d, c in zip(dsts[:2], check):
+        assert torch.allclose(d.float(), c, atol=0.05 * world, rtol=0.02), 'all_reduce differs from the NCCL fp32 sum'
+    for d in dsts:
+        d.zero_()                                    # keep values finite over the timed repetitions
+    for o in nccl_out:
+        o.zero_()
+    ar_ms, nccl_ar_ms = timed(ours_ar, args.iters), timed(nccl_ar, args.iters)
+    ar_bytes = total * world
+    result['all_reduce'] = {'bytes_per_rank': ar_bytes, 'ours_ms': round(ar_ms, 3), 'nccl_ms': round(nccl_ar_ms, 3),
+                            'ours_bus_gbs': round(2 * ar_bytes * (world - 1) / world / ar_ms / 1e6, 1),
+                            'nccl_bus_gbs': round(2 * ar_bytes * (world - 1) / world / nccl_ar_ms / 1e6, 1)}
     bucket.destroy()
 
     # ---- pipeline send/recv overlapped with a GEMM

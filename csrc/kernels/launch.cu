@@ -130,7 +130,14 @@ void all_gather(const kernels::AllGatherArgs& args, int num_sms, cudaStream_t st
 }
 
 void bucket_reduce(const kernels::BucketReduceArgs& args, int num_sms, cudaStream_t stream) {
-    launch_kernel(kernels::bucket_reduce_kernel, args, clamp_sms(num_sms), 512, 0, true, stream);
+    const int sms = clamp_sms(num_sms);
+    switch (args.peers.num_ranks) {
+        case 1: launch_kernel(kernels::bucket_reduce_kernel<1>, args, sms, 256, 0, true, stream); break;
+        case 2: launch_kernel(kernels::bucket_reduce_kernel<2>, args, sms, 256, 0, true, stream); break;
+        case 4: launch_kernel(kernels::bucket_reduce_kernel<4>, args, sms, 256, 0, true, stream); break;
+        case 8: launch_kernel(kernels::bucket_reduce_kernel<8>, args, sms, 256, 0, true, stream); break;
+        default: launch_kernel(kernels::bucket_reduce_kernel<0>, args, sms, 256, 0, true, stream); break;
+    }
 }
 
 void pp_send(const kernels::PPArgs& args, int num_sms, cudaStream_t stream) {

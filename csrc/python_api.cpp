@@ -202,6 +202,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("set_arch", [](const std::string& a) { Runtime::get().set_arch(a); });
     m.def("set_barrier_in_prologue", [](bool v) { return Runtime::get().set_barrier_in_prologue(v); });
     m.def("get_barrier_in_prologue", [] { return Runtime::get().get_barrier_in_prologue(); });
+    // names under which the reference exposes the same knobs (`csrc/runtime/jit.hpp:86-116` there): a "vector core"
+    // corresponds to an SM here, there is no separate cube-core pool, and the architecture string is "sm_100a"
+    m.def("get_num_vec_cores", [] { return Runtime::get().get_num_sms(); });
+    m.def("set_num_vec_cores", [](int n) { Runtime::get().set_num_sms(n); });
+    m.def("set_num_cube_cores", [](int) {});
+    m.def("get_num_ai_cores", [] { return Runtime::get().get_num_device_sms(); });
+    m.def("get_npu_arch", [] { return Runtime::get().get_arch(); });
+    m.def("set_npu_arch", [](const std::string& a) { Runtime::get().set_arch(a); });
     jit::register_python_api(m);
 
     py::class_<EventHandle>(m, "EventHandle")

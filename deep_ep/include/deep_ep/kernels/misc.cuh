@@ -198,33 +198,59 @@ EP_DEVICE int4 finish(const float (&acc)[8], float scale) {
     return out;
 }
 
-template <int kDtype>
+EP_DEVICE void store_result(const BucketReduceArgs& a, int64_t offset, const int4& out) {
+    const int rank = a.peers.rank, num_ranks = a.peers.num_ranks;
+    if (a.all_reduce) {
+        for (int i = 0; i < num_ranks; ++i)       // the local copy comes last
+            ptx::st_na_v4(a.peers.base[(rank + 1 + i) % num_ranks] + offset, out);
+    } else {
+        ptx::st_v4(a.peers.base[rank] + offset, out);
+    }
+}
+
+// `kNumRanks` > 0: the group size is a compile-time constant and a thread keeps `16 / kNumRanks` vectors x `kNumRanks`
+// loads in flight (16 outstanding 16-byte loads: what covers the NVLink latency with one 256-thread CTA per SM).
+// `kNumRanks` == 0: any group size, one vector at a time, eight ranks per round of loads.
+template <int kDtype, int kNumRanks>
 EP_DEVICE void reduce_bucket(const BucketReduceArgs& a, const layout::Bucket& bucket, int64_t& tile_base) {
-    constexpr int64_t kTileBytes = 16 * 1024;
-    constexpr int kPeersPerRound = 8;
+    constexpr int64_t kTileBytes = 64 * 1024;
+    constexpr int kUnroll = kNumRanks == 0 ? 1 : (kNumRanks >= 8 ? 2 : 16 / (kNumRanks < 2 ? 2 : kNumRanks));
     const int rank = a.peers.rank, num_ranks = a.peers.num_ranks;
     const int64_t shard_bytes = bucket.num_bytes / num_ranks;
     const int64_t base_off = bucket.dst_offset + int64_t(rank) * shard_bytes;
     const int64_t num_tiles = math::ceil_div(shard_bytes, kTileBytes);
+    const int64_t step = int64_t(blockDim.x) * 16;
     for (int64_t tile = (blockIdx.x + gridDim.x - tile_base % gridDim.x) % gridDim.x; tile < num_tiles; tile += gridDim.x) {
         const int64_t begin = tile * kTileBytes, end = min(begin + kTileBytes, shard_bytes);
-        for (int64_t o = begin + threadIdx.x * 16; o < end; o += blockDim.x * 16) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int p0 = 0; p0 < num_ranks; p0 += kPeersPerRound) {
-                int4 v[kPeersPerRound];
+        for (int64_t o = begin + threadIdx.x * 16; o < end; o += step * kUnroll) {
+            if constexpr (kNumRanks > 0) {
+                int4 v[kUnroll][kNumRanks];
                 #pragma unroll
-                for (int i = 0; i < kPeersPerRound; ++i)
-                    if (p0 + i < num_ranks) v[i] = ptx::ld_v4(a.peers.base[p0 + i] + base_off + o);
+                for (int u = 0; u < kUnroll; ++u) {
+                    // vectors past the end of the tile re-read its first vector and are not stored
+                    const int64_t ou = o + u * step < end ? o + u * step : o;
+                    #pragma unroll
+                    for (int i = 0; i < kNumRanks; ++i) v[u][i] = ptx::ld_v4(a.peers.base[i] + base_off + ou);
+                }
                 #pragma unroll
-                for (int i = 0; i < kPeersPerRound; ++i)
-                    if (p0 + i < num_ranks) accumulate<kDtype>(acc, v[i]);
-            }
-            const int4 out = finish<kDtype>(acc, a.scale);
-            if (a.all_reduce) {
-                for (int i = 0; i < num_ranks; ++i)
-                    ptx::st_na_v4(a.peers.base[(rank + 1 + i) % num_ranks] + base_off + o, out);     // the local copy comes last
+                for (int u = 0; u < kUnroll; ++u) {
+                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    #pragma unroll
+                    for (int i = 0; i < kNumRanks; ++i) accumulate<kDtype>(acc, v[u][i]);
+                    if (o + u * step < end) store_result(a, base_off + o + u * step, finish<kDtype>(acc, a.scale));
+                }
             } else {
-                ptx::st_v4(a.peers.base[rank] + base_off + o, out);
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int p0 = 0; p0 < num_ranks; p0 += 8) {
+                    int4 v[8];
+                    #pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        v[i] = ptx::ld_v4(a.peers.base[min(p0 + i, num_ranks - 1)] + base_off + o);
+                    #pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (p0 + i < num_ranks) accumulate<kDtype>(acc, v[i]);
+                }
+                store_result(a, base_off + o, finish<kDtype>(acc, a.scale));
             }
         }
     }
@@ -233,7 +259,8 @@ EP_DEVICE void reduce_bucket(const BucketReduceArgs& a, const layout::Bucket& bu
 
 }  // namespace reduce_detail
 
-__global__ void __launch_bounds__(512) bucket_reduce_kernel(const __grid_constant__ BucketReduceArgs a) {
+template <int kNumRanks>
+__global__ void __launch_bounds__(256) bucket_reduce_kernel(const __grid_constant__ BucketReduceArgs a) {
     const int rank = a.peers.rank;
     if (not dev::healthy(a.cs)) return;
     if (blockIdx.x == 0 and threadIdx.x < 32) dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, /*where=*/44);
@@ -241,9 +268,9 @@ __global__ void __launch_bounds__(512) bucket_reduce_kernel(const __grid_constan
     int64_t tile_base = 0;
     for (int b = 0; b < a.list.num_buckets; ++b) {
         const layout::Bucket& bucket = a.list.buckets[b];
-        if (a.dtype[b] == kReduceFP32) reduce_detail::reduce_bucket<kReduceFP32>(a, bucket, tile_base);
-        else if (a.dtype[b] == kReduceBF16) reduce_detail::reduce_bucket<kReduceBF16>(a, bucket, tile_base);
-        else reduce_detail::reduce_bucket<kReduceFP16>(a, bucket, tile_base);
+        if (a.dtype[b] == kReduceFP32) reduce_detail::reduce_bucket<kReduceFP32, kNumRanks>(a, bucket, tile_base);
+        else if (a.dtype[b] == kReduceBF16) reduce_detail::reduce_bucket<kReduceBF16, kNumRanks>(a, bucket, tile_base);
+        else reduce_detail::reduce_bucket<kReduceFP16, kNumRanks>(a, bucket, tile_base);
     }
     __threadfence_system();
     if (not dev::grid_sync(a.cs, a.host_status, gridDim.x, a.timeout_ns, rank, /*where=*/46)) return;
