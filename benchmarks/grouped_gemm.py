@@ -88,6 +88,18 @@ def main():
                                                                                    quantize_output=True), None, 2 * useful * h * 2 * i),
             'fp8_gemm2_forward': (lambda: gg.grouped_gemm_fp8_forward(a8, a8_sf, w2_8, w2_sf, psum, count), None, 2 * useful * h * i),
         })
+    if not args.skip_fp8:
+        # hardware-scaled FP8: the same operands with power-of-two (UE8M0) scales applied by the tensor core
+        x8h, x8h_sf = gg.per_token_cast_to_fp8_ue8m0(x)
+        a8h, a8h_sf = gg.per_token_cast_to_fp8_ue8m0(act)
+        w1_8h, w1h_sf = gg.per_block_cast_to_fp8_ue8m0(w1)
+        w2_8h, w2h_sf = gg.per_block_cast_to_fp8_ue8m0(w2)
+        cases.update({
+            'fp8hw_gemm1_forward': (lambda: gg.grouped_gemm_fp8_forward(x8h, x8h_sf, w1_8h, w1h_sf, psum, count), None, 2 * useful * h * 2 * i),
+            'fp8hw_gemm1_forward_swiglu_quant': (lambda: gg.grouped_gemm_fp8_forward(x8h, x8h_sf, w1_8h, w1h_sf, psum, count, swiglu=True,
+                                                                                     quantize_output=True), None, 2 * useful * h * 2 * i),
+            'fp8hw_gemm2_forward': (lambda: gg.grouped_gemm_fp8_forward(a8h, a8h_sf, w2_8h, w2h_sf, psum, count), None, 2 * useful * h * i),
+        })
     out = {'bench': 'grouped_gemm', 'experts': g, 'rows_total': rows, 'rows_useful': useful, 'hidden': h, 'inter': i,
            'peak_tflops_measured': peak, 'results': {}}
     for name, (ours, ref, flops) in cases.items():

@@ -76,6 +76,39 @@ EP_DEVICE void mma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_
         " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(uint32_t(accumulate)) : "memory");
 }
+// ---------------------------------------------------------------- block-scaled MMA (kind::mxf8f6f4)
+// D[tmem] (+)= (A * SFA) * (B * SFB): one UE8M0 (power of two) scale per row of A and per column of B for the 32
+// K elements of the instruction, read from tensor memory. Scale layout in tensor memory, for a tile of 128 rows: lane
+// r % 32 (replicated in all four lane quarters), 32-bit column r / 32, and inside the column the byte chosen by the
+// instruction descriptor's scale id (0..3); 256 columns of B therefore take eight tensor-memory columns.
+// Instruction descriptor: as for kind::f8f6f4 without the D format field, plus
+//   [4,6) scale id of B   [23] scale type (1 = UE8M0)   [29,31) scale id of A
+EP_HOST_DEVICE constexpr uint32_t make_idesc_block_scaled(uint32_t ab_format, int m, int n, uint32_t sf_id_a, uint32_t sf_id_b) {
+    return (sf_id_b << 4) | (ab_format << 7) | (ab_format << 10) | (uint32_t(n >> 3) << 17) | (1u << 23) |
+           (uint32_t(m >> 4) << 24) | (sf_id_a << 29);
+}
+EP_DEVICE void mma_mxf8_block_scaled(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                     uint32_t tmem_sfa, uint32_t tmem_sfb, bool accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(uint32_t(accumulate)), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+// Shared-memory descriptor of an unswizzled K-major matrix of 16-byte rows: 8 consecutive rows form a 128-byte core
+// matrix, core matrices follow each other every `stride_bytes`.
+EP_DEVICE uint64_t make_smem_desc_noswizzle(const void* smem_ptr, uint32_t stride_bytes) {
+    uint64_t desc = 0;
+    desc |= uint64_t((ptx::smem_addr(smem_ptr) & 0x3ffff) >> 4);
+    desc |= uint64_t(stride_bytes >> 4) << 32;
+    desc |= uint64_t(1) << 46;
+    return desc;
+}
+// Copies 32 rows x 16 bytes of shared memory into 4 tensor-memory columns of lanes 0..31 and replicates them into the
+// other three lane quarters (the layout scale factors need). Asynchronous; ordered before later MMAs of this thread.
+EP_DEVICE void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
 // The mbarrier receives one arrival when every MMA issued so far by this thread has completed.
 EP_DEVICE void commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"

@@ -65,7 +65,15 @@ struct GroupedGemmFp8Args {
     int alignment;            // rows in [count, align(count)) of a tile are written as zeros
     int* status;              // set to 1 if a bounded wait ran out (may be nullptr)
     int reg_split;            // 1: 384-thread kernel that moves registers to the promotion warps (`setmaxnreg`)
+    // hardware-scaled variant (UE8M0 = power-of-two scales, one byte each, applied by the tensor core)
+    const uint8_t* sf_a_e8;   // [rows, k / 128]
+    const uint8_t* sf_b_e8;   // [G, n / 128, k / 128]
+    uint8_t* d_sf_e8;         // SwiGLU with e4m3 output: [rows, n / 256]
 };
+
+constexpr int kFp8SfGroup = 4;             // K blocks whose scale bytes share one 32-bit tensor-memory column
+constexpr int kFp8SfStages = 4;            // shared-memory stages of re-laid-out scale factors
+constexpr int kFp8SfStageBytes = 3 * 512;  // one 128-row atom for A, two for the 256 columns of B
 
 EP_HOST_DEVICE int64_t grouped_gemm_fp8_smem_bytes(int num_stages) {
     return int64_t(num_stages) * (kGemmBlockM + kFp8BlockN) * kFp8BlockK + 1024;

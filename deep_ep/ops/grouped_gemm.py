@@ -175,6 +175,43 @@ def per_block_cast_back(w_fp8: torch.Tensor, scales: torch.Tensor) -> torch.Tens
     return w_fp8.float() * scales.repeat_interleave(128, dim=-2).repeat_interleave(128, dim=-1)
 
 
+def _ue8m0_ceil(amax_over_448: torch.Tensor):
+    """Smallest power of two >= each (positive) entry, as `(uint8 UE8M0 bytes, fp32 values)`: value = 2^(byte - 127)."""
+    bits = amax_over_448.float().contiguous().view(torch.int32)
+    byte = ((bits >> 23) & 0xff) + ((bits & 0x7fffff) != 0).int()
+    byte = byte.clamp(1, 253)
+    return byte.to(torch.uint8), (byte << 23).view(torch.float32)
+
+
+def per_token_cast_to_fp8_ue8m0(x: torch.Tensor):
+    """`[m, n]` -> `(e4m3 [m, n], uint8 [m, n / 128])` with power-of-two scales `2^ceil(log2(amax / 448))` stored as UE8M0
+    bytes: the format the hardware-scaled FP8 GEMM reads."""
+    m, n = x.shape
+    assert n % 128 == 0
+    groups = x.float().reshape(m, n // 128, 128)
+    byte, scale = _ue8m0_ceil(groups.abs().amax(dim=2).clamp(min=1e-4) / 448.0)
+    q = (groups / scale.unsqueeze(2)).to(torch.float8_e4m3fn).reshape(m, n)
+    return q.contiguous(), byte.contiguous()
+
+
+def per_block_cast_to_fp8_ue8m0(w: torch.Tensor):
+    """Weights `[..., n, k]` -> `(e4m3, uint8 [..., n / 128, k / 128])` with one power-of-two scale per 128 x 128 block."""
+    *lead, n, k = w.shape
+    assert n % 128 == 0 and k % 128 == 0
+    if lead and w.numel() > (1 << 28):
+        parts = [per_block_cast_to_fp8_ue8m0(w[i]) for i in range(w.size(0))]
+        return torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts])
+    blocks = w.float().reshape(*lead, n // 128, 128, k // 128, 128)
+    byte, scale = _ue8m0_ceil(blocks.abs().amax(dim=(-3, -1), keepdim=True).clamp(min=1e-4) / 448.0)
+    q = (blocks / scale).to(torch.float8_e4m3fn).reshape(*lead, n, k)
+    return q.contiguous(), byte.reshape(*lead, n // 128, k // 128).contiguous()
+
+
+def ue8m0_to_float(sf: torch.Tensor) -> torch.Tensor:
+    """fp32 value `2^(byte - 127)` of UE8M0 scale bytes."""
+    return (sf.to(torch.int32) << 23).view(torch.float32)
+
+
 def grouped_gemm_fp8_forward(x_fp8: torch.Tensor, x_sf: torch.Tensor, w_fp8: torch.Tensor, w_sf: torch.Tensor,
                              psum: torch.Tensor, count: torch.Tensor, swiglu: bool = False, quantize_output: bool = False,
                              num_sms: int = 0, alignment: int = 1, row_scale: Optional[torch.Tensor] = None):
@@ -182,8 +219,12 @@ def grouped_gemm_fp8_forward(x_fp8: torch.Tensor, x_sf: torch.Tensor, w_fp8: tor
 
     `x_fp8 [rows, K]` e4m3 with `x_sf [rows, K / 128]` fp32 (what an FP8 dispatch returns), `w_fp8 [G, N, K]` e4m3 with
     `w_sf [G, N / 128, K / 128]`. Result: bf16 `[rows, N]`; with `swiglu` (`w[e] = [gate; up]`) bf16 `[rows, N / 2]`, or
-    with `quantize_output` the pair `(e4m3 [rows, N / 2], fp32 [rows, N / 256])` ready to feed the next FP8 GEMM.
-    Padding rows inside an expert's aligned region are written as zeros."""
+    with `quantize_output` the pair `(e4m3 [rows, N / 2], scales [rows, N / 256])` ready to feed the next FP8 GEMM.
+    Padding rows inside an expert's aligned region are written as zeros.
+
+    Scales are either fp32 (applied in registers after every K block of 128) or uint8 UE8M0 bytes (powers of two,
+    `per_token_cast_to_fp8_ue8m0` / `per_block_cast_to_fp8_ue8m0`), which the tensor core applies itself; the latter
+    needs K to be a multiple of 512."""
     rows, n = x_fp8.size(0), w_fp8.size(1)
     if not swiglu:
         assert not quantize_output and row_scale is None
@@ -192,7 +233,7 @@ def grouped_gemm_fp8_forward(x_fp8: torch.Tensor, x_sf: torch.Tensor, w_fp8: tor
         return y
     if quantize_output:
         y = torch.empty((rows, n // 2), dtype=torch.float8_e4m3fn, device=x_fp8.device)
-        y_sf = torch.empty((rows, n // 256), dtype=torch.float32, device=x_fp8.device)
+        y_sf = torch.empty((rows, n // 256), dtype=x_sf.dtype, device=x_fp8.device)
         _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_SWIGLU, num_sms, alignment, row_scale, y_sf, FP8_REG_SPLIT)
         return y, y_sf
     y = torch.empty((rows, n // 2), dtype=torch.bfloat16, device=x_fp8.device)

@@ -218,3 +218,78 @@ def test_grouped_fp8_swiglu_and_ffn():
         pad = (c + alignment - 1) // alignment * alignment
         if pad > c:
             assert y[s + c:s + pad].abs().max().item() == 0 and act[s + c:s + pad].abs().max().item() == 0
+
+
+UE8M0_CASES = [
+    # counts per expert, alignment, K (multiple of 512), N
+    ([128, 0, 37, 256, 1, 300], 128, 512, 256),
+    ([77, 130, 5, 64], 64, 1024, 512),
+    ([500, 12, 0, 0, 129, 128, 127, 1000], 128, 2048, 768),
+]
+
+
+def _ue8m0_inputs(counts, alignment, k, n, dev):
+    from deep_ep.ops import grouped_gemm as gg
+    psum, count, rows, starts = make_layout(counts, alignment, dev)
+    x = torch.randn(rows, k, device=dev) * (1 + torch.arange(k, device=dev) // 128).float() * 3.0
+    w = torch.randn(len(counts), n, k, device=dev) * 0.05
+    w = w * (1 + (torch.arange(n, device=dev) // 128).float() * 7).view(1, n, 1) * (1 + (torch.arange(k, device=dev) // 128).float() * 0.5)
+    x_fp8, x_sf = gg.per_token_cast_to_fp8_ue8m0(x)
+    w_fp8, w_sf = gg.per_block_cast_to_fp8_ue8m0(w)
+    x_deq = x_fp8.float() * gg.ue8m0_to_float(x_sf).repeat_interleave(128, dim=1)
+    w_deq = w_fp8.float() * gg.ue8m0_to_float(w_sf).repeat_interleave(128, dim=-2).repeat_interleave(128, dim=-1)
+    return psum, count, rows, starts, x_fp8, x_sf, w_fp8, w_sf, x_deq, w_deq
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('counts,alignment,k,n', UE8M0_CASES)
+def test_grouped_fp8_hardware_scaled_forward(counts, alignment, k, n):
+    """`kind::mxf8f6f4.block_scale` GEMM with UE8M0 scales against fp32 PyTorch on the de-quantised operands."""
+    from deep_ep.ops import grouped_gemm as gg
+    torch.manual_seed(4)
+    dev = torch.device('cuda')
+    psum, count, rows, starts, x_fp8, x_sf, w_fp8, w_sf, x_deq, w_deq = _ue8m0_inputs(counts, alignment, k, n, dev)
+    out = gg.grouped_gemm_fp8_forward(x_fp8, x_sf, w_fp8, w_sf, psum, count, alignment=alignment)
+    torch.cuda.synchronize()
+    for e, (s, c) in enumerate(zip(starts, counts)):
+        if c == 0:
+            continue
+        ref = x_deq[s:s + c] @ w_deq[e].t()
+        got = out[s:s + c].float()
+        assert torch.allclose(got, ref, atol=1e-2 * ref.abs().max().item(), rtol=1e-2), f'expert {e}: {(got - ref).abs().max()}'
+        pad = (c + alignment - 1) // alignment * alignment
+        if pad > c:
+            assert out[s + c:s + pad].abs().max().item() == 0
+
+
+@pytest.mark.gpu
+def test_grouped_fp8_hardware_scaled_swiglu_chain():
+    """SwiGLU epilogue with e4m3 + UE8M0 output feeding the second hardware-scaled GEMM."""
+    from deep_ep.ops import grouped_gemm as gg
+    import torch.nn.functional as F
+    torch.manual_seed(6)
+    dev = torch.device('cuda')
+    counts, alignment, h, inter = [200, 0, 129, 64, 511], 128, 512, 512
+    psum, count, rows, starts, x_fp8, x_sf, w1_fp8, w1_sf, x_deq, w1_deq = _ue8m0_inputs(counts, alignment, h, 2 * inter, dev)
+    w2 = torch.randn(len(counts), h, inter, device=dev) * 0.05
+    w2_fp8, w2_sf = gg.per_block_cast_to_fp8_ue8m0(w2)
+    w2_deq = w2_fp8.float() * gg.ue8m0_to_float(w2_sf).repeat_interleave(128, dim=-2).repeat_interleave(128, dim=-1)
+    row_scale = torch.rand(rows, device=dev) + 0.5
+    act = gg.grouped_gemm_fp8_forward(x_fp8, x_sf, w1_fp8, w1_sf, psum, count, swiglu=True, alignment=alignment, row_scale=row_scale)
+    act_q, act_sf = gg.grouped_gemm_fp8_forward(x_fp8, x_sf, w1_fp8, w1_sf, psum, count, swiglu=True, quantize_output=True,
+                                                alignment=alignment, row_scale=row_scale)
+    assert act_sf.dtype == torch.uint8
+    y = gg.grouped_gemm_fp8_forward(act_q, act_sf, w2_fp8, w2_sf, psum, count, alignment=alignment)
+    torch.cuda.synchronize()
+    act_deq = act_q.float() * gg.ue8m0_to_float(act_sf).repeat_interleave(128, dim=1)
+    for e, (s, c) in enumerate(zip(starts, counts)):
+        if c == 0:
+            continue
+        g, u = (x_deq[s:s + c] @ w1_deq[e].t()).chunk(2, dim=-1)
+        ref_act = F.silu(g) * u * row_scale[s:s + c].unsqueeze(1)
+        scale = ref_act.abs().max().item()
+        assert torch.allclose(act[s:s + c].float(), ref_act, atol=1e-2 * scale, rtol=1e-2), f'swiglu expert {e}'
+        err = (act_deq[s:s + c] - ref_act).abs().max().item()
+        assert err <= 0.07 * scale, f'quantised swiglu expert {e}: {err} vs {scale}'
+        ref_y = act_deq[s:s + c] @ w2_deq[e].t()
+        assert torch.allclose(y[s:s + c].float(), ref_y, atol=1e-2 * ref_y.abs().max().item(), rtol=1e-2), f'ffn expert {e}'

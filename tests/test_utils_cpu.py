@@ -119,3 +119,21 @@ def test_per_block_fp8_cast_roundtrip():
     back = per_block_cast_back(q, sf)
     # e4m3 keeps 3 mantissa bits: the error of an element is at most 1/16 of its block's maximum
     assert ((back - w).abs() <= blocks.repeat_interleave(128, 1).repeat_interleave(128, 2) / 16 + 1e-12).all()
+
+
+def test_ue8m0_casts():
+    """Power-of-two (UE8M0) scales: smallest power of two that keeps every value within the e4m3 range."""
+    from deep_ep.ops.grouped_gemm import per_block_cast_to_fp8_ue8m0, per_token_cast_to_fp8_ue8m0, ue8m0_to_float
+    torch.manual_seed(1)
+    x = torch.randn(5, 384) * torch.tensor([1e-3, 0.1, 1.0, 50.0, 3000.0]).view(5, 1)
+    q, sf = per_token_cast_to_fp8_ue8m0(x)
+    assert q.dtype == torch.float8_e4m3fn and sf.dtype == torch.uint8 and sf.shape == (5, 3)
+    scale = ue8m0_to_float(sf)
+    amax = x.reshape(5, 3, 128).abs().amax(dim=2)
+    assert (scale * 448 >= amax).all() and (scale * 224 < amax.clamp(min=1e-4)).all()      # tight within a factor of two
+    assert torch.equal(torch.log2(scale), torch.log2(scale).round())
+    back = q.float() * scale.repeat_interleave(128, dim=1)
+    assert ((back - x).abs() <= amax.repeat_interleave(128, dim=1) / 8 + 1e-12).all()
+    w = torch.randn(2, 256, 128)
+    wq, wsf = per_block_cast_to_fp8_ue8m0(w)
+    assert wq.shape == w.shape and wsf.shape == (2, 2, 1) and wsf.dtype == torch.uint8
