@@ -141,7 +141,7 @@ public:
                              const std::optional<EventHandle>& previous_event,
                              bool async_with_compute_stream, bool allocate_on_comm_stream,
                              bool do_handle_copy, bool do_cpu_sync, bool do_expand, bool do_zero_padding,
-                             bool use_col_major_sf, bool defer_epilogue, bool fused_fp8_quant) {
+                             bool use_col_major_sf, bool defer_epilogue, int fused_fp8_quant) {
         EP_HOST_ASSERT(not destroyed and context->peers_ready);
         EP_HOST_ASSERT(do_expand and not do_handle_copy);
         (void) allocate_on_comm_stream;
@@ -182,6 +182,9 @@ public:
         int64_t sf_token_stride = 0, sf_pack_stride = 0;
         int num_sf_packs = 0;
         auto wire_dtype = x.scalar_type();
+        // 0: `x` is sent as given; 1: bf16 `x` is quantised in the kernel (fp32 scales amax / 448); 2: the same with the
+        // scales rounded up to powers of two
+        EP_HOST_ASSERT(fused_fp8_quant >= 0 and fused_fp8_quant <= 2);
         if (fused_fp8_quant) {
             EP_HOST_ASSERT(x.scalar_type() == torch::kBFloat16 and not sf.has_value() and hidden % 128 == 0);
             hidden_bytes = hidden, num_sf_packs = hidden / 128 * 2, sf_bytes = num_sf_packs * 2;

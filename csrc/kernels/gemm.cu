@@ -69,10 +69,11 @@ void grouped_gemm_fp8(kernels::GroupedGemmFp8Args args, const void* a, int64_t a
     const CUtensorMap map_a = make_map_2d_u8(a, a_rows, args.k, 128);
     const CUtensorMap map_b = make_map_2d_u8(b, b_rows, args.k, 128);
     const auto smem = grouped_gemm_fp8_smem_bytes(args.num_stages);
-    if (args.sf_a_e8 != nullptr) {
-        // hardware-scaled variant: UE8M0 scale bytes, whole groups of four K blocks
+    if (args.sf_b_e8 != nullptr) {
+        // hardware-scaled variant: UE8M0 scale bytes (A may also come as fp32 powers of two), whole groups of four K blocks
         EP_HOST_ASSERT_MSG(args.k % (kFp8BlockK * kFp8SfGroup) == 0, "the hardware-scaled FP8 GEMM needs K to be a multiple of 512");
-        EP_HOST_ASSERT(args.sf_b_e8 != nullptr and reinterpret_cast<uintptr_t>(args.sf_a_e8) % 4 == 0 and
+        EP_HOST_ASSERT((args.sf_a_e8 != nullptr) != (args.sf_a != nullptr));
+        EP_HOST_ASSERT(reinterpret_cast<uintptr_t>(args.sf_a_e8) % 4 == 0 and reinterpret_cast<uintptr_t>(args.sf_a) % 16 == 0 and
                        reinterpret_cast<uintptr_t>(args.sf_b_e8) % 4 == 0);
         CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_fp8_hw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         grouped_gemm_fp8_hw_kernel<<<grid, kFp8ThreadsRegSplit, smem, stream>>>(map_a, map_b, args);

@@ -115,9 +115,11 @@ void grouped_gemm_fp8(const torch::Tensor& a, const torch::Tensor& a_sf, const t
     using namespace kernels;
     for (const auto* t : {&a, &a_sf, &b, &b_sf, &d, &psum, &count}) EP_HOST_ASSERT(t->is_cuda() and t->is_contiguous());
     EP_HOST_ASSERT(a.scalar_type() == torch::kFloat8_e4m3fn and b.scalar_type() == torch::kFloat8_e4m3fn and a.dim() == 2 and b.dim() == 3);
-    // fp32 scales -> promotion in registers; uint8 scales -> UE8M0 bytes applied by the tensor core
-    const bool hw_scales = a_sf.scalar_type() == torch::kUInt8;
-    EP_HOST_ASSERT(b_sf.scalar_type() == a_sf.scalar_type() and (hw_scales or a_sf.scalar_type() == torch::kFloat32));
+    // fp32 weight scales -> promotion in registers; uint8 weight scales -> UE8M0 bytes applied by the tensor core, with the
+    // activation scales as UE8M0 bytes too or as fp32 powers of two (what a power-of-two FP8 dispatch delivers)
+    const bool hw_scales = b_sf.scalar_type() == torch::kUInt8;
+    EP_HOST_ASSERT(hw_scales or (b_sf.scalar_type() == torch::kFloat32 and a_sf.scalar_type() == torch::kFloat32));
+    EP_HOST_ASSERT(a_sf.scalar_type() == torch::kUInt8 ? hw_scales : a_sf.scalar_type() == torch::kFloat32);
     EP_HOST_ASSERT(psum.scalar_type() == torch::kInt32 and count.scalar_type() == torch::kInt32 and psum.numel() == count.numel());
     EP_HOST_ASSERT(epilogue == kEpilogueStore or epilogue == kEpilogueSwiGLU);
     const int64_t rows = a.size(0), k = a.size(1), g = psum.numel(), n = b.size(1);
@@ -129,15 +131,17 @@ void grouped_gemm_fp8(const torch::Tensor& a, const torch::Tensor& a_sf, const t
     args.epilogue = epilogue, args.num_groups = static_cast<int>(g);
     args.psum = psum.data_ptr<int>(), args.count = count.data_ptr<int>();
     args.n = static_cast<int>(n), args.k = static_cast<int>(k), args.alignment = alignment;
-    if (hw_scales) args.sf_a_e8 = a_sf.data_ptr<uint8_t>(), args.sf_b_e8 = b_sf.data_ptr<uint8_t>();
-    else args.sf_a = a_sf.data_ptr<float>(), args.sf_b = b_sf.data_ptr<float>();
+    if (a_sf.scalar_type() == torch::kUInt8) args.sf_a_e8 = a_sf.data_ptr<uint8_t>();
+    else args.sf_a = a_sf.data_ptr<float>();
+    if (hw_scales) args.sf_b_e8 = b_sf.data_ptr<uint8_t>();
+    else args.sf_b = b_sf.data_ptr<float>();
     args.d = d.data_ptr(), args.status = nullptr, args.reg_split = reg_split;
     const int64_t n_out = epilogue == kEpilogueStore ? n : n / 2;
     EP_HOST_ASSERT(d.dim() == 2 and d.size(0) == rows and d.size(1) == n_out);
     if (d_sf.has_value()) {
         EP_HOST_ASSERT(epilogue == kEpilogueSwiGLU and d.scalar_type() == torch::kFloat8_e4m3fn);
         EP_HOST_ASSERT(d_sf->is_cuda() and d_sf->is_contiguous() and d_sf->dim() == 2 and d_sf->size(0) == rows and
-                       d_sf->size(1) == n_out / 128 and d_sf->scalar_type() == a_sf.scalar_type());
+                       d_sf->size(1) == n_out / 128 and d_sf->scalar_type() == b_sf.scalar_type());
         args.out_fp8 = 1;
         if (hw_scales) args.d_sf_e8 = d_sf->data_ptr<uint8_t>();
         else args.d_sf = d_sf->data_ptr<float>();

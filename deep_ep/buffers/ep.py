@@ -216,7 +216,7 @@ class EPBuffer(BufferBase):
                  allocate_on_comm_stream: bool = False, handle: Optional[EPHandle] = None,
                  do_handle_copy: bool = False, do_cpu_sync: Optional[bool] = None, do_expand: bool = False,
                  do_zero_padding: bool = False, use_tma_aligned_col_major_sf: bool = False,
-                 defer_epilogue: bool = False, *, fused_fp8_quant: bool = False):
+                 defer_epilogue: bool = False, *, fused_fp8_quant: Union[bool, str] = False):
         """Send every token to the ranks that own its selected experts.
 
         Arguments:
@@ -239,7 +239,9 @@ class EPBuffer(BufferBase):
             defer_epilogue: return only an `EventOverlap`; `current_stream_wait()` then runs the host count
                 wait and the expand kernel and returns `(recv_x, None, recv_topk_weights, handle)`.
             fused_fp8_quant: `x` is bf16 and is quantised to e4m3 with fp32 1x128 scales inside the kernel;
-                the result is `(recv_x_fp8, recv_sf_fp32 [rows, hidden / 128])`.
+                the result is `(recv_x_fp8, recv_sf_fp32 [rows, hidden / 128])`. `'ue8m0'` rounds every scale up to a
+                power of two (`2^ceil(log2(amax / 448))`, still delivered as fp32): the form that the hardware-scaled
+                FP8 GEMM (`deep_ep.ops.grouped_gemm`) consumes directly.
 
         Returns `(recv_x | (recv_x, recv_sf), None, recv_topk_weights, handle, event)` or, deferred, the event.
         """
@@ -247,6 +249,8 @@ class EPBuffer(BufferBase):
             raise NotImplementedError('Explicit QP counts do not exist on NVLink')
         assert not do_handle_copy, '`do_handle_copy` must be False; handle copying is not supported'
         x, sf = x if isinstance(x, tuple) else (x, None)
+        assert fused_fp8_quant in (False, True, 'ue8m0'), "`fused_fp8_quant` is False, True or 'ue8m0'"
+        quant_mode = 2 if fused_fp8_quant == 'ue8m0' else int(bool(fused_fp8_quant))
         assert do_expand, 'only the expanded layout (`do_expand=True`) is implemented'
 
         if handle is not None:
@@ -278,7 +282,7 @@ class EPBuffer(BufferBase):
             x, sf, topk_idx, topk_weights, cumulative_local_expert_recv_stats, *cached,
             num_max_tokens_per_rank, num_experts, expert_alignment, num_sms, previous_event,
             async_with_compute_stream, allocate_on_comm_stream, do_handle_copy, do_cpu_sync, do_expand,
-            do_zero_padding, use_tma_aligned_col_major_sf, defer_epilogue, fused_fp8_quant)
+            do_zero_padding, use_tma_aligned_col_major_sf, defer_epilogue, quant_mode)
         event_overlap = EventOverlap(event)
 
         def finalize(dispatch_result: tuple, deterministic_by_hook: bool):

@@ -176,6 +176,13 @@ EP_DEVICE uint32_t float2_to_bf16x2(float lo, float hi) {
     __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&r);
 }
+// Smallest power of two >= x (x > 0, finite, normal) as a UE8M0 byte (value 2^(byte - 127)) and its exact reciprocal.
+EP_DEVICE void ue8m0_ceil(float x, uint32_t& byte, float& inv) {
+    const uint32_t bits = __float_as_uint(x);
+    byte = min(max((bits >> 23) + ((bits & 0x7fffffu) != 0), 1u), 253u);
+    inv = __uint_as_float((254u - byte) << 23);
+}
+
 // two fp32 -> two e4m3 (round-to-nearest-even, saturating), low byte = first argument
 EP_DEVICE uint16_t float2_to_e4m3x2(float lo, float hi) {
     uint16_t r;

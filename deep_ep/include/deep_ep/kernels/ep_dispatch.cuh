@@ -68,7 +68,9 @@ EP_DEVICE void wait_read_pending(int n) {
 
 // Quantise one BF16 row held in shared memory into e4m3 + fp32 scales in the message stage.
 // Bit-compatible with `x * (448 * (1 / max(amax, 1e-4)))` rounded to e4m3 and `scale = amax * (1/448)`.
-EP_DEVICE void quantize_row(const uint8_t* src, uint8_t* dst_fp8, float* dst_sf, int hidden, int lane) {
+// With `pow2` the scale is rounded up to a power of two (`2^ceil(log2(amax / 448))`, still sent as fp32), the form
+// the tensor core can apply itself as a UE8M0 block scale.
+EP_DEVICE void quantize_row(const uint8_t* src, uint8_t* dst_fp8, float* dst_sf, int hidden, int lane, bool pow2) {
     const int num_iters = math::ceil_div(hidden, 256);
     for (int it = 0; it < num_iters; ++it) {
         const int col = it * 256 + lane * 8;
@@ -88,7 +90,12 @@ EP_DEVICE void quantize_row(const uint8_t* src, uint8_t* dst_fp8, float* dst_sf,
         #pragma unroll
         for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         amax = fmaxf(amax, 1e-4f);
-        const float inv = __fmul_rn(__frcp_rn(amax), 448.0f);
+        float inv = __fmul_rn(__frcp_rn(amax), 448.0f), sf = __fmul_rn(amax, 1.0f / 448.0f);
+        if (pow2) {
+            uint32_t byte;
+            ptx::ue8m0_ceil(sf, byte, inv);
+            sf = __uint_as_float(byte << 23);
+        }
         if (active) {
             uint2 packed;
             packed.x = ptx::float2_to_e4m3x2(__fmul_rn(v[0], inv), __fmul_rn(v[1], inv)) |
@@ -96,7 +103,7 @@ EP_DEVICE void quantize_row(const uint8_t* src, uint8_t* dst_fp8, float* dst_sf,
             packed.y = ptx::float2_to_e4m3x2(__fmul_rn(v[4], inv), __fmul_rn(v[5], inv)) |
                        (uint32_t(ptx::float2_to_e4m3x2(__fmul_rn(v[6], inv), __fmul_rn(v[7], inv))) << 16);
             *reinterpret_cast<uint2*>(dst_fp8 + col) = packed;
-            if ((lane & 15) == 0) dst_sf[col / 128] = __fmul_rn(amax, 1.0f / 448.0f);
+            if ((lane & 15) == 0) dst_sf[col / 128] = sf;
         }
     }
 }
@@ -370,7 +377,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
             __syncwarp();
             if (not ptx::mbarrier_wait(&mbar[S + (n & 1)], (n >> 1) & 1)) failed = true;
             quantize_row(src_stages + (n & 1) * src_row_bytes, stage, reinterpret_cast<float*>(stage + tl.sf_offset()),
-                         hidden, lane);
+                         hidden, lane, a.fused_quant == 2);
         } else if (a.sf_bytes > 0) {
             sf_pack_t* dst = reinterpret_cast<sf_pack_t*>(stage + tl.sf_offset());
             for (int p = lane; p < a.sf_bytes / 2; p += 32)

@@ -28,17 +28,6 @@
 
 namespace deep_ep::kernels {
 
-namespace gemm_detail {
-
-// 2^ceil(log2(x)) as (UE8M0 byte, exact reciprocal), for x > 0 finite and normal.
-EP_DEVICE void ue8m0_ceil(float x, uint32_t& byte, float& inv) {
-    const uint32_t bits = __float_as_uint(x);
-    byte = min(max((bits >> 23) + ((bits & 0x7fffffu) != 0), 1u), 253u);
-    inv = __uint_as_float((254u - byte) << 23);
-}
-
-}  // namespace gemm_detail
-
 __global__ void __launch_bounds__(kFp8ThreadsRegSplit, 1)
 grouped_gemm_fp8_hw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                            const __grid_constant__ GroupedGemmFp8Args a) {
@@ -173,12 +162,24 @@ grouped_gemm_fp8_hw_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             const int nb0 = t.n0 / 128, nb1 = swiglu ? (a.n / 2 + t.n0) / 128 : nb0 + 1;
             const uint32_t* sfb0 = reinterpret_cast<const uint32_t*>(a.sf_b_e8) + (size_t(t.expert) * (a.n / 128) + nb0) * sf_row_words;
             const uint32_t* sfb1 = reinterpret_cast<const uint32_t*>(a.sf_b_e8) + (size_t(t.expert) * (a.n / 128) + nb1) * sf_row_words;
-            const uint32_t* sfa[4];
+            // scales of A: UE8M0 bytes, or fp32 powers of two (what the dispatch kernel's power-of-two quantiser delivers),
+            // of which only the exponent byte is kept
+            const bool a_bytes_given = a.sf_a_e8 != nullptr;
+            size_t sfa_row[4];
             #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                sfa[j] = reinterpret_cast<const uint32_t*>(a.sf_a_e8) + size_t(min(t.row_base + t.m0 + lane + 32 * j, a.total_rows - 1)) * sf_row_words;
+            for (int j = 0; j < 4; ++j) sfa_row[j] = size_t(min(t.row_base + t.m0 + lane + 32 * j, a.total_rows - 1));
             for (int g = 0; g < num_sf_groups; ++g, fs = (fs + 1 == kFp8SfStages ? 0 : fs + 1), sf_phase ^= (fs == 0)) {
-                const uint4 wa = make_uint4(__ldg(sfa[0] + g), __ldg(sfa[1] + g), __ldg(sfa[2] + g), __ldg(sfa[3] + g));
+                uint32_t wa_[4];
+                #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (a_bytes_given) {
+                        wa_[j] = __ldg(reinterpret_cast<const uint32_t*>(a.sf_a_e8) + sfa_row[j] * sf_row_words + g);
+                    } else {
+                        const uint4 f = __ldg(reinterpret_cast<const uint4*>(a.sf_a + sfa_row[j] * num_k_blocks) + g);
+                        wa_[j] = ((f.x >> 23) & 0xffu) | (((f.y >> 23) & 0xffu) << 8) | (((f.z >> 23) & 0xffu) << 16) | (((f.w >> 23) & 0xffu) << 24);
+                    }
+                }
+                const uint4 wa = make_uint4(wa_[0], wa_[1], wa_[2], wa_[3]);
                 const uint32_t w0 = __ldg(sfb0 + g), w1 = __ldg(sfb1 + g);
                 bool ok = true;
                 if (lane == 0) ok = ptx::mbarrier_wait(&sf_empty_bar[fs], sf_phase ^ 1);
@@ -267,7 +268,7 @@ grouped_gemm_fp8_hw_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
                     amax = fmaxf(fmaxf(amax, amax_sm[par][half ^ 1][row]), 1e-4f);
                     uint32_t sf_byte;
                     float inv;
-                    ue8m0_ceil(__fmul_rn(amax, 1.0f / 448.0f), sf_byte, inv);
+                    ptx::ue8m0_ceil(__fmul_rn(amax, 1.0f / 448.0f), sf_byte, inv);
                     if (written) {
                         uint8_t* out = reinterpret_cast<uint8_t*>(a.d) + size_t(grow) * a.n_out + t.n0 + half * 64;
                         #pragma unroll

@@ -26,6 +26,8 @@ class MoEConfig:
     expert_alignment: int = 128
     fp8_dispatch: bool = False          # inference (`forward_fp8`): e4m3 dispatch (1x128 scales, quantised inside the
                                         # dispatch kernel) feeding block-scaled FP8 expert GEMMs
+    fp8_scales: str = 'fp32'            # 'fp32': scales amax / 448, promoted in registers by the GEMM; 'ue8m0': powers of two,
+                                        # applied by the tensor core (hidden and intermediate must be multiples of 512)
     expert_backend: str = 'grouped'     # 'grouped': hand-written grouped GEMM kernels, 'torch': per-expert torch.mm
     num_sms: int = 0
     init_std: float = 0.02
@@ -117,10 +119,12 @@ class MoELayer(nn.Module):
     # ------------------------------------------------------------------------------------------ FP8 inference
     def quantize_weights(self) -> None:
         """Store the routed experts' weights as e4m3 with one fp32 scale per 128 x 128 block (used by `forward_fp8`)."""
-        from ..ops.grouped_gemm import per_block_cast_to_fp8
+        from ..ops.grouped_gemm import per_block_cast_to_fp8, per_block_cast_to_fp8_ue8m0
+        assert self.config.fp8_scales in ('fp32', 'ue8m0')
+        cast = per_block_cast_to_fp8_ue8m0 if self.config.fp8_scales == 'ue8m0' else per_block_cast_to_fp8
         with torch.no_grad():
-            self._w1_fp8, self._w1_sf = per_block_cast_to_fp8(self.w_gate_up)
-            self._w2_fp8, self._w2_sf = per_block_cast_to_fp8(self.w_down)
+            self._w1_fp8, self._w1_sf = cast(self.w_gate_up)
+            self._w2_fp8, self._w2_sf = cast(self.w_down)
 
     @torch.no_grad()
     def forward_fp8(self, x: torch.Tensor) -> torch.Tensor:
@@ -136,7 +140,7 @@ class MoELayer(nn.Module):
         (recv_x, recv_sf), _, recv_w, handle, _ = self.buffer.dispatch(
             x, topk_idx=topk_idx, topk_weights=topk_weights.float().contiguous(), num_experts=cfg.num_experts,
             expert_alignment=cfg.expert_alignment, num_sms=cfg.num_sms, do_expand=True, do_zero_padding=True,
-            do_cpu_sync=True, fused_fp8_quant=True)
+            do_cpu_sync=True, fused_fp8_quant='ue8m0' if cfg.fp8_scales == 'ue8m0' else True)
         y = grouped_swiglu_ffn_fp8(recv_x, recv_sf, self._w1_fp8, self._w1_sf, self._w2_fp8, self._w2_sf,
                                    handle.psum_num_recv_tokens_per_expert, handle.num_unaligned_recv_tokens_per_expert,
                                    alignment=cfg.expert_alignment, row_scale=recv_w)

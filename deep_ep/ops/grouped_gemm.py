@@ -189,7 +189,7 @@ def per_token_cast_to_fp8_ue8m0(x: torch.Tensor):
     m, n = x.shape
     assert n % 128 == 0
     groups = x.float().reshape(m, n // 128, 128)
-    byte, scale = _ue8m0_ceil(groups.abs().amax(dim=2).clamp(min=1e-4) / 448.0)
+    byte, scale = _ue8m0_ceil(groups.abs().amax(dim=2).clamp(min=1e-4) * (1.0 / 448.0))
     q = (groups / scale.unsqueeze(2)).to(torch.float8_e4m3fn).reshape(m, n)
     return q.contiguous(), byte.contiguous()
 
@@ -202,7 +202,7 @@ def per_block_cast_to_fp8_ue8m0(w: torch.Tensor):
         parts = [per_block_cast_to_fp8_ue8m0(w[i]) for i in range(w.size(0))]
         return torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts])
     blocks = w.float().reshape(*lead, n // 128, 128, k // 128, 128)
-    byte, scale = _ue8m0_ceil(blocks.abs().amax(dim=(-3, -1), keepdim=True).clamp(min=1e-4) / 448.0)
+    byte, scale = _ue8m0_ceil(blocks.abs().amax(dim=(-3, -1), keepdim=True).clamp(min=1e-4) * (1.0 / 448.0))
     q = (blocks / scale).to(torch.float8_e4m3fn).reshape(*lead, n, k)
     return q.contiguous(), byte.reshape(*lead, n // 128, k // 128).contiguous()
 
@@ -233,7 +233,7 @@ def grouped_gemm_fp8_forward(x_fp8: torch.Tensor, x_sf: torch.Tensor, w_fp8: tor
         return y
     if quantize_output:
         y = torch.empty((rows, n // 2), dtype=torch.float8_e4m3fn, device=x_fp8.device)
-        y_sf = torch.empty((rows, n // 256), dtype=x_sf.dtype, device=x_fp8.device)
+        y_sf = torch.empty((rows, n // 256), dtype=w_sf.dtype, device=x_fp8.device)
         _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_SWIGLU, num_sms, alignment, row_scale, y_sf, FP8_REG_SPLIT)
         return y, y_sf
     y = torch.empty((rows, n // 2), dtype=torch.bfloat16, device=x_fp8.device)

@@ -264,7 +264,7 @@ class SimEPRuntime:
         num_tokens, num_topk = topk_idx.shape
         assert num_tokens <= num_max_tokens_per_rank and num_experts % self.num_ranks == 0
         if fused_fp8_quant:
-            x, scales = per_token_cast_to_fp8(x)
+            x, scales = per_token_cast_to_fp8(x, round_scale=int(fused_fp8_quant) == 2)
             sf = scales.contiguous().view(torch.int16)
         x_wire = x.view(torch.uint8) if x.dtype == torch.float8_e4m3fn else x
         inputs = [RankInput(*item) for item in self._gather((x_wire, sf, topk_idx, topk_weights))]

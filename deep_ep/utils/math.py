@@ -32,11 +32,13 @@ def calc_diff(x: torch.Tensor, y: torch.Tensor) -> float:
     return (1 - 2 * (xd * yd).sum() / (xd.square().sum() + yd.square().sum())).item()
 
 
-def per_token_cast_to_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def per_token_cast_to_fp8(x: torch.Tensor, round_scale: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Quantise `[m, n]` to e4m3 with one fp32 scale per 128 consecutive columns.
 
     `scale = max(amax, 1e-4) / 448`; the value stored is `x * (448 / max(amax, 1e-4))` rounded
     to e4m3. Returns `(x_fp8 [m, n], scales [m, ceil(n / 128)] fp32)`.
+    With `round_scale` every scale is rounded up to a power of two (`2^ceil(log2(amax * (1 / 448)))`, the UE8M0 form)
+    and the stored value is `x / scale`.
     """
     assert x.dim() == 2
     m, n = x.shape
@@ -44,6 +46,12 @@ def per_token_cast_to_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     xp = torch.nn.functional.pad(x, (0, n_pad - n)) if n_pad != n else x
     groups = xp.reshape(m, n_pad // SF_GROUP, SF_GROUP)
     amax = groups.abs().float().amax(dim=2).clamp(min=1e-4)
+    if round_scale:
+        bits = (amax * (1.0 / FP8_E4M3_MAX)).contiguous().view(torch.int32)
+        exponent = (((bits >> 23) & 0xff) + ((bits & 0x7fffff) != 0).int()).clamp(1, 253)
+        scale = (exponent << 23).view(torch.float32)
+        q = (groups.float() / scale.unsqueeze(2)).to(torch.float8_e4m3fn)
+        return q.reshape(m, n_pad)[:, :n].contiguous(), scale
     q = (groups * (FP8_E4M3_MAX / amax).unsqueeze(2)).to(torch.float8_e4m3fn)
     return q.reshape(m, n_pad)[:, :n].contiguous(), amax / FP8_E4M3_MAX
 

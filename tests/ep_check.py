@@ -238,3 +238,13 @@ def check_fused_quant(buffer: deep_ep.EPBuffer, num_tokens_max: int, hidden: int
     flat = slots[slots >= 0].long()
     assert torch.equal(fx.view(torch.uint8)[flat], rx.view(torch.uint8)[flat]), 'fused e4m3 payload differs'
     assert torch.equal(fsf.view(torch.int16)[flat], rsf[flat]), 'fused scale factors differ'
+
+    # power-of-two scales: the same comparison against the torch quantiser with `round_scale`
+    (px, psf), _, _, ph, _ = buffer.dispatch(x, fused_fp8_quant='ue8m0', **common)
+    q2, s2 = per_token_cast_to_fp8(x, round_scale=True)
+    (rx2, rsf2), _, _, _, _ = buffer.dispatch((q2, s2.view(torch.int16)), **common)
+    torch.cuda.synchronize()
+    buffer.runtime.check_status()
+    assert torch.equal(px.view(torch.uint8)[flat], rx2.view(torch.uint8)[flat]), 'power-of-two e4m3 payload differs'
+    assert torch.equal(psf.view(torch.int16)[flat], rsf2[flat]), 'power-of-two scale factors differ'
+    assert torch.equal(torch.log2(psf[flat]), torch.log2(psf[flat]).round()), 'scales are not powers of two'

@@ -69,12 +69,23 @@ def _moe_worker(rank, world_size, num_tokens, hidden, inter, num_experts, num_to
     a, b = y8.float(), ref.detach()
     diff = 1 - 2 * (a * b).sum() / ((a * a).sum() + (b * b).sum())
     assert diff.item() < 5e-3, f'fp8 forward differs: {diff.item()}'
+
+    # the same with power-of-two scales end to end: the dispatch kernel rounds its scales up to powers of two and the
+    # expert GEMMs let the tensor core apply them (UE8M0 block scales)
+    if hidden % 512 == 0 and inter % 512 == 0:
+        layer.config.fp8_scales = 'ue8m0'
+        layer.quantize_weights()
+        y8h = layer.forward_fp8(x.detach())
+        torch.cuda.synchronize()
+        a = y8h.float()
+        diff = 1 - 2 * (a * b).sum() / ((a * a).sum() + (b * b).sum())
+        assert diff.item() < 8e-3, f'hardware-scaled fp8 forward differs: {diff.item()}'
     layer.destroy()
 
 
 @pytest.mark.gpu
 def test_moe_layer_single_gpu(master_port):
-    run_distributed(_moe_worker, 1, master_port, 'nccl', (300, 512, 256, 8, 2))
+    run_distributed(_moe_worker, 1, master_port, 'nccl', (300, 512, 512, 8, 2))
 
 
 @pytest.mark.gpu
@@ -82,4 +93,4 @@ def test_moe_layer_single_gpu(master_port):
 def test_moe_layer_multi_gpu(master_port):
     world = min(torch.cuda.device_count(), 8)
     world -= world % 2
-    run_distributed(_moe_worker, world, master_port, 'nccl', (300, 512, 256, 16, 4))
+    run_distributed(_moe_worker, world, master_port, 'nccl', (300, 512, 512, 16, 4))
