@@ -170,6 +170,14 @@ def main():
         result['fp8_forward_rel_diff_vs_bf16'] = round(((y8.float() - y16.float()).norm() / y16.float().norm()).item(), 5)
         result['forward_bf16_ms'] = round(time_forward(ours, x, args.steps, args.warmup), 3)
         result['forward_fp8_ms'] = round(time_forward(ours.forward_fp8, x, args.steps, args.warmup), 3)
+        if args.hidden % 512 == 0 and args.intermediate % 512 == 0:
+            # power-of-two scales: quantised that way by the dispatch kernel, applied by the tensor core in the GEMMs
+            ours.config.fp8_scales = 'ue8m0'
+            ours.quantize_weights()
+            with torch.no_grad():
+                y8h = ours.forward_fp8(x)
+            result['fp8_ue8m0_forward_rel_diff_vs_bf16'] = round(((y8h.float() - y16.float()).norm() / y16.float().norm()).item(), 5)
+            result['forward_fp8_ue8m0_ms'] = round(time_forward(ours.forward_fp8, x, args.steps, args.warmup), 3)
     if 'baseline_ms' in result:
         result['speedup'] = round(result['baseline_ms'] / result['ours_ms'], 3)
     if rank == 0:
