@@ -29,6 +29,7 @@ def main():
     p.add_argument('--num-sms', type=int, nargs='+', default=[8, 16, 32])
     p.add_argument('--replays', type=int, default=100)
     p.add_argument('--profile', action='store_true', help='print per-kernel device times of eager iterations (analysis only)')
+    p.add_argument('--phase-trace', action='store_true', help='print the per-phase time breakdown of the four EP kernels')
     args = p.parse_args()
 
     rank, world = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1))
@@ -100,6 +101,29 @@ def main():
         if rank == 0:
             for name, prof in sorted(profiles.items(), key=lambda kv: -kv[1].dur_ns):
                 print(f'  {prof.dur_us:9.2f} us x{prof.num_calls}  {name[:100]}')
+    if args.phase_trace:
+        # where the time goes inside the four kernels: `%globaltimer` stamps at the phase boundaries (eager launches)
+        common = dict(num_experts=E, num_max_tokens_per_rank=T, expert_alignment=1, num_sms=args.num_sms[-1], do_expand=True,
+                      do_cpu_sync=False, async_with_compute_stream=True, defer_epilogue=True, fused_fp8_quant=True)
+
+        def traced():
+            (rx, rsf), _, rw, h = buffer.dispatch(x, topk_idx=topk_idx, topk_weights=topk_w, **common).current_stream_wait()
+            buffer.combine(y, h, topk_weights=rw, async_with_compute_stream=True, defer_epilogue=True).current_stream_wait()
+
+        buffer.enable_phase_trace()
+        for _ in range(5):
+            traced()
+        torch.cuda.synchronize()
+        dist.barrier()
+        traced()
+        trace = buffer.read_phase_trace()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, trace)
+        buffer.disable_phase_trace()
+        if rank == 0:
+            for r, tr in enumerate(gathered):
+                print(f'phase trace rank {r} (us): ' + json.dumps({k: ({p: round(v, 2) for p, v in val.items()} if isinstance(val, dict)
+                                                                      else round(val, 2)) for k, val in tr.items()}))
     if rank == 0:
         print(json.dumps({'bench': 'ep_low_latency_cuda_graph', 'n_gpus': world, 'tokens_per_rank': T, 'hidden': H,
                           'topk': K, 'experts': E, 'routing': 'skewed: N(0,1) logits + N(0,2) expert bias',

@@ -32,6 +32,13 @@ class EPBuffer : public BufferBase {
 
     layout::EPSignals* signals() const { return static_cast<layout::EPSignals*>(context->workspace); }
 
+    // optional phase trace: 4 kernels x kTraceSlots `%globaltimer` stamps (dispatch, expand, combine, reduce)
+    torch::Tensor phase_trace;
+    unsigned long long* trace_of(int kernel) const {
+        return phase_trace.defined() ? reinterpret_cast<unsigned long long*>(phase_trace.data_ptr<int64_t>()) + kernel * kernels::kTraceSlots
+                                     : nullptr;
+    }
+
     void release_without_barrier() override {
         if (host_counts != nullptr) cudaFreeHost(host_counts), host_counts = nullptr;
         if (context != nullptr) context->finalize(), context = nullptr;
@@ -251,6 +258,7 @@ public:
         args.cumulative_stats = cumulative_local_expert_recv_stats.has_value() ? cumulative_local_expert_recv_stats->data_ptr<int>() : nullptr;
         args.ws = signals(), args.buffer_offset = context->num_workspace_bytes, args.peers = context->peers;
         args.host = host_counts_device, args.timeout_ns = context->num_gpu_timeout_ns;
+        args.trace = trace_of(0);
         launch::dispatch(args, num_sms, stream);
 
         // ---- epilogue (possibly deferred): sizes, outputs, expand kernel. The closure keeps the
@@ -294,6 +302,7 @@ public:
 
             kernels::ExpandArgs e = {};
             e.ws = signals(), e.buffer = static_cast<const uint8_t*>(context->buffer), e.host = host_counts_device;
+            e.trace = trace_of(1);
             e.psum_rank = psum_rank.data_ptr<int>(), e.psum_expert = psum_expert.data_ptr<int>();
             e.num_unaligned = num_unaligned.data_ptr<int>();
             e.recv_x = static_cast<uint8_t*>(recv_x.data_ptr());
@@ -369,6 +378,7 @@ public:
         args.wait_arrival = barrier_in_prologue;
         args.ws = signals(), args.buffer_offset = context->num_workspace_bytes, args.peers = context->peers;
         args.host = host_counts_device, args.timeout_ns = context->num_gpu_timeout_ns;
+        args.trace = trace_of(2);
         launch::combine(args, num_sms, stream);
 
         const bool with_weights = topk_weights.has_value();
@@ -380,6 +390,7 @@ public:
                 combined_topk_weights = torch::empty({num_tokens, num_topk}, torch::TensorOptions().dtype(torch::kFloat32).device(device));
             kernels::CombineReduceArgs r = {};
             r.ws = signals(), r.buffer = static_cast<const uint8_t*>(context->buffer), r.host = host_counts_device;
+            r.trace = trace_of(3);
             r.topk_idx = topk_idx.data_ptr<int64_t>();
             r.bias_0 = bias_0.has_value() ? static_cast<const uint8_t*>(bias_0->data_ptr()) : nullptr;
             r.bias_1 = bias_1.has_value() ? static_cast<const uint8_t*>(bias_1->data_ptr()) : nullptr;
@@ -423,6 +434,15 @@ public:
         args.num_local_experts = num_local_experts;
         return args;
     }
+
+    // Phase trace (diagnostics): from now on the four EP kernels stamp `%globaltimer` at their phase boundaries into the
+    // returned int64 tensor `[4, kTraceSlots]` (rows: dispatch, expand, combine, reduce; slot meaning: the `*Trace`
+    // enums of `kernels/ep_args.hpp`). Each call overwrites the stamps of its kernels.
+    torch::Tensor enable_phase_trace() {
+        phase_trace = torch::zeros({4, kernels::kTraceSlots}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, c10::cuda::current_device()));
+        return phase_trace;
+    }
+    void disable_phase_trace() { phase_trace = torch::Tensor(); }
 
     EventHandle lb_prefetch_weights(const std::vector<torch::Tensor>& redundant_expert_weights,
                                     const std::vector<torch::Tensor>& expert_weights, const torch::Tensor& redundancy_mapping,

@@ -283,6 +283,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readonly("lb_storage", &EPBuffer::lb_storage)
         .def("dispatch", &EPBuffer::dispatch)
         .def("combine", &EPBuffer::combine)
+        .def("enable_phase_trace", &EPBuffer::enable_phase_trace)
+        .def("disable_phase_trace", &EPBuffer::disable_phase_trace)
         .def("lb_prefetch_weights", &EPBuffer::lb_prefetch_weights)
         .def("lb_reduce_grads", &EPBuffer::lb_reduce_grads)
         .def("check_status", &EPBuffer::check_status);

@@ -355,6 +355,40 @@ class EPBuffer(BufferBase):
         return combined_x, combined_topk_weights, event_overlap
 
     # ------------------------------------------------------------------------------------------
+    # ------------------------------------------------------------------------------------------ diagnostics
+    _TRACE_PHASES = {
+        'dispatch': ('count', 'entry_barrier', 'grid_sync', 'count_exchange', 'push', 'stores_complete', 'flags_and_tail'),
+        'expand': ('wait_arrival', 'layout', 'copy'),
+        'combine': ('entry_barrier', 'grid_sync', 'push', 'stores_complete', 'flags_and_tail'),
+        'reduce': ('wait_arrival', 'reduce'),
+    }
+
+    def enable_phase_trace(self) -> None:
+        """From now on the four EP kernels record time stamps at their phase boundaries (a few stores per kernel)."""
+        assert not self.is_simulated, 'the phase trace exists for the CUDA kernels only'
+        self._phase_trace = self.runtime.enable_phase_trace()
+
+    def disable_phase_trace(self) -> None:
+        self.runtime.disable_phase_trace()
+        self._phase_trace = None
+
+    def read_phase_trace(self) -> dict:
+        """Durations in microseconds of the phases of the most recent dispatch / expand / combine / reduce kernels, as
+        seen by CTA 0 (`flags_and_tail` ends when the last CTA has released the completion flags). Synchronises."""
+        assert getattr(self, '_phase_trace', None) is not None, 'call enable_phase_trace() first'
+        torch.cuda.synchronize()
+        stamps = self._phase_trace.cpu().tolist()
+        out = {}
+        for row, (kernel, phases) in zip(stamps, self._TRACE_PHASES.items()):
+            out[kernel] = {name: (row[i + 1] - row[i]) / 1e3 for i, name in enumerate(phases) if row[i] and row[i + 1]}
+            last = max(row)
+            if row[0] and last:
+                out[kernel]['total'] = (last - row[0]) / 1e3
+        order = [(name, stamps[i][0]) for i, name in enumerate(self._TRACE_PHASES) if stamps[i][0]]
+        for (a, ta), (b, tb) in zip(order, order[1:]):
+            out[f'{a}_start_to_{b}_start'] = (tb - ta) / 1e3
+        return out
+
     def lb_get_theoretical_num_sms(self) -> int:
         return _C.get_num_sms()
 

@@ -9,6 +9,12 @@
 
 namespace deep_ep::dev {
 
+// Phase stamp for the optional kernel trace (one thread calls it per phase; no-op without a trace buffer).
+EP_DEVICE void trace_point(unsigned long long* trace, int slot) {
+    if (trace != nullptr) trace[slot] = ptx::globaltimer_ns();
+}
+
+
 struct Deadline {
     unsigned long long end_ns;
     EP_DEVICE explicit Deadline(long long timeout_ns) : end_ns(ptx::globaltimer_ns() + static_cast<unsigned long long>(timeout_ns)) {}

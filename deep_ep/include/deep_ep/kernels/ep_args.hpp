@@ -7,6 +7,15 @@
 
 namespace deep_ep::kernels {
 
+// Phase trace: when a kernel gets a non-null `trace`, single threads of CTA 0 (and of the CTA that finishes last) store
+// `%globaltimer` at the phase boundaries named below; the host subtracts neighbouring stamps. Each kernel owns 16 slots.
+constexpr int kTraceSlots = 16;
+enum DispatchTrace : int { kTrDispStart = 0, kTrDispCounted, kTrDispEntryBarrier, kTrDispGridSync, kTrDispCountsExchanged,
+                           kTrDispPushed, kTrDispStoresDone, kTrDispEnd };
+enum ExpandTrace : int { kTrExpStart = 0, kTrExpArrived, kTrExpLaidOut, kTrExpEnd };
+enum CombineTrace : int { kTrCombStart = 0, kTrCombEntryBarrier, kTrCombGridSync, kTrCombPushed, kTrCombStoresDone, kTrCombEnd };
+enum ReduceTrace : int { kTrRedStart = 0, kTrRedArrived, kTrRedEnd };
+
 struct DispatchArgs {
     // inputs
     const uint8_t* x;               // [T, row_bytes]: wire bytes, or BF16 source rows when fused_quant
@@ -29,6 +38,7 @@ struct DispatchArgs {
     layout::EPHostCounts* host;
     long long timeout_ns;
     int num_warps, num_stages;      // pusher warps per CTA, message stages per warp
+    unsigned long long* trace;      // optional [kTraceSlots] `%globaltimer` stamps of the phases (CTA 0 and the last CTA), or nullptr
 };
 
 struct ExpandArgs {
@@ -49,6 +59,7 @@ struct ExpandArgs {
     int cached, do_zero_padding, wait_arrival;
     long long timeout_ns;
     int num_warps, num_stages;
+    unsigned long long* trace;        // optional phase stamps, see DispatchArgs
 };
 
 struct CombineArgs {
@@ -65,6 +76,7 @@ struct CombineArgs {
     layout::EPHostCounts* host;
     long long timeout_ns;
     int num_warps, num_stages;
+    unsigned long long* trace;        // optional phase stamps, see DispatchArgs
 };
 
 struct CombineReduceArgs {
@@ -80,6 +92,7 @@ struct CombineReduceArgs {
     int rank, num_ranks;
     int wait_arrival;
     long long timeout_ns;
+    unsigned long long* trace;        // optional phase stamps, see DispatchArgs
 };
 
 namespace dispatch_detail {

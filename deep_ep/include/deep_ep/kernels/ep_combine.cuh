@@ -155,6 +155,8 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
 
     if (not dev::healthy(cs)) return;
     const unsigned epoch = a.ws->combine_epoch + 1;
+    const bool tracer = cta == 0 and threadIdx.x == 0;
+    if (tracer) dev::trace_point(a.trace, kTrCombStart);
     if (threadIdx.x == 0) {
         for (int i = 0; i < W * S; ++i) ptx::mbarrier_init(reinterpret_cast<uint64_t*>(base) + i, 1);
         ptx::fence_mbarrier_init();
@@ -164,7 +166,9 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
 
     // Entry barrier: every peer has finished the dispatch epilogue that read the shared buffer.
     if (cta == 0 and warp == 0) dev::rank_barrier_warp(cs, hs, a.peers, a.timeout_ns, kSiteEntryBarrier);
+    if (tracer) dev::trace_point(a.trace, kTrCombEntryBarrier);
     if (not dev::grid_sync(cs, hs, num_ctas, a.timeout_ns, rank, kSiteGridSync)) return;
+    if (tracer) dev::trace_point(a.trace, kTrCombGridSync);
 
     const int gw = cta * W + warp, num_gw = num_ctas * W;
     const int meta_cols = k + 2;
@@ -230,10 +234,12 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
     }
 
     // completion: all stores performed, then one flag per destination from the last CTA
+    if (tracer) dev::trace_point(a.trace, kTrCombPushed);
     ptx::bulk_wait<0>();
     ptx::fence_proxy_async();
     __threadfence_system();
     __syncthreads();
+    if (tracer) dev::trace_point(a.trace, kTrCombStoresDone);
     if (warp == 0) {
         unsigned last = 0;
         if (lane == 0) {
@@ -254,6 +260,8 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
                         dev::report_status(cs, hs, kStatusArrivalTimeout, rank, s, kSiteArrival, epoch, w);
                 }
             }
+            __syncwarp();
+            if (lane == 0) dev::trace_point(a.trace, kTrCombEnd);       // the CTA that finished last
         }
     }
 }
@@ -272,6 +280,8 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
 
     if (not dev::healthy(cs)) return;
     const unsigned epoch = a.ws->combine_epoch;
+    const bool tracer = blockIdx.x == 0 and threadIdx.x == 0;
+    if (tracer) dev::trace_point(a.trace, kTrRedStart);
     if (a.wait_arrival and warp == 0) {
         const dev::Deadline deadline(a.timeout_ns);
         for (int s = lane; s < a.num_ranks; s += 32) {
@@ -282,6 +292,7 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
     }
     __syncthreads();
     if (not dev::healthy(cs)) return;
+    if (tracer) dev::trace_point(a.trace, kTrRedArrived);
 
     const int chunks = a.hidden_bytes / 16;
     for (int t = blockIdx.x * warps_per_cta + warp; t < a.num_tokens; t += gridDim.x * warps_per_cta) {
@@ -344,6 +355,9 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
             }
         }
     }
+    // CTA 0's share is done (the other CTAs work on as many tokens each, give or take one)
+    __syncthreads();
+    if (tracer) dev::trace_point(a.trace, kTrRedEnd);
 }
 
 }  // namespace deep_ep::kernels

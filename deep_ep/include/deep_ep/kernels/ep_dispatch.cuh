@@ -132,6 +132,8 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
 
     if (not dev::healthy(cs)) return;
     const unsigned epoch = a.ws->dispatch_epoch + 1;
+    const bool tracer = cta == 0 and threadIdx.x == 0;
+    if (tracer) dev::trace_point(a.trace, kTrDispStart);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < W * (S + 2); ++i) ptx::mbarrier_init(&sm.mbar[i], 1);
@@ -183,9 +185,13 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
     // ------------------------------------------------------------------ entry barrier + grid sync
     // Every rank has finished consuming the previous contents of the receive buffers once the
     // barrier completes; no remote write is issued before the grid sync below.
-    if (cta == 0 and is_aux)
+    if (tracer) dev::trace_point(a.trace, kTrDispCounted);
+    if (cta == 0 and is_aux) {
         dev::rank_barrier_warp(cs, hs, a.peers, a.timeout_ns, kSiteEntryBarrier);
+        if (lane == 0) dev::trace_point(a.trace, kTrDispEntryBarrier);
+    }
     if (not dev::grid_sync(cs, hs, num_ctas, a.timeout_ns, rank, kSiteGridSync1)) return;
+    if (tracer) dev::trace_point(a.trace, kTrDispGridSync);
 
     // ------------------------------------------------------------------ aux warp: count exchange
     if (is_aux) {
@@ -279,6 +285,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
             a.host->num_recv_tokens = layout::pack_tagged(epoch, num_recv_tokens);
             __threadfence_system();
         }
+        if (lane == 0) dev::trace_point(a.trace, kTrDispCountsExchanged);
         return;
     }
 
@@ -412,10 +419,12 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
     }
 
     // ------------------------------------------------------------------ completion
+    if (tracer) dev::trace_point(a.trace, kTrDispPushed);
     ptx::bulk_wait<0>();
     ptx::fence_proxy_async();
     __threadfence_system();
     ptx::named_barrier(1, num_pushers);
+    if (tracer) dev::trace_point(a.trace, kTrDispStoresDone);
     if (warp == 0) {
         unsigned last = 0;
         if (lane == 0) {
@@ -436,6 +445,8 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
                         dev::report_status(cs, hs, kStatusArrivalTimeout, rank, s, kSiteArrival, epoch, w);
                 }
             }
+            __syncwarp();
+            if (lane == 0) dev::trace_point(a.trace, kTrDispEnd);       // the CTA that finished last
         }
     }
 }

@@ -60,6 +60,8 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
 
     if (not dev::healthy(cs)) return;
     const unsigned epoch = a.ws->dispatch_epoch;
+    const bool tracer = cta == 0 and threadIdx.x == 0;
+    if (tracer) dev::trace_point(a.trace, kTrExpStart);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < W * S; ++i) ptx::mbarrier_init(&mbar_all[i], 1);
@@ -80,6 +82,7 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
     for (int e = threadIdx.x; e < num_local_experts; e += blockDim.x) psum_sm[e] = a.psum_expert[e];
     __syncthreads();
     if (not dev::healthy(cs)) return;
+    if (tracer) dev::trace_point(a.trace, kTrExpArrived);
 
     const int num_recv = min(psum_rank_smem[a.num_ranks - 1], a.num_metadata_rows);
     const int per_cta = math::ceil_div(num_recv, num_ctas);
@@ -112,6 +115,7 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
             a.ws->cta_expert_count[cta][e] = total;
         }
         if (not dev::grid_sync(cs, hs, num_ctas, a.timeout_ns, a.rank, kSiteGridSync)) return;
+        if (tracer) dev::trace_point(a.trace, kTrExpLaidOut);
         // rows written by earlier CTAs: one warp per expert, lanes split the CTAs so that the loads overlap
         for (int e = warp; e < num_local_experts; e += W) {
             int partial = 0;
@@ -264,6 +268,9 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
             }
         }
     }
+    // CTA 0's share is done (every CTA copies the same number of messages, give or take one)
+    __syncthreads();
+    if (tracer) dev::trace_point(a.trace, kTrExpEnd);
 }
 
 }  // namespace deep_ep::kernels

@@ -145,9 +145,6 @@ class GroupedLinear(torch.autograd.Function):
                     if c:
                         acc[e].addmm_(dy[start:start + c].float().t(), x[start:start + c].float())
             dw = None if main_grad is not None else (acc if acc.dtype == w.dtype else acc.to(w.dtype))
-        if dx is not None:
-            # rows that belong to no expert (alignment padding) carry no gradient
-            pass
         return dx, dw, None, None, None
 
 
