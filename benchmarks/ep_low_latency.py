@@ -29,6 +29,7 @@ def main():
     p.add_argument('--num-sms', type=int, nargs='+', default=[8, 16, 32])
     p.add_argument('--replays', type=int, default=100)
     p.add_argument('--profile', action='store_true', help='print per-kernel device times of eager iterations (analysis only)')
+    p.add_argument('--warp-cooperation', action='store_true', help='let several warps share one row in the combine kernels')
     p.add_argument('--phase-trace', action='store_true', help='print the per-phase time breakdown of the four EP kernels')
     args = p.parse_args()
 
@@ -48,6 +49,8 @@ def main():
     top_logits, topk_idx = logits.topk(K, dim=-1)
     topk_w = torch.softmax(top_logits, dim=-1).float()
 
+    if args.warp_cooperation:
+        deep_ep._C.set_warp_cooperation(True)
     buffer = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=T, hidden=H, num_topk=K, explicitly_destroy=True)
     results = []
     for num_sms in args.num_sms:

@@ -379,6 +379,8 @@ public:
         args.ws = signals(), args.buffer_offset = context->num_workspace_bytes, args.peers = context->peers;
         args.host = host_counts_device, args.timeout_ns = context->num_gpu_timeout_ns;
         args.trace = trace_of(2);
+        const bool coop = Runtime::get().get_warp_cooperation();
+        args.coop = coop;
         launch::combine(args, num_sms, stream);
 
         const bool with_weights = topk_weights.has_value();
@@ -390,7 +392,7 @@ public:
                 combined_topk_weights = torch::empty({num_tokens, num_topk}, torch::TensorOptions().dtype(torch::kFloat32).device(device));
             kernels::CombineReduceArgs r = {};
             r.ws = signals(), r.buffer = static_cast<const uint8_t*>(context->buffer), r.host = host_counts_device;
-            r.trace = trace_of(3);
+            r.trace = trace_of(3), r.coop = coop;
             r.topk_idx = topk_idx.data_ptr<int64_t>();
             r.bias_0 = bias_0.has_value() ? static_cast<const uint8_t*>(bias_0->data_ptr()) : nullptr;
             r.bias_1 = bias_1.has_value() ? static_cast<const uint8_t*>(bias_1->data_ptr()) : nullptr;

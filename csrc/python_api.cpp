@@ -212,6 +212,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("set_arch", [](const std::string& a) { Runtime::get().set_arch(a); });
     m.def("set_barrier_in_prologue", [](bool v) { return Runtime::get().set_barrier_in_prologue(v); });
     m.def("get_barrier_in_prologue", [] { return Runtime::get().get_barrier_in_prologue(); });
+    m.def("set_warp_cooperation", [](bool v) { return Runtime::get().set_warp_cooperation(v); });
+    m.def("get_warp_cooperation", [] { return Runtime::get().get_warp_cooperation(); });
     // names under which the reference exposes the same knobs (`csrc/runtime/jit.hpp:86-116` there): a "vector core"
     // corresponds to an SM here, there is no separate cube-core pool, and the architecture string is "sm_100a"
     m.def("get_num_vec_cores", [] { return Runtime::get().get_num_sms(); });

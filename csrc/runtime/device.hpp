@@ -19,6 +19,7 @@ class Runtime {
     int smem_per_block = 0;
     int num_sms_override = 0;    // user override of the default SM budget (0 = automatic)
     bool barrier_in_prologue = false;
+    bool warp_cooperation = false;      // decode-sized EP calls: several warps share one row / token (see ep_combine.cuh)
     std::string arch = "sm_100a";
 
     void query() {
@@ -56,6 +57,8 @@ public:
 
     bool get_barrier_in_prologue() const { return barrier_in_prologue; }
     bool set_barrier_in_prologue(bool v) { std::swap(v, barrier_in_prologue); return v; }
+    bool get_warp_cooperation() const { return warp_cooperation; }
+    bool set_warp_cooperation(bool v) { std::swap(v, warp_cooperation); return v; }
 };
 
 }  // namespace deep_ep

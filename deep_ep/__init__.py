@@ -22,6 +22,9 @@ def init_jit() -> None:
 
 
 init_jit()
+# EP_WARP_COOPERATION=1: decode-sized combine calls let several warps share one row (`_C.set_warp_cooperation`)
+if os.environ.get('EP_WARP_COOPERATION', '0') == '1':
+    _C.set_warp_cooperation(True)
 
 from . import comm
 from .comm import (destroy_all_managed_comm, destroy_all_managed_hccl_comm, get_logical_domain_size,

@@ -77,6 +77,7 @@ struct CombineArgs {
     long long timeout_ns;
     int num_warps, num_stages;
     unsigned long long* trace;        // optional phase stamps, see DispatchArgs
+    int coop;                         // 1: when rows are scarce, several warps of a CTA share a row (decode-sized calls)
 };
 
 struct CombineReduceArgs {
@@ -93,6 +94,7 @@ struct CombineReduceArgs {
     int wait_arrival;
     long long timeout_ns;
     unsigned long long* trace;        // optional phase stamps, see DispatchArgs
+    int coop;                         // 1: when tokens are scarce, several warps share a token
 };
 
 namespace dispatch_detail {

@@ -47,8 +47,8 @@ EP_DEVICE int nth_set_bit(unsigned m, int q) { return __fns(m, 0, q + 1); }
 // into a bf16 row in shared memory. Several 16-byte chunks per lane are loaded before the first add so that
 // enough requests are in flight to cover memory latency.
 template <int kSlots, int kChunks>
-EP_DEVICE void reduce_rows_impl(const uint8_t* x, int hidden_bytes, int chunks, const int (&sl)[kSlots], uint8_t* stage, int lane) {
-    for (int c0 = lane; c0 < chunks; c0 += 32 * kChunks) {
+EP_DEVICE void reduce_rows_impl(const uint8_t* x, int hidden_bytes, int c_begin, int chunks, const int (&sl)[kSlots], uint8_t* stage, int lane) {
+    for (int c0 = c_begin + lane; c0 < chunks; c0 += 32 * kChunks) {
         int4 v[kChunks][kSlots];
         #pragma unroll
         for (int i = 0; i < kChunks; ++i)
@@ -67,7 +67,8 @@ EP_DEVICE void reduce_rows_impl(const uint8_t* x, int hidden_bytes, int chunks, 
     }
 }
 
-EP_DEVICE void reduce_rows(const uint8_t* x, int hidden_bytes, int chunks, int my_slot, unsigned valid, int count,
+// Works on the 16-byte chunks [c_begin, chunks) of the row (several warps may split a row between them).
+EP_DEVICE void reduce_rows(const uint8_t* x, int hidden_bytes, int c_begin, int chunks, int my_slot, unsigned valid, int count,
                            uint8_t* stage, int lane) {
     if (count <= 4) {
         int sl[4];
@@ -76,18 +77,18 @@ EP_DEVICE void reduce_rows(const uint8_t* x, int hidden_bytes, int chunks, int m
             sl[u] = u < count ? __shfl_sync(0xffffffffu, my_slot, nth_set_bit(valid, min(u, count - 1))) : -1;
         if (count == 2) {
             const int s2[2] = {sl[0], sl[1]};
-            reduce_rows_impl<2, 4>(x, hidden_bytes, chunks, s2, stage, lane);
+            reduce_rows_impl<2, 4>(x, hidden_bytes, c_begin, chunks, s2, stage, lane);
         } else {
-            reduce_rows_impl<4, 4>(x, hidden_bytes, chunks, sl, stage, lane);
+            reduce_rows_impl<4, 4>(x, hidden_bytes, c_begin, chunks, sl, stage, lane);
         }
     } else if (count <= 8) {
         int sl[8];
         #pragma unroll
         for (int u = 0; u < 8; ++u)
             sl[u] = u < count ? __shfl_sync(0xffffffffu, my_slot, nth_set_bit(valid, min(u, count - 1))) : -1;
-        reduce_rows_impl<8, 2>(x, hidden_bytes, chunks, sl, stage, lane);
+        reduce_rows_impl<8, 2>(x, hidden_bytes, c_begin, chunks, sl, stage, lane);
     } else {
-        for (int base = 0; base < chunks; base += 32) {       // warp-uniform trip count: shuffles inside
+        for (int base = c_begin; base < chunks; base += 32) {       // warp-uniform trip count: shuffles inside
             const int c = base + lane;
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int u = 0; u < count; ++u) {
@@ -103,8 +104,8 @@ EP_DEVICE void reduce_rows(const uint8_t* x, int hidden_bytes, int chunks, int m
 // bf16. `kChunks` 16-byte chunks per lane are in flight before the first add.
 template <int kParts, int kChunks>
 EP_DEVICE void reduce_token(const uint8_t* const (&part)[kParts], const uint8_t* b0, const uint8_t* b1, uint8_t* out,
-                            int chunks, int lane) {
-    for (int c0 = lane; c0 < chunks; c0 += 32 * kChunks) {
+                            int c_begin, int chunks, int lane) {
+    for (int c0 = c_begin + lane; c0 < chunks; c0 += 32 * kChunks) {
         int4 v[kChunks][kParts], vb0[kChunks], vb1[kChunks];
         #pragma unroll
         for (int i = 0; i < kChunks; ++i) {
@@ -177,7 +178,62 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
     int num_loads[4] = {0, 0, 0, 0};   // bulk loads issued per stage (mbarrier parity)
     bool failed = false;
 
-    for (int q = 0; q < num_ranks and not failed; ++q) {
+    // Decode-sized calls leave most warps without a row while the few busy ones walk through a row in a dozen
+    // dependent round trips. With `coop`, P warps of a CTA (a power of two, the same in the whole CTA) share every
+    // row: each reduces 1/P of the 16-byte chunks into the group's stage and the group's first warp sends it.
+    int P = 1;
+    if (a.coop) {
+        const int total_rows = min(psum_rank_smem[num_ranks - 1], a.num_metadata_rows);
+        while (2 * P <= W and W % (2 * P) == 0 and int64_t(total_rows) * (2 * P) <= num_gw) P *= 2;
+    }
+    if (P > 1) {
+        const int group = warp / P, part = warp % P, groups_per_cta = W / P;
+        const int gg = cta * groups_per_cta + group, num_gg = num_ctas * groups_per_cta;
+        uint8_t* group_stages = base + math::align<int64_t>(int64_t(W) * S * 8, 128) + int64_t(group * P) * S * token_bytes;
+        const int c_begin = chunks * part / P, c_end = chunks * (part + 1) / P;
+        const int bar_id = 1 + group, bar_threads = 32 * P;
+        for (int q = 0; q < num_ranks; ++q) {
+            const int s = (rank + 1 + gg + q) % num_ranks;
+            const int begin = s == 0 ? 0 : psum_rank_smem[s - 1];
+            const int end = min(psum_rank_smem[s], a.num_metadata_rows);
+            for (int row = begin + gg; row < end; row += num_gg, ++n) {
+                // every warp of the group reads the same metadata and therefore takes the same branches
+                uint8_t* stage = group_stages + (n % S) * token_bytes;
+                const int my_slot = lane < k ? a.recv_src_metadata[int64_t(row) * meta_cols + lane] : -1;
+                int src_global = 0, master = 0;
+                if (lane == 0) {
+                    src_global = a.recv_src_metadata[int64_t(row) * meta_cols + k];
+                    master = a.recv_src_metadata[int64_t(row) * meta_cols + k + 1];
+                }
+                src_global = __shfl_sync(0xffffffffu, src_global, 0);
+                master = __shfl_sync(0xffffffffu, master, 0);
+                const unsigned valid = __ballot_sync(0xffffffffu, my_slot >= 0);
+                const int count = __popc(valid);
+                const int token = src_global - s * a.num_max_tokens;
+                if (count == 0 or token < 0 or token >= a.num_max_tokens or master < 0) {
+                    if (part == 0) ptx::bulk_commit();
+                    continue;
+                }
+                if (part == 0) dispatch_detail::wait_read_pending(S - 1);     // the store issued S rows ago has read the stage
+                ptx::named_barrier(bar_id, bar_threads);
+                reduce_rows(a.x, a.hidden_bytes, c_begin, c_end, my_slot, valid, count, stage, lane);
+                if (part == 0 and lane < k)
+                    reinterpret_cast<float*>(stage + tl.weight_offset())[lane] =
+                        (my_slot >= 0 and a.topk_weights != nullptr) ? a.topk_weights[my_slot] : 0.f;
+                ptx::fence_proxy_async_smem();
+                ptx::named_barrier(bar_id, bar_threads);
+                if (part == 0) {
+                    if (lane == 0) {
+                        const int dst_group = num_ranks >= k ? master : rank;
+                        ptx::bulk_store(a.peers.base[s] + a.buffer_offset + bl.offset(dst_group, token), stage, token_bytes);
+                    }
+                    ptx::bulk_commit();
+                }
+            }
+        }
+    }
+
+    for (int q = 0; q < num_ranks and not failed and P == 1; ++q) {
         // visit sources in an order rotated by rank and warp so that, at any moment, the ranks of
         // the node spread their pushes over all destinations instead of converging on one
         const int s = (rank + 1 + gw + q) % num_ranks;
@@ -210,7 +266,7 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
                     ptx::bulk_load(stage, a.x + int64_t(slot) * a.hidden_bytes, a.hidden_bytes, &mbar[stage_idx]);
                 }
             } else {
-                reduce_rows(a.x, a.hidden_bytes, chunks, my_slot, valid, count, stage, lane);
+                reduce_rows(a.x, a.hidden_bytes, 0, chunks, my_slot, valid, count, stage, lane);
             }
             if (lane < k)
                 reinterpret_cast<float*>(stage + tl.weight_offset())[lane] =
@@ -295,7 +351,14 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
     if (tracer) dev::trace_point(a.trace, kTrRedArrived);
 
     const int chunks = a.hidden_bytes / 16;
-    for (int t = blockIdx.x * warps_per_cta + warp; t < a.num_tokens; t += gridDim.x * warps_per_cta) {
+    // With `coop` and fewer tokens than warps, P consecutive warps share a token (1 / P of the chunks each).
+    const int total_warps = gridDim.x * warps_per_cta;
+    int P = 1;
+    if (a.coop)
+        while (P < 8 and int64_t(a.num_tokens) * (2 * P) <= total_warps) P *= 2;
+    for (int unit = blockIdx.x * warps_per_cta + warp; unit < a.num_tokens * P; unit += total_warps) {
+        const int t = unit / P, part_idx = unit % P;
+        const int c_begin = chunks * part_idx / P, c_end = chunks * (part_idx + 1) / P;
         // lane j owns top-k position j
         int r = -1;
         if (lane < k) {
@@ -323,23 +386,23 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
         uint8_t* out = a.combined_x + int64_t(t) * a.hidden_bytes;
         if (count <= 4) {
             const uint8_t* p4[4] = {part[0], part[1], part[2], part[3]};
-            reduce_token<4, 4>(p4, b0, b1, out, chunks, lane);
+            reduce_token<4, 4>(p4, b0, b1, out, c_begin, c_end, lane);
         } else if (count <= kUnroll) {
-            reduce_token<kUnroll, 2>(part, b0, b1, out, chunks, lane);
+            reduce_token<kUnroll, 2>(part, b0, b1, out, c_begin, c_end, lane);
         } else {
-            for (int base = 0; base < chunks; base += 32) {      // warp-uniform trip count: shuffles inside
+            for (int base = c_begin; base < c_end; base += 32) {      // warp-uniform trip count: shuffles inside
                 const int c = base + lane;
                 float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                if (c < chunks and b0 != nullptr) accumulate(acc, ptx::ld_nc_v4(b0 + c * 16));
-                if (c < chunks and b1 != nullptr) accumulate(acc, ptx::ld_nc_v4(b1 + c * 16));
+                if (c < c_end and b0 != nullptr) accumulate(acc, ptx::ld_nc_v4(b0 + c * 16));
+                if (c < c_end and b1 != nullptr) accumulate(acc, ptx::ld_nc_v4(b1 + c * 16));
                 for (int u = 0; u < count; ++u) {
                     const int g = __shfl_sync(0xffffffffu, group, nth_set_bit(masters, u));
-                    if (c < chunks) accumulate(acc, ptx::ld_v4(a.buffer + bl.offset(g, t) + c * 16));
+                    if (c < c_end) accumulate(acc, ptx::ld_v4(a.buffer + bl.offset(g, t) + c * 16));
                 }
-                if (c < chunks) ptx::st_na_v4(out + c * 16, pack(acc));
+                if (c < c_end) ptx::st_na_v4(out + c * 16, pack(acc));
             }
         }
-        if (a.combined_topk_weights != nullptr) {
+        if (a.combined_topk_weights != nullptr and part_idx == 0) {
             // position j reads its weight from the partial produced by the rank that owns expert j
             int master_group = -1;
             for (int j = 0; j < k; ++j) {
