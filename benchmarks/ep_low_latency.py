@@ -29,6 +29,8 @@ def main():
     p.add_argument('--num-sms', type=int, nargs='+', default=[8, 16, 32])
     p.add_argument('--replays', type=int, default=100)
     p.add_argument('--profile', action='store_true', help='print per-kernel device times of eager iterations (analysis only)')
+    p.add_argument('--layers', type=int, default=0,
+                   help='also capture this many dispatch + combine pairs in one graph and report the time per pair')
     p.add_argument('--warp-cooperation', action='store_true', help='let several warps share one row in the combine kernels')
     p.add_argument('--phase-trace', action='store_true', help='print the per-phase time breakdown of the four EP kernels')
     args = p.parse_args()
@@ -89,8 +91,33 @@ def main():
         t = torch.tensor([d_us, c_us], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         num_recv = int(handle.psum_num_recv_tokens_per_rank[-1])
-        results.append({'num_sms': num_sms, 'dispatch_us': round(t[0].item(), 2), 'combine_us': round(t[1].item(), 2),
-                        'recv_tokens_rank0': num_recv})
+        entry = {'num_sms': num_sms, 'dispatch_us': round(t[0].item(), 2), 'combine_us': round(t[1].item(), 2),
+                 'recv_tokens_rank0': num_recv}
+        if args.layers > 0:
+            # a decode step as a serving engine captures it: `layers` dispatch + combine pairs in ONE graph, so the cost of
+            # launching a graph is paid once per step and not once per operation
+            g_step = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g_step, stream=side):
+                    for _ in range(args.layers):
+                        (rx2, _), _, rw2, h2 = buffer.dispatch(x, topk_idx=topk_idx, topk_weights=topk_w, **common).current_stream_wait()
+                        buffer.combine(y, h2, topk_weights=rw2, async_with_compute_stream=True, defer_epilogue=True).current_stream_wait()
+            torch.cuda.synchronize()
+            dist.barrier()
+            step_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.replays)]
+            for i in range(3 + args.replays):
+                a_ev, b_ev = step_ev[max(i - 3, 0)]
+                a_ev.record()
+                g_step.replay()
+                b_ev.record()
+            torch.cuda.synchronize()
+            buffer.runtime.check_status()
+            per_pair = torch.tensor([sum(a_ev.elapsed_time(b_ev) for a_ev, b_ev in step_ev) / len(step_ev) * 1e3 / args.layers],
+                                    device=dev, dtype=torch.float64)
+            dist.all_reduce(per_pair, op=dist.ReduceOp.MAX)
+            entry['dispatch_plus_combine_us_in_one_graph'] = round(per_pair.item(), 2)
+            entry['layers_per_graph'] = args.layers
+        results.append(entry)
     if args.profile:
         from deep_ep.utils.testing import bench_kineto
         common = dict(num_experts=E, num_max_tokens_per_rank=T, expert_alignment=1, num_sms=args.num_sms[-1], do_expand=True,
