@@ -130,6 +130,8 @@ def main():
     p.add_argument('--steps', type=int, default=10)
     p.add_argument('--warmup', type=int, default=3)
     p.add_argument('--skip-baseline', action='store_true')
+    p.add_argument('--fuse-combine', action='store_true',
+                   help='let the second expert GEMM store single-row tokens straight into the combine landing slots of their owners')
     p.add_argument('--forward-fp8', action='store_true',
                    help='also time the inference forward: BF16 path against the FP8 path (e4m3 dispatch + block-scaled FP8 GEMMs)')
     args = p.parse_args()
@@ -142,12 +144,13 @@ def main():
     dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
     torch.manual_seed(7 + rank)
     cfg = MoEConfig(hidden=args.hidden, intermediate=args.intermediate, num_experts=args.num_experts, num_topk=args.num_topk,
-                    num_shared_experts=1, num_max_tokens_per_rank=args.num_tokens, expert_alignment=128)
+                    num_shared_experts=1, num_max_tokens_per_rank=args.num_tokens, expert_alignment=128,
+                    fuse_combine=args.fuse_combine)
     ours = MoELayer(dist.group.WORLD, cfg, device=dev)
     x = torch.randn(args.num_tokens, args.hidden, device=dev, dtype=torch.bfloat16, requires_grad=True)
 
     result = {'bench': 'moe_layer_fwd_bwd', 'n_gpus': world, 'tokens_per_rank': args.num_tokens, 'hidden': args.hidden,
-              'intermediate': args.intermediate, 'experts': args.num_experts, 'topk': args.num_topk, 'dtype': 'bf16'}
+              'intermediate': args.intermediate, 'experts': args.num_experts, 'topk': args.num_topk, 'dtype': 'bf16', 'fuse_combine': args.fuse_combine}
     if not args.skip_baseline:
         base = BaselineMoELayer(ours).to(dev)
         with torch.no_grad():                      # same function, different plumbing: outputs must agree

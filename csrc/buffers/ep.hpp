@@ -339,7 +339,8 @@ public:
                             const torch::Tensor& psum_num_recv_tokens_per_rank,
                             int num_experts, int num_max_tokens_per_rank, int num_sms,
                             const std::optional<EventHandle>& previous_event,
-                            bool async_with_compute_stream, bool allocate_on_comm_stream, bool defer_epilogue) {
+                            bool async_with_compute_stream, bool allocate_on_comm_stream, bool defer_epilogue,
+                            bool skip_single_rows) {
         EP_HOST_ASSERT(not destroyed and context->peers_ready);
         (void) allocate_on_comm_stream;
         const int num_ranks = context->num_ranks;
@@ -380,7 +381,7 @@ public:
         args.host = host_counts_device, args.timeout_ns = context->num_gpu_timeout_ns;
         args.trace = trace_of(2);
         const bool coop = Runtime::get().get_warp_cooperation();
-        args.coop = coop;
+        args.coop = coop, args.skip_single = skip_single_rows;
         launch::combine(args, num_sms, stream);
 
         const bool with_weights = topk_weights.has_value();
@@ -435,6 +436,37 @@ public:
         args.mapping = mapping.data_ptr<int>(), args.num_redundant = static_cast<int>(mapping.size(1));
         args.num_local_experts = num_local_experts;
         return args;
+    }
+
+    // Landing addresses for GEMM epilogues that take over the combine push of single-row tokens: `route[r]` is where
+    // expanded row r (bf16, `hidden` values) has to be stored instead of the GEMM's output tensor, 0 for all other rows.
+    // The caller passes the table to the producing GEMM and then calls `combine(..., skip_single_rows=true)` with the
+    // same handle. Between the dispatch epilogues of ALL ranks and the first store through the table there must be a
+    // barrier over the group (the landing area is the one dispatch has just been read from).
+    torch::Tensor build_combine_route(const torch::Tensor& recv_src_metadata, const torch::Tensor& psum_num_recv_tokens_per_rank,
+                                      int num_expanded_rows, int num_max_tokens_per_rank, int hidden) const {
+        EP_HOST_ASSERT(not destroyed and context->peers_ready);
+        EP_HOST_ASSERT(recv_src_metadata.is_cuda() and recv_src_metadata.is_contiguous() and recv_src_metadata.dim() == 2 and
+                       recv_src_metadata.scalar_type() == torch::kInt32);
+        EP_HOST_ASSERT(psum_num_recv_tokens_per_rank.is_cuda() and psum_num_recv_tokens_per_rank.scalar_type() == torch::kInt32 and
+                       psum_num_recv_tokens_per_rank.numel() == context->num_ranks);
+        const int num_topk = static_cast<int>(recv_src_metadata.size(1)) - 2;
+        EP_HOST_ASSERT(num_topk >= 1 and num_expanded_rows >= 0 and hidden > 0 and (hidden * 2) % 16 == 0);
+        const layout::CombineTokenLayout tl(hidden * 2, num_topk);
+        EP_HOST_ASSERT_MSG(get_combine_buffer_size(context->num_ranks, num_max_tokens_per_rank, hidden, num_topk) <= num_bytes,
+                           "EP buffer too small for this combine");
+        (void) tl;
+        auto route = torch::zeros({num_expanded_rows}, torch::TensorOptions().dtype(torch::kInt64).device(recv_src_metadata.device()));
+        if (recv_src_metadata.size(0) == 0 or num_expanded_rows == 0) return route;
+        kernels::CombineRouteArgs args = {};
+        args.recv_src_metadata = recv_src_metadata.data_ptr<int>();
+        args.psum_rank = psum_num_recv_tokens_per_rank.data_ptr<int>();
+        args.num_metadata_rows = static_cast<int>(recv_src_metadata.size(0)), args.num_expanded_rows = num_expanded_rows;
+        args.num_topk = num_topk, args.num_max_tokens = num_max_tokens_per_rank, args.hidden_bytes = hidden * 2;
+        args.buffer_offset = context->num_workspace_bytes, args.peers = context->peers;
+        args.route = reinterpret_cast<unsigned long long*>(route.data_ptr<int64_t>());
+        launch::combine_route(args, c10::cuda::getCurrentCUDAStream());
+        return route;
     }
 
     // Phase trace (diagnostics): from now on the four EP kernels stamp `%globaltimer` at their phase boundaries into the

@@ -27,6 +27,8 @@ void dispatch(kernels::DispatchArgs args, int num_sms, cudaStream_t stream);
 void dispatch_expand(kernels::ExpandArgs args, int num_sms, cudaStream_t stream);
 void combine(kernels::CombineArgs args, int num_sms, cudaStream_t stream);
 void combine_reduce(kernels::CombineReduceArgs args, int num_sms, cudaStream_t stream);
+// Fills `args.route` (zero-initialised by the caller) with the landing address of every single-row token's row.
+void combine_route(const kernels::CombineRouteArgs& args, cudaStream_t stream);
 
 void barrier(const kernels::BarrierArgs& args, cudaStream_t stream);
 void engram_fetch(const kernels::EngramFetchArgs& args, int num_sms, cudaStream_t stream);

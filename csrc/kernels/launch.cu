@@ -9,6 +9,7 @@
 #include <deep_ep/kernels/ep_dispatch.cuh>
 #include <deep_ep/kernels/ep_expand.cuh>
 #include <deep_ep/kernels/ep_layout.cuh>
+#include <deep_ep/kernels/ep_route.cuh>
 #include <deep_ep/kernels/misc.cuh>
 
 #include "api.hpp"
@@ -96,6 +97,11 @@ void combine(kernels::CombineArgs args, int num_sms, cudaStream_t stream) {
     args.num_warps = config.num_warps, args.num_stages = config.num_stages;
     launch_kernel(kernels::ep_combine_kernel, args, clamp_sms(num_sms), 32 * config.num_warps,
                   config.smem_bytes, true, stream);
+}
+
+void combine_route(const kernels::CombineRouteArgs& args, cudaStream_t stream) {
+    const int blocks = std::max(1, std::min((args.num_metadata_rows + 255) / 256, 592));
+    launch_kernel(kernels::ep_combine_route_kernel, args, blocks, 256, 0, false, stream);
 }
 
 void combine_reduce(kernels::CombineReduceArgs args, int num_sms, cudaStream_t stream) {

@@ -62,7 +62,8 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> get_dispatch_layout(cons
 // mode 1: d[rows, n] = a[rows, k] * b[g, k, n]; mode 2: d[g, m, n] += a[rows, m]^T * b[rows, n] (fp32).
 void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const torch::Tensor& psum,
                   const torch::Tensor& count, int mode, int epilogue, int num_sms, int alignment,
-                  const std::optional<torch::Tensor>& row_scale, const std::optional<torch::Tensor>& keep, bool use_pairs) {
+                  const std::optional<torch::Tensor>& row_scale, const std::optional<torch::Tensor>& keep, bool use_pairs,
+                  const std::optional<torch::Tensor>& route) {
     using namespace kernels;
     EP_HOST_ASSERT(a.is_cuda() and b.is_cuda() and d.is_cuda() and a.is_contiguous() and b.is_contiguous() and d.is_contiguous());
     EP_HOST_ASSERT(a.scalar_type() == torch::kBFloat16 and b.scalar_type() == torch::kBFloat16 and a.dim() == 2 and b.dim() == 3);
@@ -73,6 +74,12 @@ void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::T
     args.psum = psum.data_ptr<int>(), args.count = count.data_ptr<int>();
     args.d = d.data_ptr(), args.status = nullptr, args.alignment = alignment;
     const int64_t rows = a.size(0), g = args.num_groups;
+    if (route.has_value()) {
+        // destination table of `EPBuffer.build_combine_route`: rows with an entry are stored there instead of `d`
+        EP_HOST_ASSERT(epilogue == kEpilogueStore and route->is_cuda() and route->is_contiguous() and
+                       route->scalar_type() == torch::kInt64 and route->numel() >= rows);
+        args.route = reinterpret_cast<const unsigned long long*>(route->data_ptr<int64_t>());
+    }
     if (row_scale.has_value()) {
         EP_HOST_ASSERT(epilogue != kEpilogueStore and row_scale->is_cuda() and row_scale->is_contiguous() and
                        row_scale->scalar_type() == torch::kFloat32 and row_scale->numel() == rows);
@@ -266,7 +273,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("num_sms") = 0);
     m.def("grouped_gemm", &grouped_gemm, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
           py::arg("mode"), py::arg("epilogue") = 0, py::arg("num_sms") = 0, py::arg("alignment") = 1,
-          py::arg("row_scale") = py::none(), py::arg("keep") = py::none(), py::arg("use_pairs") = false);
+          py::arg("row_scale") = py::none(), py::arg("keep") = py::none(), py::arg("use_pairs") = false,
+          py::arg("route") = py::none());
     m.def("grouped_gemm_fp8", &grouped_gemm_fp8, py::arg("a"), py::arg("a_sf"), py::arg("b"), py::arg("b_sf"), py::arg("d"),
           py::arg("psum"), py::arg("count"), py::arg("epilogue") = 0, py::arg("num_sms") = 0, py::arg("alignment") = 1,
           py::arg("row_scale") = py::none(), py::arg("d_sf") = py::none(), py::arg("reg_split") = true);
@@ -285,6 +293,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readonly("lb_storage", &EPBuffer::lb_storage)
         .def("dispatch", &EPBuffer::dispatch)
         .def("combine", &EPBuffer::combine)
+        .def("build_combine_route", &EPBuffer::build_combine_route)
         .def("enable_phase_trace", &EPBuffer::enable_phase_trace)
         .def("disable_phase_trace", &EPBuffer::disable_phase_trace)
         .def("lb_prefetch_weights", &EPBuffer::lb_prefetch_weights)

@@ -316,7 +316,7 @@ class EPBuffer(BufferBase):
                 bias: Union[None, torch.Tensor, Tuple[torch.Tensor, torch.Tensor]] = None,
                 num_sms: int = 0, num_qps: int = 0, previous_event: Optional[EventHandle] = None,
                 async_with_compute_stream: bool = False, allocate_on_comm_stream: bool = False,
-                defer_epilogue: bool = False):
+                defer_epilogue: bool = False, *, fused_single_rows: bool = False):
         """Reduce expert outputs back to the ranks that own the tokens.
 
         Arguments:
@@ -325,6 +325,9 @@ class EPBuffer(BufferBase):
             topk_weights: `[num_expanded_tokens]` fp32 or `None`; routed back positionally, never multiplied in.
             bias: `None`, one tensor or a tuple of two `[num_tokens, hidden]` bf16 tensors added before the partials.
             num_sms: ignored, combine uses `handle.num_sms`.
+            fused_single_rows: the rows of `x` that are their token's only row on this rank were not written to `x`
+                but stored by the producing GEMM straight into the owners' landing slots (`build_combine_route`);
+                combine then sends only the routed weights for them.
             defer_epilogue: return only the event; `current_stream_wait()` runs the reduction and returns
                 `(combined_x, combined_topk_weights)`.
 
@@ -345,7 +348,8 @@ class EPBuffer(BufferBase):
         result, event, deferred_epilogue = self.runtime.combine(
             x, topk_weights, bias_0, bias_1, handle.recv_src_metadata, handle.topk_idx,
             handle.psum_num_recv_tokens_per_rank, handle.num_experts, handle.num_max_tokens_per_rank,
-            handle.num_sms, previous_event, async_with_compute_stream, allocate_on_comm_stream, defer_epilogue)
+            handle.num_sms, previous_event, async_with_compute_stream, allocate_on_comm_stream, defer_epilogue,
+            fused_single_rows)
         event_overlap = EventOverlap(event)
         if deferred_epilogue is not None:
             event_overlap.register_hook_after_wait(deferred_epilogue)
@@ -355,6 +359,20 @@ class EPBuffer(BufferBase):
         return combined_x, combined_topk_weights, event_overlap
 
     # ------------------------------------------------------------------------------------------
+    def build_combine_route(self, handle: EPHandle, hidden: int) -> torch.Tensor:
+        """Destination table for a GEMM that produces the `x` of the next `combine` with this handle.
+
+        `route[r]` (`hidden` = columns of the rows to come; int64 device addresses, 0 = none) tells the GEMM epilogue (`route=` of
+        `deep_ep.ops.grouped_gemm.grouped_gemm_forward` / `grouped_gemm_dgrad`) to store expanded row r directly into
+        the combine landing slot of its token's owner, local or over NVLink, instead of its output tensor. That is
+        possible for tokens with exactly one row on this rank, whose combine message is the row itself; the transfer
+        then overlaps the GEMM tile by tile. Afterwards call `combine(x, handle, ..., fused_single_rows=True)`.
+        Call `barrier()` on this buffer between the dispatch that produced `handle` and the GEMM that uses the table.
+        """
+        assert not self.is_simulated, 'GEMM epilogues that store into landing slots exist on CUDA only'
+        return self.runtime.build_combine_route(handle.recv_src_metadata, handle.psum_num_recv_tokens_per_rank,
+                                                int(handle.num_expanded_tokens), handle.num_max_tokens_per_rank, hidden)
+
     # ------------------------------------------------------------------------------------------ diagnostics
     _TRACE_PHASES = {
         'dispatch': ('count', 'entry_barrier', 'grid_sync', 'count_exchange', 'push', 'stores_complete', 'flags_and_tail'),

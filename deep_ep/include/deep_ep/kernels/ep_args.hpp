@@ -78,6 +78,8 @@ struct CombineArgs {
     int num_warps, num_stages;
     unsigned long long* trace;        // optional phase stamps, see DispatchArgs
     int coop;                         // 1: when rows are scarce, several warps of a CTA share a row (decode-sized calls)
+    int skip_single;                  // 1: rows that are their token's only one were already stored into the owner's landing
+                                      //    slot by a GEMM epilogue (`ep_route.cuh`); only their routed weights are sent
 };
 
 struct CombineReduceArgs {
@@ -95,6 +97,17 @@ struct CombineReduceArgs {
     long long timeout_ns;
     unsigned long long* trace;        // optional phase stamps, see DispatchArgs
     int coop;                         // 1: when tokens are scarce, several warps share a token
+};
+
+// Destination table for GEMM epilogues that take over the combine push of single-row tokens (`ep_route.cuh`).
+struct CombineRouteArgs {
+    const int* recv_src_metadata;     // [rows, k + 2]: expanded row per top-k position (-1 = none), source token, master position
+    const int* psum_rank;             // [R] inclusive prefix of received tokens per source rank
+    int num_metadata_rows, num_expanded_rows;
+    int num_topk, num_max_tokens, hidden_bytes;
+    int64_t buffer_offset;            // landing buffer offset inside every rank's allocation
+    layout::PeerTable peers;
+    unsigned long long* route;        // [num_expanded_rows], zero-initialised by the caller
 };
 
 namespace dispatch_detail {

@@ -214,6 +214,26 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
                     if (part == 0) ptx::bulk_commit();
                     continue;
                 }
+                if (count == 1 and a.skip_single) {
+                    // payload already delivered by the producing GEMM: the group's first warp sends the weights alone
+                    if (part == 0) {
+                        dispatch_detail::wait_read_pending(S - 1);
+                        __syncwarp();
+                        if (a.topk_weights != nullptr) {
+                            if (lane < k)
+                                reinterpret_cast<float*>(stage + tl.weight_offset())[lane] = my_slot >= 0 ? a.topk_weights[my_slot] : 0.f;
+                            ptx::fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                const int dst_group = num_ranks >= k ? master : rank;
+                                ptx::bulk_store(a.peers.base[s] + a.buffer_offset + bl.offset(dst_group, token) + tl.weight_offset(),
+                                                stage + tl.weight_offset(), token_bytes - tl.weight_offset());
+                            }
+                        }
+                        ptx::bulk_commit();
+                    }
+                    continue;
+                }
                 if (part == 0) dispatch_detail::wait_read_pending(S - 1);     // the store issued S rows ago has read the stage
                 ptx::named_barrier(bar_id, bar_threads);
                 reduce_rows(a.x, a.hidden_bytes, c_begin, c_end, my_slot, valid, count, stage, lane);
@@ -258,6 +278,24 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
             // the stage may still be read by the store issued S rows ago
             dispatch_detail::wait_read_pending(S - 1);
             __syncwarp();
+
+            if (count == 1 and a.skip_single) {
+                // the row itself already sits in the owner's landing slot (stored there by the GEMM that produced it):
+                // only the routed weights behind it are sent
+                if (a.topk_weights != nullptr) {
+                    if (lane < k)
+                        reinterpret_cast<float*>(stage + tl.weight_offset())[lane] = my_slot >= 0 ? a.topk_weights[my_slot] : 0.f;
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int group = num_ranks >= k ? master : rank;
+                        ptx::bulk_store(a.peers.base[s] + a.buffer_offset + bl.offset(group, token) + tl.weight_offset(),
+                                        stage + tl.weight_offset(), token_bytes - tl.weight_offset());
+                    }
+                }
+                ptx::bulk_commit();
+                continue;
+            }
 
             if (count == 1) {
                 const int slot = __shfl_sync(0xffffffffu, my_slot, __ffs(valid) - 1);

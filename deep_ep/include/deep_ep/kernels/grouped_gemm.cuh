@@ -193,6 +193,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quarter = warp & 3;                    // tensor-memory lane quarter this warp may access
         const int row = quarter * 32 + lane;
         int local_tile = 0;
+        bool stored_remotely = false;
         for (int tile = blockIdx.x; tile < num_tiles and not error_flag; tile += gridDim.x, ++local_tile) {
             const Tile t = locate_tile(a, tile_prefix, tile);
             const int acc = local_tile & 1, use = local_tile >> 1;
@@ -271,6 +272,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             } else {
                 __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + size_t(t.row_base + t.m0 + row) * a.n_out + t.n0;
+                if (a.route != nullptr and valid) {
+                    // a row that is its token's only contribution from this rank goes straight to the token's owner
+                    const unsigned long long target = __ldg(a.route + t.row_base + t.m0 + row);
+                    if (target != 0) out = reinterpret_cast<__nv_bfloat16*>(target) + t.n0, stored_remotely = true;
+                }
                 const bool written = row < t.rows_written;
                 for (int c = 0; c < BN; c += 32) {
                     uint32_t r[32];
@@ -292,6 +298,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             __syncwarp();
             if (lane == 0) ptx::mbarrier_arrive(&tmem_empty_bar[acc]);
         }
+        if (stored_remotely) __threadfence_system();     // peer stores are performed before the kernel completes
     }
 
     // ---- teardown: every thread arrives here, then the allocating warp frees tensor memory

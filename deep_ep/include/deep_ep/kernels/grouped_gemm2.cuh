@@ -188,6 +188,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;                       // row inside this CTA's 128-row half
         int local_tile = 0;
+        bool stored_remotely = false;
         for (int tile = pair; tile < num_tiles and not error_flag; tile += num_pairs, ++local_tile) {
             const Tile t = locate_tile(a, tile_prefix, tile);
             const int acc = local_tile & 1, use = local_tile >> 1;
@@ -267,6 +268,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     }
                 } else {
                     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + grow * a.n_out + t.n0;
+                    if (a.route != nullptr and valid) {
+                        // a row that is its token's only contribution from this rank goes straight to the token's owner
+                        const unsigned long long target = __ldg(a.route + grow);
+                        if (target != 0) out = reinterpret_cast<__nv_bfloat16*>(target) + t.n0, stored_remotely = true;
+                    }
                     for (int c = 0; c < kPairN; c += 32) {
                         uint32_t r[32];
                         tc::tmem_ld_32x32(taddr + c, r);
@@ -288,6 +294,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             __syncwarp();
             if (lane == 0) tc::mbarrier_arrive_cluster(tc::map_to_cta(&tmem_empty_bar[acc], 0));
         }
+        if (stored_remotely) __threadfence_system();     // peer stores are performed before the kernel completes
     }
 
     // ---- teardown: no CTA leaves while its partner may still signal its barriers or read its shared memory

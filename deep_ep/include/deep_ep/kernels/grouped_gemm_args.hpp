@@ -33,6 +33,10 @@ struct GroupedGemmArgs {
     const float* row_scale;   // optional fp32 [rows] factor applied by the SwiGLU epilogues
     int alignment;            // expert alignment: rows in [count, align(count)) of a tile are written as zeros
     int* status;              // set to 1 if a bounded wait ran out (may be nullptr)
+    // Plain-store epilogue only (forward / dgrad): optional [rows] table of destination addresses. A non-zero entry
+    // is where row r's n_out bf16 values go INSTEAD of d (local or a peer's memory: the combine landing slot of a
+    // token that has only this one row on this rank, see `ep_route.cuh`); zero = store into d as usual.
+    const unsigned long long* route;
 };
 
 EP_HOST_DEVICE int64_t grouped_gemm_smem_bytes(int block_n, int num_stages) {

@@ -28,6 +28,8 @@ class MoEConfig:
                                         # dispatch kernel) feeding block-scaled FP8 expert GEMMs
     fp8_scales: str = 'fp32'            # 'fp32': scales amax / 448, promoted in registers by the GEMM; 'ue8m0': powers of two,
                                         # applied by the tensor core (hidden and intermediate must be multiples of 512)
+    fuse_combine: bool = False          # the second expert GEMM stores the rows of single-row tokens straight into their
+                                        # owners' combine landing slots (over NVLink, tile by tile); combine sends the rest
     expert_backend: str = 'grouped'     # 'grouped': hand-written grouped GEMM kernels, 'torch': per-expert torch.mm
     num_sms: int = 0
     init_std: float = 0.02
@@ -58,16 +60,16 @@ class _Combine(torch.autograd.Function):
     """y = combine(x). Backward: grad_x = cached dispatch(grad_y) (every expanded row receives its token's gradient)."""
 
     @staticmethod
-    def forward(ctx, x, layer, handle):
+    def forward(ctx, x, layer, handle, fused_single_rows=False):
         ctx.layer, ctx.handle = layer, handle
-        combined, _, _ = layer.buffer.combine(x, handle)
+        combined, _, _ = layer.buffer.combine(x, handle, fused_single_rows=fused_single_rows)
         return combined
 
     @staticmethod
     def backward(ctx, grad_y):
         grad_x, _, _, _, _ = ctx.layer.buffer.dispatch(grad_y.contiguous(), handle=ctx.handle, do_expand=True,
                                                        do_zero_padding=True)
-        return grad_x, None, None
+        return grad_x, None, None, None
 
 
 class MoELayer(nn.Module):
@@ -109,12 +111,14 @@ class MoELayer(nn.Module):
         topk_weights = topk_weights / topk_weights.sum(dim=-1, keepdim=True)
         return topk_idx, topk_weights
 
-    def experts(self, recv_x: torch.Tensor, recv_w: torch.Tensor, handle: EPHandle) -> torch.Tensor:
+    def experts(self, recv_x: torch.Tensor, recv_w: torch.Tensor, handle: EPHandle,
+                route: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Expert FFN on the expanded rows, already multiplied by each row's routing weight."""
         from ..ops.grouped_gemm import grouped_swiglu_ffn
         return grouped_swiglu_ffn(recv_x, self.w_gate_up, self.w_down, handle.psum_num_recv_tokens_per_expert,
                                   handle.num_unaligned_recv_tokens_per_expert, handle.num_recv_tokens_per_expert_list,
-                                  self.config.expert_alignment, backend=self.config.expert_backend, row_scale=recv_w)
+                                  self.config.expert_alignment, backend=self.config.expert_backend, row_scale=recv_w,
+                                  route=route)
 
     # ------------------------------------------------------------------------------------------ FP8 inference
     def quantize_weights(self) -> None:
@@ -154,8 +158,14 @@ class MoELayer(nn.Module):
         topk_idx, topk_weights = self.route(x.detach())
         recv_x, recv_w = _Dispatch.apply(x, topk_idx, topk_weights.float().contiguous(), self)
         handle = self._handle
-        y = self.experts(recv_x, recv_w, handle)
-        out = _Combine.apply(y, self, handle)
+        route = None
+        if self.config.fuse_combine:
+            # landing addresses of the rows the second GEMM may deliver itself; the barrier makes sure every rank has
+            # finished reading the landing area (its dispatch epilogue) before the first such store
+            route = self.buffer.build_combine_route(handle, self.config.hidden)
+            self.buffer.barrier()
+        y = self.experts(recv_x, recv_w, handle, route)
+        out = _Combine.apply(y, self, handle, route is not None)
         if self.config.num_shared_experts > 0:
             g, u = F.linear(x, self.shared_gate_up).chunk(2, dim=-1)
             out = out + F.linear(F.silu(g) * u, self.shared_down)

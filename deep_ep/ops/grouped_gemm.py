@@ -31,17 +31,21 @@ EPILOGUE_STORE, EPILOGUE_SWIGLU, EPILOGUE_SWIGLU_KEEP = 0, 1, 2
 
 def grouped_gemm_forward(x: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
                          swiglu: bool = False, num_sms: int = 0, alignment: int = 1,
-                         row_scale: Optional[torch.Tensor] = None, keep_preactivation: bool = False):
+                         row_scale: Optional[torch.Tensor] = None, keep_preactivation: bool = False,
+                         route: Optional[torch.Tensor] = None):
     """`y[rows_e] = x[rows_e] @ w[e].T` with `w [G, N, K]`; with `swiglu`, `w[e] = [gate; up]` and
     `y = silu(x @ gate.T) * (x @ up.T) * row_scale` (`[rows, N / 2]`); `keep_preactivation` also returns the bf16
     `[gate | up]` matrix. Padding rows inside an expert's aligned region are written as zeros; rows that belong to no
-    region are left untouched."""
+    region are left untouched. `route` (plain store only, from `EPBuffer.build_combine_route`): rows with an entry are
+    stored at that address (the combine landing slot of their token's owner) instead of the returned tensor."""
     n_out = w.size(1) // 2 if swiglu else w.size(1)
     y = torch.empty((x.size(0), n_out), dtype=torch.bfloat16, device=x.device)
     if not swiglu:
         assert row_scale is None and not keep_preactivation
-        _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_STORE, num_sms, alignment, None, None, _pairs(MODE_FORWARD))
+        _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_STORE, num_sms, alignment, None, None, _pairs(MODE_FORWARD),
+                        route)
         return y
+    assert route is None
     keep = torch.empty((x.size(0), w.size(1)), dtype=torch.bfloat16, device=x.device) if keep_preactivation else None
     _C.grouped_gemm(x, w, y, psum, count, MODE_FORWARD, EPILOGUE_SWIGLU_KEEP if keep_preactivation else EPILOGUE_SWIGLU,
                     num_sms, alignment, row_scale, keep, _pairs(MODE_FORWARD))
@@ -49,10 +53,11 @@ def grouped_gemm_forward(x: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, c
 
 
 def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
-                       num_sms: int = 0, alignment: int = 1) -> torch.Tensor:
-    """`dx[rows_e] = dy[rows_e] @ w[e]` with `w [G, N, K]` read as stored (no transpose copy)."""
+                       num_sms: int = 0, alignment: int = 1, route: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`dx[rows_e] = dy[rows_e] @ w[e]` with `w [G, N, K]` read as stored (no transpose copy); `route` as in
+    `grouped_gemm_forward`."""
     dx = torch.empty((dy.size(0), w.size(2)), dtype=torch.bfloat16, device=dy.device)
-    _C.grouped_gemm(dy, w, dx, psum, count, MODE_DGRAD, EPILOGUE_STORE, num_sms, alignment, None, None, _pairs(MODE_DGRAD))
+    _C.grouped_gemm(dy, w, dx, psum, count, MODE_DGRAD, EPILOGUE_STORE, num_sms, alignment, None, None, _pairs(MODE_DGRAD), route)
     return dx
 
 
@@ -78,10 +83,11 @@ class GroupedSwiGLUFFN(torch.autograd.Function):
     Requires the expert alignment to be a multiple of 128 (every padding row is then written as zero by a tile)."""
 
     @staticmethod
-    def forward(ctx, x, w_gate_up, w_down, row_scale, psum, count, alignment):
+    def forward(ctx, x, w_gate_up, w_down, row_scale, psum, count, alignment, route=None):
         act, h = grouped_gemm_forward(x, w_gate_up, psum, count, swiglu=True, alignment=alignment, row_scale=row_scale,
                                       keep_preactivation=True)
-        y = grouped_gemm_forward(act, w_down, psum, count, alignment=alignment)
+        # with `route`, rows that are their token's only one leave this GEMM for the owner's combine landing slot
+        y = grouped_gemm_forward(act, w_down, psum, count, alignment=alignment, route=route)
         ctx.save_for_backward(x, w_gate_up, w_down, row_scale, psum, count, h, act)
         ctx.alignment = alignment
         return y
@@ -95,7 +101,7 @@ class GroupedSwiGLUFFN(torch.autograd.Function):
         dh = _C.swiglu_backward(h, dact, row_scale)
         dx = grouped_gemm_dgrad(dh, w_gate_up, psum, count, alignment=ctx.alignment) if ctx.needs_input_grad[0] else None
         dw_gate_up = _wgrad(dh, x, w_gate_up, psum, count, ctx.alignment) if ctx.needs_input_grad[1] else None
-        return dx, dw_gate_up, dw_down, None, None, None, None
+        return dx, dw_gate_up, dw_down, None, None, None, None, None
 
 
 def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, dw: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
@@ -267,18 +273,21 @@ def _torch_ffn(x, w_gate_up, w_down, psum, count):
 
 def grouped_swiglu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, psum: torch.Tensor,
                        unaligned: torch.Tensor, per_expert_list: Optional[List[int]], alignment: int,
-                       backend: str = 'grouped', row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       backend: str = 'grouped', row_scale: Optional[torch.Tensor] = None,
+                       route: Optional[torch.Tensor] = None) -> torch.Tensor:
     """SwiGLU FFN of every local expert on its rows. `w_gate_up [G, 2I, H]` (gate rows first), `w_down [G, H, I]`.
 
     Padding rows of the result are zero. In inference mode the SwiGLU is fused into the first GEMM's epilogue;
     under autograd the pre-activation is kept for the backward pass.
     """
     if backend == 'torch' or not (_supported(x, w_gate_up) and _supported(x, w_down)):
+        assert route is None
         y = _torch_ffn(x, w_gate_up, w_down, psum, unaligned)
         return y if row_scale is None else y * row_scale.unsqueeze(1).to(y.dtype)
     if alignment % 128 == 0 and w_gate_up.size(1) % 256 == 0:
         # fused path: no elementwise passes, padding rows come out as zeros
-        return GroupedSwiGLUFFN.apply(x, w_gate_up, w_down, row_scale, psum, unaligned, alignment)
+        return GroupedSwiGLUFFN.apply(x, w_gate_up, w_down, row_scale, psum, unaligned, alignment, route)
+    assert route is None, 'a combine route needs the fused FFN path (alignment % 128 == 0, intermediate % 128 == 0)'
     if row_scale is not None:
         y = grouped_swiglu_ffn(x, w_gate_up, w_down, psum, unaligned, per_expert_list, alignment, backend)
         return y * row_scale.unsqueeze(1).to(y.dtype)

@@ -311,8 +311,9 @@ class SimEPRuntime:
 
     def combine(self, x, topk_weights, bias_0, bias_1, recv_src_metadata, topk_idx, psum_rank,
                 num_experts, num_max_tokens_per_rank, num_sms, previous_event,
-                async_with_compute_stream, allocate_on_comm_stream, defer_epilogue):
+                async_with_compute_stream, allocate_on_comm_stream, defer_epilogue, skip_single_rows=False):
         from ..utils.event import EventHandle
+        assert not skip_single_rows, 'GEMM epilogues that store into landing slots exist on CUDA only'
         num_tokens, num_topk = topk_idx.shape
         num_recv = int(psum_rank[-1])
         metadata = recv_src_metadata[:num_recv]

@@ -1,5 +1,7 @@
 """The expert-parallel MoE layer (dispatch -> grouped tcgen05 GEMMs -> combine) against a dense fp32 PyTorch
 computation of the same layer, forward and backward, and the FP8 inference path against the BF16 one."""
+import os
+
 import pytest
 import torch
 
@@ -94,3 +96,49 @@ def test_moe_layer_multi_gpu(master_port):
     world = min(torch.cuda.device_count(), 8)
     world -= world % 2
     run_distributed(_moe_worker, world, master_port, 'nccl', (300, 512, 512, 16, 4))
+
+
+def _new_paths_worker(rank, world_size):
+    """Opt-in paths against the default ones, bit for bit: the second expert GEMM delivering single-row tokens itself,
+    and several warps sharing a row in decode-sized combine calls."""
+    import torch.distributed as dist
+    import deep_ep
+    from deep_ep.models.moe_layer import MoEConfig, MoELayer
+    from ep_check import check_dispatch_combine
+    dev = torch.device('cuda')
+    torch.manual_seed(21)
+    cfg = MoEConfig(hidden=512, intermediate=256, num_experts=8 * world_size, num_topk=4, num_max_tokens_per_rank=200,
+                    expert_alignment=128)
+    layer = MoELayer(dist.group.WORLD, cfg, device=dev)
+    torch.manual_seed(300 + rank)
+    x = torch.randn(200, 512, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        plain = layer(x)
+        layer.config.fuse_combine = True
+        fused = layer(x)
+        fused_again = layer(x)
+    torch.cuda.synchronize()
+    layer.buffer.runtime.check_status()
+    assert torch.equal(plain, fused) and torch.equal(plain, fused_again), 'fused combine route changes the result'
+    layer.destroy()
+
+    deep_ep._C.set_warp_cooperation(True)
+    try:
+        with torch.inference_mode():
+            buffer = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=64, hidden=1024, num_topk=8, explicitly_destroy=True,
+                                      num_gpu_timeout_secs=10, num_cpu_timeout_secs=30)
+            check_dispatch_combine(buffer, 64, 1024, 8, 8 * world_size, do_cpu_sync=True, defer=True, masked_ratio=0.1,
+                                   unbalanced_ratio=2.0, quick=True, num_sms=16)
+            buffer.destroy()
+    finally:
+        deep_ep._C.set_warp_cooperation(False)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(os.environ.get('EP_TEST_NEW_PATHS', '0') != '1',
+                    reason='paths that have not run on a GPU yet; set EP_TEST_NEW_PATHS=1 to try them')
+def test_opt_in_paths_match_default_paths(master_port):
+    world = max(1, min(torch.cuda.device_count(), 8))
+    if world > 1:
+        world -= world % 2
+    run_distributed(_new_paths_worker, world, master_port, 'nccl')
