@@ -43,6 +43,29 @@ CUtensorMap make_map_2d_u8(const void* base, int64_t rows, int64_t cols, int box
     return map;
 }
 
+// One word of mapped pinned host memory that the GEMM kernels set when one of their bounded waits ran out. It is looked
+// at before every launch, so a kernel that gave up (and left its output incomplete) is reported at the next call at the
+// latest instead of passing silently.
+struct FailureWord {
+    int* host = nullptr;
+    int* device = nullptr;
+    FailureWord() {
+        CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&host), sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable));
+        *host = 0;
+        CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&device), host, 0));
+    }
+};
+
+int* failure_word_checked() {
+    static FailureWord word;
+    if (*static_cast<volatile int*>(word.host) != 0) {
+        *word.host = 0;
+        throw EPException("Grouped GEMM", __FILE__, __LINE__,
+                          "an earlier grouped GEMM kernel gave up waiting on one of its barriers; its output is incomplete");
+    }
+    return word.device;
+}
+
 }  // namespace
 
 void grouped_gemm_fp8(kernels::GroupedGemmFp8Args args, const void* a, int64_t a_rows, const void* b, int64_t b_rows,
@@ -52,6 +75,7 @@ void grouped_gemm_fp8(kernels::GroupedGemmFp8Args args, const void* a, int64_t a
     EP_HOST_ASSERT_MSG(args.k > 0 and args.k % kFp8BlockK == 0, "K must be a multiple of 128");
     EP_HOST_ASSERT(a_rows > 0);
     CUDA_CHECK(cudaFree(nullptr));       // the driver call below needs a current context
+    args.status = failure_word_checked();
     if (args.epilogue != kEpilogueStore) {
         EP_HOST_ASSERT_MSG(args.epilogue == kEpilogueSwiGLU and args.n % 256 == 0, "SwiGLU needs N (gate + up) to be a multiple of 256");
         args.n_out = args.n / 2;
@@ -93,6 +117,7 @@ void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, 
     EP_HOST_ASSERT(args.num_groups > 0 and args.num_groups <= kMaxLocalExperts);
     // the driver call below needs a current context; autograd worker threads may not have touched the runtime yet
     CUDA_CHECK(cudaFree(nullptr));
+    args.status = failure_word_checked();
     if (args.epilogue != kEpilogueStore) {
         EP_HOST_ASSERT(args.mode == kModeForward and args.n % 256 == 0);
         args.block_n = 256, args.block_n_out = 128, args.n_out = args.n / 2;

@@ -308,7 +308,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc::fence_after_thread_sync();
         tc::tmem_dealloc(tmem_base, 512);
     }
-    if (threadIdx.x == 0 and error_flag and a.status != nullptr) atomicExch(a.status, 1);
+    // a bounded wait ran out: leave a mark where the host finds it (mapped host memory) before its next launch
+    if (threadIdx.x == 0 and error_flag and a.status != nullptr) {
+        *reinterpret_cast<volatile int*>(a.status) = 1;
+        __threadfence_system();
+    }
 }
 
 }  // namespace deep_ep::kernels
