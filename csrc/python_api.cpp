@@ -118,7 +118,7 @@ void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::T
 void grouped_gemm_fp8(const torch::Tensor& a, const torch::Tensor& a_sf, const torch::Tensor& b, const torch::Tensor& b_sf,
                       const torch::Tensor& d, const torch::Tensor& psum, const torch::Tensor& count, int epilogue, int num_sms,
                       int alignment, const std::optional<torch::Tensor>& row_scale, const std::optional<torch::Tensor>& d_sf,
-                      bool reg_split) {
+                      bool reg_split, const std::optional<torch::Tensor>& route) {
     using namespace kernels;
     for (const auto* t : {&a, &a_sf, &b, &b_sf, &d, &psum, &count}) EP_HOST_ASSERT(t->is_cuda() and t->is_contiguous());
     EP_HOST_ASSERT(a.scalar_type() == torch::kFloat8_e4m3fn and b.scalar_type() == torch::kFloat8_e4m3fn and a.dim() == 2 and b.dim() == 3);
@@ -159,6 +159,12 @@ void grouped_gemm_fp8(const torch::Tensor& a, const torch::Tensor& a_sf, const t
         EP_HOST_ASSERT(epilogue == kEpilogueSwiGLU and row_scale->is_cuda() and row_scale->is_contiguous() and
                        row_scale->scalar_type() == torch::kFloat32 and row_scale->numel() == rows);
         args.row_scale = row_scale->data_ptr<float>();
+    }
+    if (route.has_value()) {
+        // destination table of `EPBuffer.build_combine_route` (hardware-scaled kernel, plain-store epilogue only)
+        EP_HOST_ASSERT(hw_scales and epilogue == kEpilogueStore and route->is_cuda() and route->is_contiguous() and
+                       route->scalar_type() == torch::kInt64 and route->numel() >= rows);
+        args.route = reinterpret_cast<const unsigned long long*>(route->data_ptr<int64_t>());
     }
     launch::grouped_gemm_fp8(args, a.data_ptr(), rows, b.data_ptr(), g * n, num_sms, c10::cuda::getCurrentCUDAStream());
 }
@@ -277,7 +283,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("route") = py::none());
     m.def("grouped_gemm_fp8", &grouped_gemm_fp8, py::arg("a"), py::arg("a_sf"), py::arg("b"), py::arg("b_sf"), py::arg("d"),
           py::arg("psum"), py::arg("count"), py::arg("epilogue") = 0, py::arg("num_sms") = 0, py::arg("alignment") = 1,
-          py::arg("row_scale") = py::none(), py::arg("d_sf") = py::none(), py::arg("reg_split") = true);
+          py::arg("row_scale") = py::none(), py::arg("d_sf") = py::none(), py::arg("reg_split") = true,
+          py::arg("route") = py::none());
     m.def("swiglu_backward", &swiglu_backward, py::arg("h"), py::arg("dact"), py::arg("row_scale") = py::none());
     m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
           py::arg("num_sms") = 0, py::arg("accumulate") = true, py::arg("use_pairs") = false);

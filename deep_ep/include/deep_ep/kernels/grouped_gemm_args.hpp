@@ -73,6 +73,8 @@ struct GroupedGemmFp8Args {
     const uint8_t* sf_a_e8;   // [rows, k / 128]
     const uint8_t* sf_b_e8;   // [G, n / 128, k / 128]
     uint8_t* d_sf_e8;         // SwiGLU with e4m3 output: [rows, n / 256]
+    // plain-store epilogue of the hardware-scaled kernel: optional destination table, see GroupedGemmArgs::route
+    const unsigned long long* route;
 };
 
 constexpr int kFp8SfGroup = 4;             // K blocks whose scale bytes share one 32-bit tensor-memory column

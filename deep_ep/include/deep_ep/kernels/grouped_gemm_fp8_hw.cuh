@@ -203,6 +203,7 @@ grouped_gemm_fp8_hw_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         const int col_a = swiglu ? half * 64 : half * 128;
         const int col_b = swiglu ? 128 + half * 64 : half * 128 + 64;
         int local_tile = 0;
+        bool stored_remotely = false;
         for (int tile = blockIdx.x; tile < num_tiles and not error_flag; tile += gridDim.x, ++local_tile) {
             const Fp8Tile t = locate_fp8_tile(a, tile_prefix, tile, block_n_out);
             const int grow = t.row_base + t.m0 + row;
@@ -224,6 +225,11 @@ grouped_gemm_fp8_hw_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             const bool valid = row < t.rows_valid, written = row < t.rows_written;
             if (not swiglu) {
                 __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + size_t(grow) * a.n_out + t.n0 + half * 128;
+                if (a.route != nullptr and valid) {
+                    // a row that is its token's only contribution from this rank goes straight to the token's owner
+                    const unsigned long long target = __ldg(a.route + grow);
+                    if (target != 0) out = reinterpret_cast<__nv_bfloat16*>(target) + t.n0 + half * 128, stored_remotely = true;
+                }
                 if (written) {
                     #pragma unroll
                     for (int v = 0; v < 16; ++v) {
@@ -288,6 +294,7 @@ grouped_gemm_fp8_hw_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
                 }
             }
         }
+        if (stored_remotely) __threadfence_system();     // peer stores are performed before the kernel completes
     }
 
     // ---- teardown: every thread arrives here, then the allocating warp frees tensor memory

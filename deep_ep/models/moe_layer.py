@@ -145,10 +145,14 @@ class MoELayer(nn.Module):
             x, topk_idx=topk_idx, topk_weights=topk_weights.float().contiguous(), num_experts=cfg.num_experts,
             expert_alignment=cfg.expert_alignment, num_sms=cfg.num_sms, do_expand=True, do_zero_padding=True,
             do_cpu_sync=True, fused_fp8_quant='ue8m0' if cfg.fp8_scales == 'ue8m0' else True)
+        route = None
+        if cfg.fuse_combine and cfg.fp8_scales == 'ue8m0':
+            route = self.buffer.build_combine_route(handle, cfg.hidden)
+            self.buffer.barrier()
         y = grouped_swiglu_ffn_fp8(recv_x, recv_sf, self._w1_fp8, self._w1_sf, self._w2_fp8, self._w2_sf,
                                    handle.psum_num_recv_tokens_per_expert, handle.num_unaligned_recv_tokens_per_expert,
-                                   alignment=cfg.expert_alignment, row_scale=recv_w)
-        out, _, _ = self.buffer.combine(y, handle)
+                                   alignment=cfg.expert_alignment, row_scale=recv_w, route=route)
+        out, _, _ = self.buffer.combine(y, handle, fused_single_rows=route is not None)
         if cfg.num_shared_experts > 0:
             g, u = F.linear(x, self.shared_gate_up).chunk(2, dim=-1)
             out = out + F.linear(F.silu(g) * u, self.shared_down)

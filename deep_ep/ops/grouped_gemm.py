@@ -217,7 +217,8 @@ def ue8m0_to_float(sf: torch.Tensor) -> torch.Tensor:
 
 def grouped_gemm_fp8_forward(x_fp8: torch.Tensor, x_sf: torch.Tensor, w_fp8: torch.Tensor, w_sf: torch.Tensor,
                              psum: torch.Tensor, count: torch.Tensor, swiglu: bool = False, quantize_output: bool = False,
-                             num_sms: int = 0, alignment: int = 1, row_scale: Optional[torch.Tensor] = None):
+                             num_sms: int = 0, alignment: int = 1, row_scale: Optional[torch.Tensor] = None,
+                             route: Optional[torch.Tensor] = None):
     """`y[rows_e] = (x_fp8 * x_sf)[rows_e] @ (w_fp8[e] * w_sf[e]).T` on the FP8 tensor cores.
 
     `x_fp8 [rows, K]` e4m3 with `x_sf [rows, K / 128]` fp32 (what an FP8 dispatch returns), `w_fp8 [G, N, K]` e4m3 with
@@ -232,8 +233,10 @@ def grouped_gemm_fp8_forward(x_fp8: torch.Tensor, x_sf: torch.Tensor, w_fp8: tor
     if not swiglu:
         assert not quantize_output and row_scale is None
         y = torch.empty((rows, n), dtype=torch.bfloat16, device=x_fp8.device)
-        _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_STORE, num_sms, alignment, None, None, FP8_REG_SPLIT)
+        _C.grouped_gemm_fp8(x_fp8, x_sf, w_fp8, w_sf, y, psum, count, EPILOGUE_STORE, num_sms, alignment, None, None, FP8_REG_SPLIT,
+                            route)
         return y
+    assert route is None
     if quantize_output:
         y = torch.empty((rows, n // 2), dtype=torch.float8_e4m3fn, device=x_fp8.device)
         y_sf = torch.empty((rows, n // 256), dtype=w_sf.dtype, device=x_fp8.device)
@@ -246,13 +249,15 @@ def grouped_gemm_fp8_forward(x_fp8: torch.Tensor, x_sf: torch.Tensor, w_fp8: tor
 
 def grouped_swiglu_ffn_fp8(x_fp8: torch.Tensor, x_sf: torch.Tensor, w_gate_up: torch.Tensor, w_gate_up_sf: torch.Tensor,
                            w_down: torch.Tensor, w_down_sf: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
-                           alignment: int = 128, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           alignment: int = 128, row_scale: Optional[torch.Tensor] = None,
+                           route: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Forward-only FP8 expert FFN over dispatched FP8 rows: GEMM1 with the SwiGLU epilogue re-quantises its output per
     row and 128 columns, GEMM2 consumes that directly; the result is bf16 `[rows, H]`. No elementwise pass touches
     global memory between the dispatch and the combine."""
     act, act_sf = grouped_gemm_fp8_forward(x_fp8, x_sf, w_gate_up, w_gate_up_sf, psum, count, swiglu=True,
                                            quantize_output=True, alignment=alignment, row_scale=row_scale)
-    return grouped_gemm_fp8_forward(act, act_sf, w_down, w_down_sf, psum, count, alignment=alignment)
+    # `route` (power-of-two scales only): single-row tokens leave GEMM2 for their owners' combine landing slots
+    return grouped_gemm_fp8_forward(act, act_sf, w_down, w_down_sf, psum, count, alignment=alignment, route=route)
 
 
 def _torch_ffn(x, w_gate_up, w_down, psum, count):

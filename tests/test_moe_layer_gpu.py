@@ -122,6 +122,18 @@ def _new_paths_worker(rank, world_size):
     assert torch.equal(plain, fused) and torch.equal(plain, fused_again), 'fused combine route changes the result'
     layer.destroy()
 
+    # the same through the FP8 inference path with power-of-two scales (GEMM2 = the hardware-scaled kernel)
+    cfg8 = MoEConfig(hidden=512, intermediate=512, num_experts=8 * world_size, num_topk=4, num_max_tokens_per_rank=200,
+                     expert_alignment=128, fp8_scales='ue8m0')
+    layer8 = MoELayer(dist.group.WORLD, cfg8, device=dev)
+    plain8 = layer8.forward_fp8(x)
+    layer8.config.fuse_combine = True
+    fused8 = layer8.forward_fp8(x)
+    torch.cuda.synchronize()
+    layer8.buffer.runtime.check_status()
+    assert torch.equal(plain8, fused8), 'fused combine route changes the FP8 result'
+    layer8.destroy()
+
     deep_ep._C.set_warp_cooperation(True)
     try:
         with torch.inference_mode():
