@@ -52,7 +52,11 @@ class _Dispatch(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_recv_x, _grad_w):
-        grad_x, _, _ = ctx.layer.buffer.combine(grad_recv_x.contiguous(), ctx.handle)
+        # with `fuse_combine` the data-gradient GEMM that produced `grad_recv_x` has already stored the rows of
+        # single-row tokens into their owners' landing slots
+        grad_x, _, _ = ctx.layer.buffer.combine(grad_recv_x.contiguous(), ctx.handle,
+                                                fused_single_rows=ctx.layer._backward_route_used)
+        ctx.layer._backward_route_used = False
         return grad_x, None, None, None
 
 
@@ -98,6 +102,7 @@ class MoELayer(nn.Module):
             group, num_max_tokens_per_rank=config.num_max_tokens_per_rank, hidden=h, num_topk=config.num_topk,
             explicitly_destroy=True)
         self._handle: Optional[EPHandle] = None
+        self._backward_route_used = False
 
     def destroy(self) -> None:
         if self._own_buffer and self.buffer is not None:
@@ -115,10 +120,16 @@ class MoELayer(nn.Module):
                 route: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Expert FFN on the expanded rows, already multiplied by each row's routing weight."""
         from ..ops.grouped_gemm import grouped_swiglu_ffn
+        backward_route = None
+        if route is not None and torch.is_grad_enabled() and recv_x.requires_grad:
+            def barrier_then_mark():
+                self.buffer.barrier()
+                self._backward_route_used = True
+            backward_route = (route, barrier_then_mark)
         return grouped_swiglu_ffn(recv_x, self.w_gate_up, self.w_down, handle.psum_num_recv_tokens_per_expert,
                                   handle.num_unaligned_recv_tokens_per_expert, handle.num_recv_tokens_per_expert_list,
                                   self.config.expert_alignment, backend=self.config.expert_backend, row_scale=recv_w,
-                                  route=route)
+                                  route=route, backward_route=backward_route)
 
     # ------------------------------------------------------------------------------------------ FP8 inference
     def quantize_weights(self) -> None:

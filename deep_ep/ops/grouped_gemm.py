@@ -83,13 +83,16 @@ class GroupedSwiGLUFFN(torch.autograd.Function):
     Requires the expert alignment to be a multiple of 128 (every padding row is then written as zero by a tile)."""
 
     @staticmethod
-    def forward(ctx, x, w_gate_up, w_down, row_scale, psum, count, alignment, route=None):
+    def forward(ctx, x, w_gate_up, w_down, row_scale, psum, count, alignment, route=None, backward_route=None):
         act, h = grouped_gemm_forward(x, w_gate_up, psum, count, swiglu=True, alignment=alignment, row_scale=row_scale,
                                       keep_preactivation=True)
         # with `route`, rows that are their token's only one leave this GEMM for the owner's combine landing slot
         y = grouped_gemm_forward(act, w_down, psum, count, alignment=alignment, route=route)
         ctx.save_for_backward(x, w_gate_up, w_down, row_scale, psum, count, h, act)
         ctx.alignment = alignment
+        # `backward_route = (table, barrier)`: the data-gradient GEMM of the first layer feeds the combine that is the
+        # backward of dispatch, so it can deliver single-row tokens the same way; `barrier()` is called right before it
+        ctx.backward_route = backward_route
         return y
 
     @staticmethod
@@ -99,9 +102,15 @@ class GroupedSwiGLUFFN(torch.autograd.Function):
         dact = grouped_gemm_dgrad(dy, w_down, psum, count, alignment=ctx.alignment)
         dw_down = _wgrad(dy, act, w_down, psum, count, ctx.alignment) if ctx.needs_input_grad[2] else None
         dh = _C.swiglu_backward(h, dact, row_scale)
-        dx = grouped_gemm_dgrad(dh, w_gate_up, psum, count, alignment=ctx.alignment) if ctx.needs_input_grad[0] else None
+        dx = None
+        if ctx.needs_input_grad[0]:
+            table = None
+            if ctx.backward_route is not None:
+                table, barrier = ctx.backward_route
+                barrier()
+            dx = grouped_gemm_dgrad(dh, w_gate_up, psum, count, alignment=ctx.alignment, route=table)
         dw_gate_up = _wgrad(dh, x, w_gate_up, psum, count, ctx.alignment) if ctx.needs_input_grad[1] else None
-        return dx, dw_gate_up, dw_down, None, None, None, None, None
+        return dx, dw_gate_up, dw_down, None, None, None, None, None, None
 
 
 def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, dw: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,
@@ -279,7 +288,7 @@ def _torch_ffn(x, w_gate_up, w_down, psum, count):
 def grouped_swiglu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, psum: torch.Tensor,
                        unaligned: torch.Tensor, per_expert_list: Optional[List[int]], alignment: int,
                        backend: str = 'grouped', row_scale: Optional[torch.Tensor] = None,
-                       route: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       route: Optional[torch.Tensor] = None, backward_route=None) -> torch.Tensor:
     """SwiGLU FFN of every local expert on its rows. `w_gate_up [G, 2I, H]` (gate rows first), `w_down [G, H, I]`.
 
     Padding rows of the result are zero. In inference mode the SwiGLU is fused into the first GEMM's epilogue;
@@ -291,8 +300,8 @@ def grouped_swiglu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.T
         return y if row_scale is None else y * row_scale.unsqueeze(1).to(y.dtype)
     if alignment % 128 == 0 and w_gate_up.size(1) % 256 == 0:
         # fused path: no elementwise passes, padding rows come out as zeros
-        return GroupedSwiGLUFFN.apply(x, w_gate_up, w_down, row_scale, psum, unaligned, alignment, route)
-    assert route is None, 'a combine route needs the fused FFN path (alignment % 128 == 0, intermediate % 128 == 0)'
+        return GroupedSwiGLUFFN.apply(x, w_gate_up, w_down, row_scale, psum, unaligned, alignment, route, backward_route)
+    assert route is None and backward_route is None, 'a combine route needs the fused FFN path (alignment % 128 == 0, intermediate % 128 == 0)'
     if row_scale is not None:
         y = grouped_swiglu_ffn(x, w_gate_up, w_down, psum, unaligned, per_expert_list, alignment, backend)
         return y * row_scale.unsqueeze(1).to(y.dtype)

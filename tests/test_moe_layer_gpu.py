@@ -120,6 +120,16 @@ def _new_paths_worker(rank, world_size):
     torch.cuda.synchronize()
     layer.buffer.runtime.check_status()
     assert torch.equal(plain, fused) and torch.equal(plain, fused_again), 'fused combine route changes the result'
+    # forward + backward: the data-gradient GEMM of the first layer delivers single-row tokens of the backward combine
+    grads = []
+    for fuse in (False, True):
+        layer.config.fuse_combine = fuse
+        xg = x.clone().requires_grad_()
+        layer(xg).backward(torch.ones_like(x))
+        grads.append(xg.grad.clone())
+    torch.cuda.synchronize()
+    layer.buffer.runtime.check_status()
+    assert torch.equal(grads[0], grads[1]), 'fused combine route changes the input gradient'
     layer.destroy()
 
     # the same through the FP8 inference path with power-of-two scales (GEMM2 = the hardware-scaled kernel)
