@@ -229,7 +229,10 @@ def main():
     # the published figures use the whole chip for communication; so does this benchmark unless told otherwise
     num_sms = args.num_sms or min(128, deep_ep._C.get_num_device_sms())
 
-    # synthetic inputs, generated on the host in pinned memory (the end-to-end arm copies them every step)
+    # synthetic inputs, generated on the host in pinned memory (the end-to-end arm copies them every step); the process
+    # first moves to the CPUs next to its GPU so that those buffers are local to the GPU's PCIe root
+    from deep_ep.utils.envs import bind_to_device_numa_node
+    numa_node = bind_to_device_numa_node(local_rank)
     x_host = torch.randn(T, H, dtype=torch.bfloat16).pin_memory()
     logits_host = torch.randn(T, E)
     top_logits, topk_idx_host = logits_host.topk(K, dim=-1)
@@ -397,7 +400,9 @@ def main():
             line['e2e'] = {'value': round(sum_dispatch_bytes / (e2e_ms_max * 1e6), 2),
                            'unit': 'GB/s of dispatch bytes over the whole end-to-end step (H2D + fused-quant dispatch + expand + combine + reduce + D2H)',
                            'step_ms': round(e2e_ms_max, 4), 'step_gbs_dispatch_plus_combine': round(step_bytes / (e2e_ms_max * 1e6), 2),
-                           'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': d2h_bytes}
+                           'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': d2h_bytes,
+                           'input_pipeline': 'pinned host buffers on the NUMA node of the GPU (node %s of rank 0); the copy of step i + 1 '
+                                             'overlaps the kernels of step i' % numa_node}
         print(json.dumps(line))
     buffer.destroy()
     dist.destroy_process_group()

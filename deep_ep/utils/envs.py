@@ -24,6 +24,34 @@ def default_device() -> torch.device:
     return torch.device('cuda', torch.cuda.current_device()) if has_cuda() else torch.device('cpu')
 
 
+def bind_to_device_numa_node(device_index: int) -> Optional[int]:
+    """Restrict this process to the CPUs of the NUMA node that the given GPU is attached to.
+
+    Pinned host buffers allocated afterwards then sit in memory local to the GPU's PCIe root, which is what host-to-device
+    copies of several ranks at once are limited by on two-socket machines. Only this process's CPU affinity changes.
+    Returns the node, or `None` when it cannot be determined (nothing is changed then).
+    """
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        bus = f'{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0'
+        with open(f'/sys/bus/pci/devices/{bus}/numa_node') as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f'/sys/devices/system/node/node{node}/cpulist') as f:
+            cpus = set()
+            for part in f.read().strip().split(','):
+                lo, _, hi = part.partition('-')
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:   # no CUDA device, no sysfs, no permission: leave the process as it is
+        return None
+
+
 def init_seed(global_seed: int) -> None:
     """Seed torch and `random` with `global_seed + rank` so that ranks draw different data."""
     global _local_seed, _global_seed

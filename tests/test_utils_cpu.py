@@ -146,3 +146,12 @@ def test_parallel_namespace_lists_every_strategy():
     assert par.BucketBuffer is deep_ep.BucketBuffer and par.EngramBuffer is deep_ep.EngramBuffer
     assert {cls.__name__ for group in (par.ep, par.pp, par.dp, par.engram) for cls in group} >= {
         'EPBuffer', 'PPBuffer', 'BucketBuffer', 'EngramBuffer', 'MoELayer'}
+
+
+def test_numa_binding_is_a_noop_without_a_gpu():
+    import os
+    from deep_ep.utils.envs import bind_to_device_numa_node
+    before = os.sched_getaffinity(0)
+    if not torch.cuda.is_available():
+        assert bind_to_device_numa_node(0) is None
+        assert os.sched_getaffinity(0) == before
