@@ -138,6 +138,7 @@ public:
         kernels::BucketReduceArgs args = {};
         args.peers = context->peers, args.cs = context->common_signals, args.host_status = context->host_status_device;
         args.timeout_ns = context->num_gpu_timeout_ns, args.scale = scale, args.all_reduce = all_reduce;
+        args.use_multicast = context->peers.mc_base != nullptr;      // NVLS route (EP_NVLS=1): the switch adds and broadcasts
         args.list.num_buckets = static_cast<int>(srcs.size());
         std::vector<torch::Tensor> results;
         const auto storage_ptr = reinterpret_cast<int64_t>(storage.data_ptr());

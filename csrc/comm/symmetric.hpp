@@ -17,6 +17,8 @@
 #include <deep_ep/common/exception.hpp>
 #include <deep_ep/common/compiled.hpp>
 
+#include "vmm.hpp"
+
 namespace deep_ep::comm {
 
 // Peer mappings are cached per process: a peer allocation shared by several groups is opened once.
@@ -59,19 +61,30 @@ class SymmetricMemory {
 public:
     void* ptr = nullptr;
     int64_t num_bytes = 0;
+    // set on the virtual-memory-management route (`EP_SYMMETRIC_VMM=1` / `EP_NVLS=1`), see vmm.hpp
+    std::unique_ptr<VmmAllocation> vmm;
+    size_t vmm_granularity_bytes = 0;
 
-    explicit SymmetricMemory(int64_t num_bytes) : num_bytes(num_bytes) {
+    SymmetricMemory(int64_t num_bytes, bool use_vmm = false, int num_ranks = 1, bool with_multicast = false) : num_bytes(num_bytes) {
         EP_HOST_ASSERT(num_bytes > 0 and num_bytes % kNumAllocationAlignmentBytes == 0);
+        if (use_vmm) {
+            CUDA_CHECK(cudaFree(nullptr));          // the driver calls need a current context
+            vmm_granularity_bytes = vmm_granularity(num_ranks, with_multicast);
+            vmm = std::make_unique<VmmAllocation>(static_cast<size_t>(num_bytes), vmm_granularity_bytes);
+            ptr = reinterpret_cast<void*>(vmm->va);
+            return;
+        }
         CUDA_CHECK(cudaMalloc(&ptr, static_cast<size_t>(num_bytes)));
         CUDA_CHECK(cudaMemset(ptr, 0, static_cast<size_t>(num_bytes)));
         CUDA_CHECK(cudaDeviceSynchronize());
     }
     SymmetricMemory(const SymmetricMemory&) = delete;
     ~SymmetricMemory() {
-        if (ptr != nullptr) cudaFree(ptr);
+        if (vmm == nullptr and ptr != nullptr) cudaFree(ptr);
     }
 
     std::string export_handle() const {
+        EP_HOST_ASSERT(vmm == nullptr);
         cudaIpcMemHandle_t handle;
         CUDA_CHECK(cudaIpcGetMemHandle(&handle, ptr));
         return std::string(reinterpret_cast<const char*>(&handle), sizeof(handle));

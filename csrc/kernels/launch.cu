@@ -137,6 +137,11 @@ void all_gather(const kernels::AllGatherArgs& args, int num_sms, cudaStream_t st
 
 void bucket_reduce(const kernels::BucketReduceArgs& args, int num_sms, cudaStream_t stream) {
     const int sms = clamp_sms(num_sms);
+    if (args.use_multicast) {
+        EP_HOST_ASSERT(args.peers.mc_base != nullptr);
+        launch_kernel(kernels::bucket_reduce_multicast_kernel, args, sms, 256, 0, true, stream);
+        return;
+    }
     switch (args.peers.num_ranks) {
         case 1: launch_kernel(kernels::bucket_reduce_kernel<1>, args, sms, 256, 0, true, stream); break;
         case 2: launch_kernel(kernels::bucket_reduce_kernel<2>, args, sms, 256, 0, true, stream); break;

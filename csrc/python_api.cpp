@@ -236,6 +236,24 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("get_npu_arch", [] { return Runtime::get().get_arch(); });
     m.def("set_npu_arch", [](const std::string& a) { Runtime::get().set_arch(a); });
     jit::register_python_api(m);
+    // Host-only self-test of the descriptor exchange used by the virtual-memory-management route: a pipe's two ends travel
+    // through `FdServer` / `receive_fds` inside this process and must still be connected to each other afterwards.
+    m.def("fd_exchange_selftest", [] {
+        int ends[2];
+        EP_HOST_ASSERT(::pipe(ends) == 0);
+        bool ok = false;
+        {
+            comm::FdServer server({ends[0], ends[1]}, 1, 10);
+            const auto received = comm::receive_fds(server.name, 2, 10);
+            const char out = 'x';
+            char in = 0;
+            ok = ::write(received[1], &out, 1) == 1 and ::read(ends[0], &in, 1) == 1 and in == out and
+                 received[0] != ends[0] and received[1] != ends[1];
+            ::close(received[0]), ::close(received[1]);
+        }
+        ::close(ends[0]), ::close(ends[1]);
+        return ok;
+    });
 
     py::class_<EventHandle>(m, "EventHandle")
         .def(py::init<>())
@@ -249,7 +267,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readonly("num_gpu_buffer_bytes", &comm::Context::num_gpu_buffer_bytes)
         .def_readonly("num_rdma_storage_bytes", &comm::Context::num_rdma_storage_bytes)
         .def_readonly("peers_ready", &comm::Context::peers_ready)
-        .def("get_local_handle", [](const comm::Context& c) { return py::bytes(c.get_local_handle()); })
+        .def("get_local_handle", [](comm::Context& c) { return py::bytes(c.get_local_handle()); })
+        .def("multicast_pending", &comm::Context::multicast_pending)
+        .def("bind_multicast", &comm::Context::bind_multicast)
+        .def("has_multicast", [](const comm::Context& c) { return c.peers.mc_base != nullptr; })
         .def("set_peer_handles", [](comm::Context& c, const std::vector<py::bytes>& handles) {
             std::vector<std::string> raw;
             for (const auto& h : handles) raw.emplace_back(static_cast<std::string>(h));

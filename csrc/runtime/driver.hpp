@@ -35,6 +35,24 @@ EP_DRIVER_FN(cuModuleLoad)
 EP_DRIVER_FN(cuModuleGetFunction)
 EP_DRIVER_FN(cuFuncSetAttribute)
 EP_DRIVER_FN(cuLaunchKernelEx)
+// virtual memory management and NVLink multicast (the optional NVLS route of the symmetric allocation)
+EP_DRIVER_FN(cuCtxGetDevice)
+EP_DRIVER_FN(cuDeviceGetAttribute)
+EP_DRIVER_FN(cuMemGetAllocationGranularity)
+EP_DRIVER_FN(cuMemCreate)
+EP_DRIVER_FN(cuMemRelease)
+EP_DRIVER_FN(cuMemAddressReserve)
+EP_DRIVER_FN(cuMemAddressFree)
+EP_DRIVER_FN(cuMemMap)
+EP_DRIVER_FN(cuMemUnmap)
+EP_DRIVER_FN(cuMemSetAccess)
+EP_DRIVER_FN(cuMemExportToShareableHandle)
+EP_DRIVER_FN(cuMemImportFromShareableHandle)
+EP_DRIVER_FN(cuMulticastGetGranularity)
+EP_DRIVER_FN(cuMulticastCreate)
+EP_DRIVER_FN(cuMulticastAddDevice)
+EP_DRIVER_FN(cuMulticastBindMem)
+EP_DRIVER_FN(cuMulticastUnbind)
 
 #undef EP_DRIVER_FN
 

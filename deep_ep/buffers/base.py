@@ -54,6 +54,11 @@ def connect_peers(context, group: dist.ProcessGroup) -> None:
             assert _C.check_peer_access(device, peer_device), f'GPU {device} cannot access GPU {peer_device} (rank {rank}) directly'
     handles = [h for h, _, _ in exchanged]
     context.set_peer_handles(handles)
+    if context.multicast_pending():
+        # NVLS route (EP_NVLS=1): every device has joined the multicast object; binding memory needs all of them in
+        dist.barrier(group)
+        context.bind_multicast()
+        dist.barrier(group)
 
 
 def sync_group(group: dist.ProcessGroup) -> None:

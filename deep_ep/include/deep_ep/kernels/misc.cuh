@@ -208,6 +208,57 @@ EP_DEVICE void store_result(const BucketReduceArgs& a, int64_t offset, const int
     }
 }
 
+// NVLS variants: one instruction fetches the 16-byte vector from every GPU of the multicast group and returns the sum
+// (accumulated in fp32 inside the switch), one instruction stores a vector to every GPU.
+template <int kDtype>
+EP_DEVICE int4 multimem_ld_reduce_v4(const void* mc_ptr) {
+    int4 v;
+    if constexpr (kDtype == kReduceFP32) {
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_ptr) : "memory");
+    } else if constexpr (kDtype == kReduceBF16) {
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_ptr) : "memory");
+    } else {
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_ptr) : "memory");
+    }
+    return v;
+}
+
+template <int kDtype>
+EP_DEVICE void reduce_bucket_multicast(const BucketReduceArgs& a, const layout::Bucket& bucket, int64_t& tile_base) {
+    constexpr int64_t kTileBytes = 64 * 1024;
+    constexpr int kUnroll = 4;
+    const int rank = a.peers.rank, num_ranks = a.peers.num_ranks;
+    const int64_t shard_bytes = bucket.num_bytes / num_ranks;
+    const int64_t base_off = bucket.dst_offset + int64_t(rank) * shard_bytes;
+    const int64_t num_tiles = math::ceil_div(shard_bytes, kTileBytes);
+    const int64_t step = int64_t(blockDim.x) * 16;
+    for (int64_t tile = (blockIdx.x + gridDim.x - tile_base % gridDim.x) % gridDim.x; tile < num_tiles; tile += gridDim.x) {
+        const int64_t begin = tile * kTileBytes, end = min(begin + kTileBytes, shard_bytes);
+        for (int64_t o = begin + threadIdx.x * 16; o < end; o += step * kUnroll) {
+            int4 v[kUnroll];
+            #pragma unroll
+            for (int u = 0; u < kUnroll; ++u)
+                v[u] = multimem_ld_reduce_v4<kDtype>(a.peers.mc_base + base_off + (o + u * step < end ? o + u * step : o));
+            #pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                if (o + u * step >= end) break;
+                int4 out = v[u];
+                if (a.scale != 1.0f) {
+                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    accumulate<kDtype>(acc, v[u]);
+                    out = finish<kDtype>(acc, a.scale);
+                }
+                if (a.all_reduce) ag_detail::multimem_st_v4(a.peers.mc_base + base_off + o + u * step, out);
+                else ptx::st_v4(a.peers.base[rank] + base_off + o + u * step, out);
+            }
+        }
+    }
+    tile_base += num_tiles;
+}
+
 // `kNumRanks` > 0: the group size is a compile-time constant and a thread keeps `16 / kNumRanks` vectors x `kNumRanks`
 // loads in flight (16 outstanding 16-byte loads: what covers the NVLink latency with one 256-thread CTA per SM).
 // `kNumRanks` == 0: any group size, one vector at a time, eight ranks per round of loads.
@@ -275,6 +326,24 @@ __global__ void __launch_bounds__(256) bucket_reduce_kernel(const __grid_constan
     __threadfence_system();
     if (not dev::grid_sync(a.cs, a.host_status, gridDim.x, a.timeout_ns, rank, /*where=*/46)) return;
     if (blockIdx.x == 0 and threadIdx.x < 32) dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, /*where=*/47);
+}
+
+// The same collective through the NVLink multicast mapping (`peers.mc_base`, present on the NVLS route only).
+__global__ void __launch_bounds__(256) bucket_reduce_multicast_kernel(const __grid_constant__ BucketReduceArgs a) {
+    const int rank = a.peers.rank;
+    if (not dev::healthy(a.cs)) return;
+    if (blockIdx.x == 0 and threadIdx.x < 32) dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, /*where=*/48);
+    if (not dev::grid_sync(a.cs, a.host_status, gridDim.x, a.timeout_ns, rank, /*where=*/49)) return;
+    int64_t tile_base = 0;
+    for (int b = 0; b < a.list.num_buckets; ++b) {
+        const layout::Bucket& bucket = a.list.buckets[b];
+        if (a.dtype[b] == kReduceFP32) reduce_detail::reduce_bucket_multicast<kReduceFP32>(a, bucket, tile_base);
+        else if (a.dtype[b] == kReduceBF16) reduce_detail::reduce_bucket_multicast<kReduceBF16>(a, bucket, tile_base);
+        else reduce_detail::reduce_bucket_multicast<kReduceFP16>(a, bucket, tile_base);
+    }
+    __threadfence_system();
+    if (not dev::grid_sync(a.cs, a.host_status, gridDim.x, a.timeout_ns, rank, /*where=*/50)) return;
+    if (blockIdx.x == 0 and threadIdx.x < 32) dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, /*where=*/51);
 }
 
 // ---------------------------------------------------------------------------------------- load balancing

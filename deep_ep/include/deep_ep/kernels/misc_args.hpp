@@ -49,6 +49,8 @@ struct BucketReduceArgs {
     int dtype[kMaxBuckets];           // ReduceDtype per bucket
     float scale;                      // applied to the fp32 sum before it is rounded to the tensor's dtype
     int all_reduce;                   // 0: the reduced shard stays on its owner; 1: it is also stored to every peer
+    int use_multicast;                // 1: `multimem.ld_reduce` / `multimem.st` through `peers.mc_base` (the NVSwitch adds and
+                                      //    broadcasts; the order of the additions is the switch's, not rank order)
 };
 
 struct PPArgs {

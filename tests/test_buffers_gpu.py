@@ -475,3 +475,43 @@ def _lb_worker(rank, world):
 @pytest.mark.gpu
 def test_lb_prefetch_and_reduce(master_port):
     run_distributed(_lb_worker, _world(), master_port, 'nccl')
+
+
+def _nvls_worker(rank, world):
+    """Symmetric allocation through the virtual-memory-management route with an NVLink multicast object (`EP_NVLS=1`):
+    all-gather through `multimem.st`, all-reduce through `multimem.ld_reduce` + `multimem.st`."""
+    import os
+    import torch.distributed as dist
+    os.environ['EP_NVLS'] = '1'
+    import deep_ep
+    group = dist.group.WORLD
+    bucket = deep_ep.BucketBuffer(group, 64 << 20, explicitly_destroy=True, num_gpu_timeout_secs=10)
+    assert bucket.contexts[0].has_multicast()
+    with bucket.session() as session:
+        n = 8 * 4096
+        gathered = session.allocate((world, n), torch.bfloat16)
+        gathered.fill_(float('nan'))
+        gathered[rank] = rank + 1
+        out = bucket.all_gather(gathered[rank]).wait()
+        assert torch.equal(out.view(world, n)[:, 0].float(), torch.arange(world, device='cuda').float() + 1)
+        assert torch.equal(out.view(world, n)[:, -1].float(), torch.arange(world, device='cuda').float() + 1)
+        for dtype in (torch.float32, torch.bfloat16):
+            t = session.allocate((world * 8 * 1000,), dtype)
+            g = torch.Generator(device='cuda').manual_seed(7 + rank)
+            mine = torch.randn(t.numel(), device='cuda', generator=g).to(dtype)
+            t.copy_(mine)
+            ref = mine.float().clone()
+            dist.all_reduce(ref)
+            got = bucket.all_reduce(t, scale=0.5).wait()
+            # the switch chooses the order of the additions: equal up to rounding, not bitwise
+            assert torch.allclose(got.float(), (ref * 0.5).to(dtype).float(), atol=0.05 * world, rtol=0.02), f'all_reduce {dtype}'
+    torch.cuda.synchronize()
+    bucket.destroy()
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(__import__('os').environ.get('EP_TEST_NEW_PATHS', '0') != '1',
+                    reason='path that has not run on a GPU yet; set EP_TEST_NEW_PATHS=1 to try it')
+def test_nvls_route_all_gather_and_all_reduce(master_port):
+    run_distributed(_nvls_worker, _world(), master_port, 'nccl')

@@ -155,3 +155,9 @@ def test_numa_binding_is_a_noop_without_a_gpu():
     if not torch.cuda.is_available():
         assert bind_to_device_numa_node(0) is None
         assert os.sched_getaffinity(0) == before
+
+
+def test_descriptor_exchange_between_processes_of_a_node():
+    """The file-descriptor hand-over that the virtual-memory-management route of the symmetric allocation relies on."""
+    import deep_ep
+    assert deep_ep._C.fd_exchange_selftest()
