@@ -77,9 +77,12 @@ public:
             // object of the group (`multimem.*` instructions); EP_SYMMETRIC_VMM=1: the same allocation route without multicast
             const bool want_multicast = env_flag("EP_NVLS") and num_ranks > 1;
             const bool use_vmm = want_multicast or env_flag("EP_SYMMETRIC_VMM");
+            if (want_multicast) {
+                CUDA_CHECK(cudaFree(nullptr));      // the driver query needs a current context
+                EP_HOST_ASSERT_MSG(multicast_supported(), "EP_NVLS=1 but this GPU reports no multicast support");
+            }
             memory = std::make_shared<SymmetricMemory>(num_workspace_bytes + num_gpu_buffer_bytes + num_rdma_storage_bytes,
                                                        use_vmm, num_ranks, want_multicast);
-            if (want_multicast) EP_HOST_ASSERT_MSG(multicast_supported(), "EP_NVLS=1 but this GPU reports no multicast support");
             wants_multicast = want_multicast;
         }
         workspace = memory->ptr;
@@ -203,6 +206,7 @@ public:
         for (const auto& h : opened_handles) IpcMappingCache::get().close(h);
         opened_handles.clear();
         if (multicast != nullptr) {
+            multicast->unmap();
             if (multicast_bound) driver::cuMulticastUnbind()(multicast->handle, vmm_detail::current_device(), 0, memory->vmm->size);
             multicast = nullptr, peers.mc_base = nullptr;
         }

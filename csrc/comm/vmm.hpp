@@ -236,11 +236,15 @@ public:
         DRV_CHECK(driver::cuMemSetAccess()(va, size, &access, 1));
     }
 
+    void unmap() {
+        if (va == 0) return;
+        driver::cuMemUnmap()(va, size);
+        driver::cuMemAddressFree()(va, size);
+        va = 0;
+    }
+
     ~VmmPeerMapping() {
-        if (va != 0) {
-            driver::cuMemUnmap()(va, size);
-            driver::cuMemAddressFree()(va, size);
-        }
+        unmap();
         if (handle != 0) driver::cuMemRelease()(handle);
     }
 };
