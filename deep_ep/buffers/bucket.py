@@ -10,7 +10,7 @@ from .._C_loader import _C
 from ..utils.event import EventOverlap
 from ..utils.math import align
 from .allocator import BufferAllocator
-from .base import BufferBase, connect_peers
+from .base import BufferBase, connect_peers, sync_group
 
 
 class BucketSession:
@@ -149,17 +149,22 @@ class BucketBuffer(BufferBase):
         self.num_bytes = num_bytes
         self._active_session: Optional[BucketSession] = None
         super().__init__(explicitly_destroy)
-        self.runtime = _C.BucketBuffer([g.rank() for g in self.groups], [g.size() for g in self.groups],
-                                       [h.get() for h in self.comm_handles], num_bytes, use_huge1g_page,
-                                       num_gpu_timeout_secs, explicitly_destroy)
+        self.is_simulated = not torch.cuda.is_available()
+        if self.is_simulated:
+            # CPU process groups (gloo): same Python layer over `deep_ep.sim.buffers.SimBucketRuntime`
+            from ..sim.buffers import SimBucketRuntime
+            self.runtime = SimBucketRuntime(self.groups, num_bytes)
+        else:
+            self.runtime = _C.BucketBuffer([g.rank() for g in self.groups], [g.size() for g in self.groups],
+                                           [h.get() for h in self.comm_handles], num_bytes, use_huge1g_page,
+                                           num_gpu_timeout_secs, explicitly_destroy)
         self.contexts = self.runtime.contexts
-        for context, g in zip(self.contexts, self.groups):
-            connect_peers(context, g)
+        if not self.is_simulated:
+            for context, g in zip(self.contexts, self.groups):
+                connect_peers(context, g)
         self.storage = self.runtime.storage
-        torch.cuda.synchronize()
         for g in self.groups:
-            dist.barrier(g)
-        torch.cuda.synchronize()
+            sync_group(g)
         if plan is not None:
             plan.materialize(self.storage)
 

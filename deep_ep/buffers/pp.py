@@ -32,9 +32,14 @@ class PPBuffer(BufferBase):
         self.rank_idx, self.num_ranks = group.rank(), group.size()
         self.comm_handle = comm.get_comm_handle(group)
         super().__init__(explicitly_destroy)
-        self.runtime = _C.PPBuffer(self.rank_idx, self.num_ranks, self.comm_handle.get(), num_max_tensor_bytes,
-                                   num_max_inflight_tensors, use_huge1g_page, num_gpu_timeout_secs, explicitly_destroy)
-        connect_peers(self.runtime.context, group)
+        self.is_simulated = not torch.cuda.is_available()
+        if self.is_simulated:
+            from ..sim.buffers import SimPPRuntime
+            self.runtime = SimPPRuntime(group, num_max_tensor_bytes, num_max_inflight_tensors)
+        else:
+            self.runtime = _C.PPBuffer(self.rank_idx, self.num_ranks, self.comm_handle.get(), num_max_tensor_bytes,
+                                       num_max_inflight_tensors, use_huge1g_page, num_gpu_timeout_secs, explicitly_destroy)
+            connect_peers(self.runtime.context, group)
         self.context = self.runtime.context
         self.storage = self.runtime.storage
         sync_group(group)
