@@ -197,13 +197,13 @@ def _ue8m0_ceil(amax_over_448: torch.Tensor):
 
 def per_token_cast_to_fp8_ue8m0(x: torch.Tensor):
     """`[m, n]` -> `(e4m3 [m, n], uint8 [m, n / 128])` with power-of-two scales `2^ceil(log2(amax / 448))` stored as UE8M0
-    bytes: the format the hardware-scaled FP8 GEMM reads."""
-    m, n = x.shape
-    assert n % 128 == 0
-    groups = x.float().reshape(m, n // 128, 128)
-    byte, scale = _ue8m0_ceil(groups.abs().amax(dim=2).clamp(min=1e-4) * (1.0 / 448.0))
-    q = (groups / scale.unsqueeze(2)).to(torch.float8_e4m3fn).reshape(m, n)
-    return q.contiguous(), byte.contiguous()
+    bytes: the format the hardware-scaled FP8 GEMM reads. Same quantiser as
+    `deep_ep.utils.math.per_token_cast_to_fp8(x, round_scale=True)` (and as the dispatch kernel's `'ue8m0'` mode), with
+    the scales reduced to their exponent byte."""
+    from ..utils.math import per_token_cast_to_fp8
+    assert x.size(1) % 128 == 0
+    q, scale = per_token_cast_to_fp8(x, round_scale=True)
+    return q, ((scale.contiguous().view(torch.int32) >> 23) & 0xff).to(torch.uint8).contiguous()
 
 
 def per_block_cast_to_fp8_ue8m0(w: torch.Tensor):
