@@ -65,6 +65,14 @@ def main():
         for e, (s, c) in enumerate(ranges):
             torch.mm(a[s:s + c], w[e].t())
 
+    # library grouped GEMM (`torch.nn.functional.grouped_mm`, one launch for all experts) as a second baseline for the
+    # forward GEMMs; group e spans its aligned region, i.e. it also multiplies the zero padding rows
+    region_ends = (starts + aligned).int().to(dev)
+    grouped_mm = getattr(torch.nn.functional, 'grouped_mm', None)
+
+    def library_grouped(a, w):
+        return grouped_mm(a, w.transpose(-2, -1), offs=region_ends)
+
     cases = {
         'gemm1_forward': (lambda: gg.grouped_gemm_forward(x, w1, psum, count), lambda: torch_fwd(x, w1), 2 * useful * h * 2 * i),
         'gemm1_forward_swiglu': (lambda: gg.grouped_gemm_forward(x, w1, psum, count, swiglu=True), None, 2 * useful * h * 2 * i),
@@ -111,6 +119,14 @@ def main():
         if ref is not None and not args.skip_torch:
             r_min, r_avg = bench(ref, args.iters)
             entry.update({'torch_loop_ms': round(r_avg, 4), 'torch_loop_tflops': round(flops / (r_avg * 1e-3) / 1e12, 1)})
+        if name in ('gemm1_forward', 'gemm2_forward') and grouped_mm is not None and not args.skip_torch:
+            operands = (x, w1) if name == 'gemm1_forward' else (act, w2)
+            try:
+                g_min, g_avg = bench(lambda: library_grouped(*operands), args.iters)
+                entry.update({'torch_grouped_mm_ms': round(g_avg, 4),
+                              'torch_grouped_mm_tflops': round(flops / (g_avg * 1e-3) / 1e12, 1)})
+            except Exception as e:      # not available for this architecture / build
+                entry['torch_grouped_mm_error'] = str(e).splitlines()[0][:200]
         out['results'][name] = entry
     print(json.dumps(out))
 
