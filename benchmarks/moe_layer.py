@@ -27,8 +27,10 @@ from deep_ep.models.moe_layer import MoEConfig, MoELayer  # noqa: E402
 class BaselineMoELayer(nn.Module):
     """Permute by expert, `all_to_all_single` the (token, expert) copies, per-expert `F.linear`, exchange back, weighted sum."""
 
-    def __init__(self, ours: MoELayer):
+    def __init__(self, ours: MoELayer, use_grouped_mm: bool = False):
         super().__init__()
+        # expert GEMMs: one cuBLAS call per expert (default) or the library's grouped GEMM, `F.grouped_mm`, one per layer
+        self.use_grouped_mm = use_grouped_mm
         self.group, self.config = ours.group, ours.config
         self.world = ours.num_ranks
         self.num_local_experts = ours.num_local_experts
@@ -60,6 +62,11 @@ class BaselineMoELayer(nn.Module):
                                                 counts.reshape(-1))
         by_expert = torch.argsort(expert_of_row, stable=True)
         rows = recv[by_expert]
+        if self.use_grouped_mm:
+            offs = counts.sum(0).cumsum(0).int()
+            g, u = F.grouped_mm(rows, self.w_gate_up.transpose(-2, -1), offs=offs).chunk(2, dim=-1)
+            out = F.grouped_mm(F.silu(g) * u, self.w_down.transpose(-2, -1), offs=offs)
+            return self._finish(x, out, by_expert, sc, rc, topk_w, order, k)
         outs, start = [], 0
         # unbind once: indexing the stacked parameter per expert would make autograd materialise a full-size
         # gradient of all experts for every expert
@@ -70,6 +77,9 @@ class BaselineMoELayer(nn.Module):
                 outs.append(F.linear(F.silu(g) * u, w2s[e]))
             start += c
         out = torch.cat(outs) if outs else torch.empty_like(rows)
+        return self._finish(x, out, by_expert, sc, rc, topk_w, order, k)
+
+    def _finish(self, x, out, by_expert, sc, rc, topk_w, order, k):
         back_rows = torch.empty_like(out)
         back_rows[by_expert] = out
         back = dist_fn.all_to_all_single(torch.empty((sum(sc), x.size(1)), dtype=x.dtype, device=x.device), back_rows, sc, rc,
@@ -130,6 +140,8 @@ def main():
     p.add_argument('--steps', type=int, default=10)
     p.add_argument('--warmup', type=int, default=3)
     p.add_argument('--skip-baseline', action='store_true')
+    p.add_argument('--baseline-grouped-mm', action='store_true',
+                   help='baseline expert GEMMs through torch.nn.functional.grouped_mm instead of one cuBLAS call per expert')
     p.add_argument('--fuse-combine', action='store_true',
                    help='let the second expert GEMM store single-row tokens straight into the combine landing slots of their owners')
     p.add_argument('--forward-fp8', action='store_true',
@@ -152,7 +164,8 @@ def main():
     result = {'bench': 'moe_layer_fwd_bwd', 'n_gpus': world, 'tokens_per_rank': args.num_tokens, 'hidden': args.hidden,
               'intermediate': args.intermediate, 'experts': args.num_experts, 'topk': args.num_topk, 'dtype': 'bf16', 'fuse_combine': args.fuse_combine}
     if not args.skip_baseline:
-        base = BaselineMoELayer(ours).to(dev)
+        base = BaselineMoELayer(ours, use_grouped_mm=args.baseline_grouped_mm).to(dev)
+        result['baseline_gemm'] = 'F.grouped_mm' if args.baseline_grouped_mm else 'per-expert F.linear'
         with torch.no_grad():                      # same function, different plumbing: outputs must agree
             y_ours, y_base = ours(x), base(x)
         rel = ((y_ours.float() - y_base.float()).norm() / y_base.float().norm()).item()
