@@ -65,6 +65,8 @@ def _wgrad(dy, x, w, psum, count, alignment):
     """Weight gradient of one grouped linear layer, honouring a persistent fp32 `main_grad` buffer on the parameter."""
     main_grad = getattr(w, 'main_grad', None)
     if alignment % 64 == 0:
+        # fp32 accumulation happens in tensor memory; without a persistent fp32 buffer the result is rounded once and
+        # stored in the parameter's dtype, which avoids materialising an fp32 copy of every expert
         acc = main_grad if main_grad is not None else torch.empty(w.shape, dtype=w.dtype, device=w.device)
         grouped_gemm_wgrad(dy, x, acc, psum, count, accumulate=main_grad is not None)
     else:
@@ -146,20 +148,7 @@ class GroupedLinear(torch.autograd.Function):
         x, w, psum, count = ctx.saved_tensors
         dy = dy.contiguous()
         dx = grouped_gemm_dgrad(dy, w, psum, count) if ctx.needs_input_grad[0] else None
-        dw = None
-        if ctx.needs_input_grad[1]:
-            main_grad = getattr(w, 'main_grad', None)
-            if ctx.alignment % 64 == 0:
-                # fp32 accumulation happens in tensor memory; without a persistent fp32 buffer the result is rounded
-                # once and stored in the parameter's dtype, which avoids materialising an fp32 copy of every expert
-                acc = main_grad if main_grad is not None else torch.empty(w.shape, dtype=w.dtype, device=w.device)
-                grouped_gemm_wgrad(dy, x, acc, psum, count, accumulate=main_grad is not None)
-            else:
-                acc = main_grad if main_grad is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
-                for e, (start, c) in enumerate(_ranges(psum, count)):
-                    if c:
-                        acc[e].addmm_(dy[start:start + c].float().t(), x[start:start + c].float())
-            dw = None if main_grad is not None else (acc if acc.dtype == w.dtype else acc.to(w.dtype))
+        dw = _wgrad(dy, x, w, psum, count, ctx.alignment) if ctx.needs_input_grad[1] else None
         return dx, dw, None, None, None
 
 
