@@ -141,6 +141,28 @@ def main():
     result['pp_overlap'] = {'pp_ms': round(pp_ms, 3), 'gemm_ms': round(gemm_ms, 3), 'overlapped_ms': round(both_ms, 3),
                             'pp_gbs': round(act.nbytes / pp_ms / 1e6, 1),
                             'overlap_efficiency': round((pp_ms + gemm_ms - both_ms) / min(pp_ms, gemm_ms), 3)}
+
+    # the same exchange with NCCL point-to-point (send to the next rank, receive from the previous one), alone and
+    # overlapped with the GEMM, for comparison
+    if world > 1:
+        def nccl_pp():
+            ops = [dist.P2POp(dist.isend, act, nxt), dist.P2POp(dist.irecv, recv, prv)]
+            for work in dist.batch_isend_irecv(ops):
+                work.wait()
+
+        def nccl_overlapped():
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                nccl_pp()
+            torch.mm(act, w)
+            torch.cuda.current_stream().wait_stream(side)
+
+        try:
+            nccl_ms, nccl_both_ms = timed(nccl_pp, args.iters), timed(nccl_overlapped, args.iters)
+            result['pp_overlap'].update({'nccl_p2p_ms': round(nccl_ms, 3), 'nccl_p2p_overlapped_ms': round(nccl_both_ms, 3),
+                                         'nccl_p2p_gbs': round(act.nbytes / nccl_ms / 1e6, 1)})
+        except Exception as e:
+            result['pp_overlap']['nccl_p2p_error'] = str(e).splitlines()[0][:200]
     if rank == 0:
         print(json.dumps(result))
     pp.destroy()
