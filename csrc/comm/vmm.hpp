@@ -75,6 +75,13 @@ class FdServer {
             }
             const int conn = ::accept(listen_fd, nullptr, nullptr);
             if (conn < 0) continue;
+            // only processes of the same user may receive the descriptors
+            ucred cred;
+            socklen_t cred_len = sizeof(cred);
+            if (::getsockopt(conn, SOL_SOCKET, SO_PEERCRED, &cred, &cred_len) != 0 or cred.uid != ::geteuid()) {
+                ::close(conn);
+                continue;
+            }
             // one byte of payload carries the descriptors as ancillary data
             char payload = static_cast<char>(fds.size());
             iovec iov = {&payload, 1};
