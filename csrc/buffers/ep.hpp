@@ -340,7 +340,7 @@ public:
                             int num_experts, int num_max_tokens_per_rank, int num_sms,
                             const std::optional<EventHandle>& previous_event,
                             bool async_with_compute_stream, bool allocate_on_comm_stream, bool defer_epilogue,
-                            bool skip_single_rows) {
+                            bool skip_single_rows, bool apply_weights) {
         EP_HOST_ASSERT(not destroyed and context->peers_ready);
         (void) allocate_on_comm_stream;
         const int num_ranks = context->num_ranks;
@@ -381,7 +381,9 @@ public:
         args.host = host_counts_device, args.timeout_ns = context->num_gpu_timeout_ns;
         args.trace = trace_of(2);
         const bool coop = Runtime::get().get_warp_cooperation();
-        args.coop = coop, args.skip_single = skip_single_rows;
+        EP_HOST_ASSERT_MSG(not apply_weights or (topk_weights.has_value() and not skip_single_rows),
+                           "a weighted combine needs `topk_weights` and cannot be mixed with GEMM-delivered rows");
+        args.coop = coop, args.skip_single = skip_single_rows, args.weighted = apply_weights;
         launch::combine(args, num_sms, stream);
 
         const bool with_weights = topk_weights.has_value();

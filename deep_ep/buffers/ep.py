@@ -316,7 +316,7 @@ class EPBuffer(BufferBase):
                 bias: Union[None, torch.Tensor, Tuple[torch.Tensor, torch.Tensor]] = None,
                 num_sms: int = 0, num_qps: int = 0, previous_event: Optional[EventHandle] = None,
                 async_with_compute_stream: bool = False, allocate_on_comm_stream: bool = False,
-                defer_epilogue: bool = False, *, fused_single_rows: bool = False):
+                defer_epilogue: bool = False, *, fused_single_rows: bool = False, apply_weights: bool = False):
         """Reduce expert outputs back to the ranks that own the tokens.
 
         Arguments:
@@ -325,6 +325,8 @@ class EPBuffer(BufferBase):
             topk_weights: `[num_expanded_tokens]` fp32 or `None`; routed back positionally, never multiplied in.
             bias: `None`, one tensor or a tuple of two `[num_tokens, hidden]` bf16 tensors added before the partials.
             num_sms: ignored, combine uses `handle.num_sms`.
+            apply_weights: multiply every expanded row by its entry of `topk_weights` inside the kernel, before the
+                fp32 sum (the reference never multiplies weights in; off by default). The weights are still routed back.
             fused_single_rows: the rows of `x` that are their token's only row on this rank were not written to `x`
                 but stored by the producing GEMM straight into the owners' landing slots (`build_combine_route`);
                 combine then sends only the routed weights for them.
@@ -349,7 +351,7 @@ class EPBuffer(BufferBase):
             x, topk_weights, bias_0, bias_1, handle.recv_src_metadata, handle.topk_idx,
             handle.psum_num_recv_tokens_per_rank, handle.num_experts, handle.num_max_tokens_per_rank,
             handle.num_sms, previous_event, async_with_compute_stream, allocate_on_comm_stream, defer_epilogue,
-            fused_single_rows)
+            fused_single_rows, apply_weights)
         event_overlap = EventOverlap(event)
         if deferred_epilogue is not None:
             event_overlap.register_hook_after_wait(deferred_epilogue)

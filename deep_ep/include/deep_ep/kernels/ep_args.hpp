@@ -78,6 +78,7 @@ struct CombineArgs {
     int num_warps, num_stages;
     unsigned long long* trace;        // optional phase stamps, see DispatchArgs
     int coop;                         // 1: when rows are scarce, several warps of a CTA share a row (decode-sized calls)
+    int weighted;                     // 1: every expanded row is multiplied by its entry of `topk_weights` before the sum
     int skip_single;                  // 1: rows that are their token's only one were already stored into the owner's landing
                                       //    slot by a GEMM epilogue (`ep_route.cuh`); only their routed weights are sent
 };

@@ -100,6 +100,47 @@ EP_DEVICE void reduce_rows(const uint8_t* x, int hidden_bytes, int c_begin, int 
     }
 }
 
+EP_DEVICE void accumulate_scaled(float (&acc)[8], const int4& v, float scale) {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = ptx::bf16x2_to_float2(w[i]);
+        acc[2 * i] = fmaf(scale, f.x, acc[2 * i]), acc[2 * i + 1] = fmaf(scale, f.y, acc[2 * i + 1]);
+    }
+}
+
+// Opt-in weighted variant: fp32 sum of `weight_j * row_j` in top-k order, one rounding to bf16 (lane j holds the slot and
+// the weight of top-k position j). Four chunks per lane are in flight per row.
+EP_DEVICE void reduce_rows_weighted(const uint8_t* x, int hidden_bytes, int c_begin, int chunks, int my_slot, float my_weight,
+                                    unsigned valid, int count, uint8_t* stage, int lane) {
+    for (int base = c_begin; base < chunks; base += 32 * 4) {           // warp-uniform trip count: shuffles inside
+        float acc[4][8];
+        #pragma unroll
+        for (int i = 0; i < 4; ++i)
+            #pragma unroll
+            for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+        for (int u = 0; u < count; ++u) {
+            const int src_lane = nth_set_bit(valid, u);
+            const int slot = __shfl_sync(0xffffffffu, my_slot, src_lane);
+            const float weight = __shfl_sync(0xffffffffu, my_weight, src_lane);
+            int4 v[4];
+            #pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int c = base + 32 * i + lane;
+                if (c < chunks) v[i] = ptx::ld_nc_v4(x + int64_t(slot) * hidden_bytes + c * 16);
+            }
+            #pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (base + 32 * i + lane < chunks) accumulate_scaled(acc[i], v[i], weight);
+        }
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = base + 32 * i + lane;
+            if (c < chunks) *reinterpret_cast<int4*>(stage + c * 16) = pack(acc[i]);
+        }
+    }
+}
+
 // Owner-side reduction of one token: fp32 sum of bias_0, bias_1 and the partials in slot order, one rounding to
 // bf16. `kChunks` 16-byte chunks per lane are in flight before the first add.
 template <int kParts, int kChunks>
@@ -236,7 +277,11 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
                 }
                 if (part == 0) dispatch_detail::wait_read_pending(S - 1);     // the store issued S rows ago has read the stage
                 ptx::named_barrier(bar_id, bar_threads);
-                reduce_rows(a.x, a.hidden_bytes, c_begin, c_end, my_slot, valid, count, stage, lane);
+                if (a.weighted and a.topk_weights != nullptr)
+                    reduce_rows_weighted(a.x, a.hidden_bytes, c_begin, c_end, my_slot, my_slot >= 0 ? a.topk_weights[my_slot] : 0.f,
+                                         valid, count, stage, lane);
+                else
+                    reduce_rows(a.x, a.hidden_bytes, c_begin, c_end, my_slot, valid, count, stage, lane);
                 if (part == 0 and lane < k)
                     reinterpret_cast<float*>(stage + tl.weight_offset())[lane] =
                         (my_slot >= 0 and a.topk_weights != nullptr) ? a.topk_weights[my_slot] : 0.f;
@@ -297,12 +342,18 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
                 continue;
             }
 
-            if (count == 1) {
+            // opt-in: rows are multiplied by their routing weights before the sum (single rows too, so no plain copy)
+            const bool weighted = a.weighted and a.topk_weights != nullptr;
+            const bool single_copy = count == 1 and not weighted;
+            if (single_copy) {
                 const int slot = __shfl_sync(0xffffffffu, my_slot, __ffs(valid) - 1);
                 if (lane == 0) {
                     ptx::mbarrier_arrive_expect_tx(&mbar[stage_idx], a.hidden_bytes);
                     ptx::bulk_load(stage, a.x + int64_t(slot) * a.hidden_bytes, a.hidden_bytes, &mbar[stage_idx]);
                 }
+            } else if (weighted) {
+                reduce_rows_weighted(a.x, a.hidden_bytes, 0, chunks, my_slot, my_slot >= 0 ? a.topk_weights[my_slot] : 0.f, valid,
+                                     count, stage, lane);
             } else {
                 reduce_rows(a.x, a.hidden_bytes, 0, chunks, my_slot, valid, count, stage, lane);
             }
@@ -311,7 +362,7 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
                     (my_slot >= 0 and a.topk_weights != nullptr) ? a.topk_weights[my_slot] : 0.f;
             ptx::fence_proxy_async_smem();
             __syncwarp();
-            if (count == 1) {
+            if (single_copy) {
                 if (not ptx::mbarrier_wait(&mbar[stage_idx], num_loads[stage_idx] & 1)) failed = true;
                 ++num_loads[stage_idx];
                 if (__any_sync(0xffffffffu, failed)) {

@@ -163,8 +163,10 @@ def expand(layout: DispatchLayout, inputs: List[RankInput], num_expanded_rows: i
     return recv_x, recv_sf, recv_w
 
 
-def combine_partials(x: torch.Tensor, topk_weights: Optional[torch.Tensor], metadata: torch.Tensor, num_topk: int):
-    """Per received row: fp32 sum of its expanded rows in top-k order -> bf16, and the routed weights."""
+def combine_partials(x: torch.Tensor, topk_weights: Optional[torch.Tensor], metadata: torch.Tensor, num_topk: int,
+                     apply_weights: bool = False):
+    """Per received row: fp32 sum of its expanded rows in top-k order -> bf16, and the routed weights. With
+    `apply_weights` every row is multiplied by its routing weight (fused multiply-add in fp32) before the sum."""
     slots = metadata[:, :num_topk].long()
     num_rows, hidden = metadata.size(0), x.size(1)
     acc = torch.zeros((num_rows, hidden), dtype=torch.float32)
@@ -172,7 +174,10 @@ def combine_partials(x: torch.Tensor, topk_weights: Optional[torch.Tensor], meta
     for j in range(num_topk):
         valid = slots[:, j] >= 0
         rows = valid.nonzero(as_tuple=True)[0]
-        acc[rows] += x[slots[rows, j]].float()
+        if apply_weights:
+            acc[rows] = torch.addcmul(acc[rows], x[slots[rows, j]].float(), topk_weights[slots[rows, j]].unsqueeze(1))
+        else:
+            acc[rows] += x[slots[rows, j]].float()
         if topk_weights is not None:
             weights[rows, j] = topk_weights[slots[rows, j]]
     return acc.to(x.dtype), weights
@@ -311,13 +316,15 @@ class SimEPRuntime:
 
     def combine(self, x, topk_weights, bias_0, bias_1, recv_src_metadata, topk_idx, psum_rank,
                 num_experts, num_max_tokens_per_rank, num_sms, previous_event,
-                async_with_compute_stream, allocate_on_comm_stream, defer_epilogue, skip_single_rows=False):
+                async_with_compute_stream, allocate_on_comm_stream, defer_epilogue, skip_single_rows=False,
+                apply_weights=False):
         from ..utils.event import EventHandle
         assert not skip_single_rows, 'GEMM epilogues that store into landing slots exist on CUDA only'
+        assert not apply_weights or topk_weights is not None, 'a weighted combine needs `topk_weights`'
         num_tokens, num_topk = topk_idx.shape
         num_recv = int(psum_rank[-1])
         metadata = recv_src_metadata[:num_recv]
-        partials, weights = combine_partials(x, topk_weights, metadata, num_topk)
+        partials, weights = combine_partials(x, topk_weights, metadata, num_topk, apply_weights)
         src_global = metadata[:, num_topk].long()
         gathered = self._gather((partials, weights, src_global))
 

@@ -66,6 +66,12 @@ def _worker(rank, world_size, deterministic):
         assert torch.equal(combined_w, topk_weights)
         expected = (x.unsqueeze(1) * topk_weights.unsqueeze(2)).sum(1)
         assert torch.allclose(combined, expected, atol=1e-5, rtol=1e-5)
+        # the same with the weights applied inside combine (opt-in; the reference's combine never multiplies them in)
+        combined_in, combined_w_in, _ = buffer.combine(recv_x, handle, topk_weights=recv_w, apply_weights=True)
+        assert torch.equal(combined_w_in, topk_weights)
+        assert torch.allclose(combined_in, expected, atol=1e-5, rtol=1e-5)
+        with pytest.raises(AssertionError):
+            buffer.combine(recv_x, handle, apply_weights=True)             # needs the weights
 
         # cached replay with new payload and new weights keeps the handle and the layout
         x2, w2 = torch.randn_like(x), torch.rand_like(topk_weights)

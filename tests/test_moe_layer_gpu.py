@@ -144,6 +144,24 @@ def _new_paths_worker(rank, world_size):
     assert torch.equal(plain8, fused8), 'fused combine route changes the FP8 result'
     layer8.destroy()
 
+    # weights applied inside the combine kernel against weights applied by the caller (one rounding less, so not bitwise)
+    with torch.inference_mode():
+        buffer = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=96, hidden=512, num_topk=4, explicitly_destroy=True,
+                                  num_gpu_timeout_secs=10, num_cpu_timeout_secs=30)
+        xb = torch.randn(96, 512, device=dev, dtype=torch.bfloat16)
+        idx = torch.rand(96, 8 * world_size, device=dev).topk(4, dim=-1).indices
+        w = torch.rand(96, 4, device=dev)
+        recv_x, _, recv_w, handle, _ = buffer.dispatch(xb, topk_idx=idx, topk_weights=w, num_experts=8 * world_size,
+                                                       expert_alignment=16, do_expand=True, do_zero_padding=True)
+        inside, w_back, _ = buffer.combine(recv_x, handle, topk_weights=recv_w, apply_weights=True)
+        outside, _, _ = buffer.combine((recv_x.float() * recv_w.unsqueeze(1)).to(torch.bfloat16), handle, topk_weights=recv_w)
+        torch.cuda.synchronize()
+        assert torch.equal(w_back, w)
+        expected = xb.float() * w.sum(dim=1, keepdim=True)
+        assert torch.allclose(inside.float(), expected, atol=3e-2, rtol=2e-2)
+        assert torch.allclose(inside.float(), outside.float(), atol=3e-2, rtol=2e-2)
+        buffer.destroy()
+
     deep_ep._C.set_warp_cooperation(True)
     try:
         with torch.inference_mode():
