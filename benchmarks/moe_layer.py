@@ -142,6 +142,7 @@ def main():
     p.add_argument('--skip-baseline', action='store_true')
     p.add_argument('--baseline-grouped-mm', action='store_true',
                    help='baseline expert GEMMs through torch.nn.functional.grouped_mm instead of one cuBLAS call per expert')
+    p.add_argument('--overlap-shared-expert', action='store_true', help='run the shared expert on a side stream')
     p.add_argument('--fuse-combine', action='store_true',
                    help='let the second expert GEMM store single-row tokens straight into the combine landing slots of their owners')
     p.add_argument('--forward-fp8', action='store_true',
@@ -157,7 +158,7 @@ def main():
     torch.manual_seed(7 + rank)
     cfg = MoEConfig(hidden=args.hidden, intermediate=args.intermediate, num_experts=args.num_experts, num_topk=args.num_topk,
                     num_shared_experts=1, num_max_tokens_per_rank=args.num_tokens, expert_alignment=128,
-                    fuse_combine=args.fuse_combine)
+                    fuse_combine=args.fuse_combine, overlap_shared_expert=args.overlap_shared_expert)
     ours = MoELayer(dist.group.WORLD, cfg, device=dev)
     x = torch.randn(args.num_tokens, args.hidden, device=dev, dtype=torch.bfloat16, requires_grad=True)
 

@@ -28,6 +28,7 @@ class MoEConfig:
                                         # dispatch kernel) feeding block-scaled FP8 expert GEMMs
     fp8_scales: str = 'fp32'            # 'fp32': scales amax / 448, promoted in registers by the GEMM; 'ue8m0': powers of two,
                                         # applied by the tensor core (hidden and intermediate must be multiples of 512)
+    overlap_shared_expert: bool = False # run the shared expert on a side stream next to dispatch / routed experts / combine
     fuse_combine: bool = False          # the second expert GEMM stores the rows of single-row tokens straight into their
                                         # owners' combine landing slots (over NVLink, tile by tile); combine sends the rest
     expert_backend: str = 'grouped'     # 'grouped': hand-written grouped GEMM kernels, 'torch': per-expert torch.mm
@@ -103,6 +104,7 @@ class MoELayer(nn.Module):
             explicitly_destroy=True)
         self._handle: Optional[EPHandle] = None
         self._backward_route_used = False
+        self._side_stream = None
 
     def destroy(self) -> None:
         if self._own_buffer and self.buffer is not None:
@@ -169,7 +171,19 @@ class MoELayer(nn.Module):
             out = out + F.linear(F.silu(g) * u, self.shared_down)
         return out
 
+    def _shared_expert(self, x: torch.Tensor) -> torch.Tensor:
+        g, u = F.linear(x, self.shared_gate_up).chunk(2, dim=-1)
+        return F.linear(F.silu(g) * u, self.shared_down)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shared = None
+        if self.config.num_shared_experts > 0 and self.config.overlap_shared_expert and x.is_cuda:
+            # the shared expert only needs `x`: it runs on its own stream while the routed path communicates
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream()
+            self._side_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._side_stream):
+                shared = self._shared_expert(x)
         topk_idx, topk_weights = self.route(x.detach())
         recv_x, recv_w = _Dispatch.apply(x, topk_idx, topk_weights.float().contiguous(), self)
         handle = self._handle
@@ -181,7 +195,10 @@ class MoELayer(nn.Module):
             self.buffer.barrier()
         y = self.experts(recv_x, recv_w, handle, route)
         out = _Combine.apply(y, self, handle, route is not None)
-        if self.config.num_shared_experts > 0:
-            g, u = F.linear(x, self.shared_gate_up).chunk(2, dim=-1)
-            out = out + F.linear(F.silu(g) * u, self.shared_down)
+        if shared is not None:
+            torch.cuda.current_stream().wait_stream(self._side_stream)
+            shared.record_stream(torch.cuda.current_stream())
+            out = out + shared
+        elif self.config.num_shared_experts > 0:
+            out = out + self._shared_expert(x)
         return out

@@ -132,6 +132,21 @@ def _new_paths_worker(rank, world_size):
     assert torch.equal(grads[0], grads[1]), 'fused combine route changes the input gradient'
     layer.destroy()
 
+    # shared expert on a side stream: same numbers, forward and backward
+    cfg_s = MoEConfig(hidden=512, intermediate=256, num_experts=8 * world_size, num_topk=4, num_shared_experts=1,
+                      num_max_tokens_per_rank=200, expert_alignment=128)
+    layer_s = MoELayer(dist.group.WORLD, cfg_s, device=dev)
+    results = []
+    for overlap in (False, True):
+        layer_s.config.overlap_shared_expert = overlap
+        xs = x.clone().requires_grad_()
+        ys = layer_s(xs)
+        ys.backward(torch.ones_like(ys))
+        torch.cuda.synchronize()
+        results.append((ys.detach().clone(), xs.grad.clone()))
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    layer_s.destroy()
+
     # the same through the FP8 inference path with power-of-two scales (GEMM2 = the hardware-scaled kernel)
     cfg8 = MoEConfig(hidden=512, intermediate=512, num_experts=8 * world_size, num_topk=4, num_max_tokens_per_rank=200,
                      expert_alignment=128, fp8_scales='ue8m0')
