@@ -93,17 +93,26 @@ class BaselineMoELayer(nn.Module):
 
 
 def time_layer(layer, x, steps, warmup):
+    """Forward + backward per step. Gradients are dropped after every step (`zero_grad(set_to_none=True)` of a training
+    loop), for both layers alike: otherwise every step after the first would also pay an elementwise accumulation pass
+    over all expert weight gradients, which belongs to neither layer."""
     grad = torch.randn_like(x)
-    for _ in range(warmup):
+    params = list(layer.parameters())
+
+    def step():
         layer(x).backward(grad)
-    for p in layer.parameters():
-        p.grad = None
+        for p in params:
+            p.grad = None
+        x.grad = None
+
+    for _ in range(warmup):
+        step()
     torch.cuda.synchronize()
     dist.barrier()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     for a, b in ev:
         a.record()
-        layer(x).backward(grad)
+        step()
         b.record()
     torch.cuda.synchronize()
     ms = sum(a.elapsed_time(b) for a, b in ev) / steps
