@@ -154,6 +154,9 @@ def main():
     p.add_argument('--overlap-shared-expert', action='store_true', help='run the shared expert on a side stream')
     p.add_argument('--fuse-combine', action='store_true',
                    help='let the second expert GEMM store single-row tokens straight into the combine landing slots of their owners')
+    p.add_argument('--fp8-training', action='store_true',
+                   help='also time forward + backward with the routed experts\' forward and data-gradient GEMMs in FP8 '
+                        '(power-of-two block scales applied by the tensor core; weight gradients stay bf16)')
     p.add_argument('--forward-fp8', action='store_true',
                    help='also time the inference forward: BF16 path against the FP8 path (e4m3 dispatch + block-scaled FP8 GEMMs)')
     args = p.parse_args()
@@ -189,6 +192,21 @@ def main():
     flops = 3 * 2 * rows * args.hidden * args.intermediate * 3
     result['ours_tflops_per_gpu'] = round(flops / (result['ours_ms'] * 1e-3) / 1e12, 1)
     result['tokens_per_s_total'] = round(args.num_tokens * world / (result['ours_ms'] * 1e-3))
+    if args.fp8_training:
+        assert args.hidden % 512 == 0 and args.intermediate % 512 == 0
+        x.grad = None
+        ours(x).backward(torch.ones_like(x))
+        gx16 = x.grad.clone()
+        ours.config.fp8_training = True
+        x.grad = None
+        ours(x).backward(torch.ones_like(x))
+        result['fp8_training_dx_rel_diff_vs_bf16'] = round(((x.grad.float() - gx16.float()).norm() / gx16.float().norm()).item(), 5)
+        for p_ in ours.parameters():
+            p_.grad = None
+        result['ours_fp8_training_ms'] = round(time_layer(ours, x, args.steps, args.warmup), 3)
+        ours.config.fp8_training = False
+        ours._fp8_cache = None
+        torch.cuda.empty_cache()
     if args.forward_fp8:
         ours.quantize_weights()
         with torch.no_grad():

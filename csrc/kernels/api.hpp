@@ -58,6 +58,15 @@ void grouped_gemm_fp8(kernels::GroupedGemmFp8Args args, const void* a, int64_t a
 void swiglu_backward(const void* h, const void* dact, const float* row_scale, void* dh, int64_t rows, int inter,
                      cudaStream_t stream);
 
+// FP8 training path. Row-wise e4m3 quantisation of bf16 `x [rows, cols]` with one power-of-two scale (UE8M0 byte) per 128
+// columns; the SwiGLU of `h = [gate | up]` (times `row_scale`) as bf16 (`act`, optional) and quantised the same way; and
+// weights `w [rows, cols]` (stacked matrices of `n` rows) with one scale per 128 x 128 block plus, optionally, every matrix
+// transposed (`qt [rows / n, cols, n]`, `sft [rows / n, cols / 128, n / 128]`).
+void row_quant_ue8m0(const void* x, void* q, void* sf, int64_t rows, int cols, cudaStream_t stream);
+void swiglu_quant_ue8m0(const void* h, const float* row_scale, void* act, void* q, void* sf, int64_t rows, int inter,
+                        cudaStream_t stream);
+void block_quant_ue8m0(const void* w, void* q, void* sf, void* qt, void* sft, int64_t rows, int cols, int n, cudaStream_t stream);
+
 // Test hook: a one-warp kernel that waits (bounded) for a flag nobody sets and records the status.
 void bounded_wait_probe(layout::CommonSignals* cs, layout::HostStatus* host_status, long long timeout_ns,
                         cudaStream_t stream);

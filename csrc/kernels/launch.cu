@@ -169,6 +169,34 @@ void swiglu_backward(const void* h, const void* dact, const float* row_scale, vo
     launch_kernel(kernels::swiglu_backward_kernel, args, static_cast<int>(blocks), 256, 0, false, stream);
 }
 
+void row_quant_ue8m0(const void* x, void* q, void* sf, int64_t rows, int cols, cudaStream_t stream) {
+    EP_HOST_ASSERT(cols > 0 and cols % 128 == 0);
+    if (rows == 0) return;
+    const kernels::RowQuantArgs args = {static_cast<const uint8_t*>(x), static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), rows, cols};
+    const int64_t blocks = std::min<int64_t>((rows + 7) / 8, 148 * 8);
+    launch_kernel(kernels::row_quant_ue8m0_kernel, args, static_cast<int>(blocks), 256, 0, false, stream);
+}
+
+void swiglu_quant_ue8m0(const void* h, const float* row_scale, void* act, void* q, void* sf, int64_t rows, int inter,
+                        cudaStream_t stream) {
+    EP_HOST_ASSERT(inter > 0 and inter % 128 == 0);
+    if (rows == 0) return;
+    const kernels::SwiGLUQuantArgs args = {static_cast<const uint8_t*>(h), row_scale, static_cast<uint8_t*>(act),
+                                           static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), rows, inter};
+    const int64_t blocks = std::min<int64_t>((rows + 7) / 8, 148 * 8);
+    launch_kernel(kernels::swiglu_quant_ue8m0_kernel, args, static_cast<int>(blocks), 256, 0, false, stream);
+}
+
+void block_quant_ue8m0(const void* w, void* q, void* sf, void* qt, void* sft, int64_t rows, int cols, int n, cudaStream_t stream) {
+    EP_HOST_ASSERT(cols > 0 and cols % 128 == 0 and n > 0 and n % 128 == 0 and rows % n == 0);
+    EP_HOST_ASSERT((qt == nullptr) == (sft == nullptr) and rows / 128 <= 65535);
+    if (rows == 0) return;
+    const kernels::BlockQuantArgs args = {static_cast<const uint8_t*>(w), static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf),
+                                          static_cast<uint8_t*>(qt), static_cast<uint8_t*>(sft), rows, cols, n};
+    kernels::block_quant_ue8m0_kernel<<<dim3(cols / 128, static_cast<unsigned>(rows / 128)), 256, 0, stream>>>(args);
+    CUDA_CHECK(cudaGetLastError());
+}
+
 void lb_exchange(const kernels::LBArgs& args, int num_sms, cudaStream_t stream) {
     launch_kernel(kernels::lb_exchange_kernel, args, clamp_sms(num_sms), 512, 0, true, stream);
 }

@@ -182,6 +182,53 @@ torch::Tensor swiglu_backward(const torch::Tensor& h, const torch::Tensor& dact,
     return dh;
 }
 
+// bf16 [rows, cols] -> (e4m3 [rows, cols], UE8M0 bytes [rows, cols / 128]): power-of-two scales, the operand format of
+// the hardware-scaled FP8 GEMM
+std::tuple<torch::Tensor, torch::Tensor> row_quant_ue8m0(const torch::Tensor& x) {
+    EP_HOST_ASSERT(x.is_cuda() and x.is_contiguous() and x.scalar_type() == torch::kBFloat16 and x.dim() == 2 and x.size(1) % 128 == 0);
+    auto q = torch::empty(x.sizes(), x.options().dtype(torch::kFloat8_e4m3fn));
+    auto sf = torch::empty({x.size(0), x.size(1) / 128}, x.options().dtype(torch::kUInt8));
+    launch::row_quant_ue8m0(x.data_ptr(), q.data_ptr(), sf.data_ptr(), x.size(0), static_cast<int>(x.size(1)),
+                            c10::cuda::getCurrentCUDAStream());
+    return {q, sf};
+}
+
+// h = [gate | up] bf16 [rows, 2 * inter] -> silu(gate) * up * row_scale as (bf16 or None, e4m3, UE8M0 bytes [rows, inter / 128])
+std::tuple<std::optional<torch::Tensor>, torch::Tensor, torch::Tensor> swiglu_quant_ue8m0(
+        const torch::Tensor& h, const std::optional<torch::Tensor>& row_scale, bool keep_bf16) {
+    EP_HOST_ASSERT(h.is_cuda() and h.is_contiguous() and h.scalar_type() == torch::kBFloat16 and h.dim() == 2 and h.size(1) % 256 == 0);
+    if (row_scale.has_value())
+        EP_HOST_ASSERT(row_scale->is_cuda() and row_scale->is_contiguous() and row_scale->scalar_type() == torch::kFloat32 and
+                       row_scale->numel() == h.size(0));
+    const int64_t rows = h.size(0), inter = h.size(1) / 2;
+    std::optional<torch::Tensor> act;
+    if (keep_bf16) act = torch::empty({rows, inter}, h.options());
+    auto q = torch::empty({rows, inter}, h.options().dtype(torch::kFloat8_e4m3fn));
+    auto sf = torch::empty({rows, inter / 128}, h.options().dtype(torch::kUInt8));
+    launch::swiglu_quant_ue8m0(h.data_ptr(), row_scale.has_value() ? row_scale->data_ptr<float>() : nullptr,
+                               act.has_value() ? act->data_ptr() : nullptr, q.data_ptr(), sf.data_ptr(), rows,
+                               static_cast<int>(inter), c10::cuda::getCurrentCUDAStream());
+    return {act, q, sf};
+}
+
+// w bf16 [g, n, k] -> (e4m3 [g, n, k], UE8M0 [g, n / 128, k / 128]) and, with `transposed`, also
+// (e4m3 [g, k, n], UE8M0 [g, k / 128, n / 128]): the same quantised values, every matrix transposed
+std::vector<torch::Tensor> block_quant_ue8m0(const torch::Tensor& w, bool transposed) {
+    EP_HOST_ASSERT(w.is_cuda() and w.is_contiguous() and w.scalar_type() == torch::kBFloat16 and w.dim() == 3);
+    const int64_t g = w.size(0), n = w.size(1), k = w.size(2);
+    EP_HOST_ASSERT(n % 128 == 0 and k % 128 == 0);
+    const auto fp8 = w.options().dtype(torch::kFloat8_e4m3fn), u8 = w.options().dtype(torch::kUInt8);
+    auto q = torch::empty({g, n, k}, fp8);
+    auto sf = torch::empty({g, n / 128, k / 128}, u8);
+    torch::Tensor qt, sft;
+    if (transposed) qt = torch::empty({g, k, n}, fp8), sft = torch::empty({g, k / 128, n / 128}, u8);
+    launch::block_quant_ue8m0(w.data_ptr(), q.data_ptr(), sf.data_ptr(), transposed ? qt.data_ptr() : nullptr,
+                              transposed ? sft.data_ptr() : nullptr, g * n, static_cast<int>(k), static_cast<int>(n),
+                              c10::cuda::getCurrentCUDAStream());
+    if (transposed) return {q, sf, qt, sft};
+    return {q, sf};
+}
+
 // d[g, m, n] (fp32) (+)= a[rows_e, m]^T * b[rows_e, n] for every expert e; padding rows of `a` or `b` must be zero.
 void grouped_gemm_wgrad(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const torch::Tensor& psum,
                         const torch::Tensor& count, int num_sms, bool accumulate, bool use_pairs) {
@@ -307,6 +354,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("row_scale") = py::none(), py::arg("d_sf") = py::none(), py::arg("reg_split") = true,
           py::arg("route") = py::none());
     m.def("swiglu_backward", &swiglu_backward, py::arg("h"), py::arg("dact"), py::arg("row_scale") = py::none());
+    m.def("row_quant_ue8m0", &row_quant_ue8m0, py::arg("x"));
+    m.def("swiglu_quant_ue8m0", &swiglu_quant_ue8m0, py::arg("h"), py::arg("row_scale") = py::none(), py::arg("keep_bf16") = true);
+    m.def("block_quant_ue8m0", &block_quant_ue8m0, py::arg("w"), py::arg("transposed") = false);
     m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("psum"), py::arg("count"),
           py::arg("num_sms") = 0, py::arg("accumulate") = true, py::arg("use_pairs") = false);
 

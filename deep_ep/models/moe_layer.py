@@ -28,6 +28,9 @@ class MoEConfig:
                                         # dispatch kernel) feeding block-scaled FP8 expert GEMMs
     fp8_scales: str = 'fp32'            # 'fp32': scales amax / 448, promoted in registers by the GEMM; 'ue8m0': powers of two,
                                         # applied by the tensor core (hidden and intermediate must be multiples of 512)
+    fp8_training: bool = False          # training: forward and data-gradient GEMMs of the routed experts in FP8 (e4m3, power-of-two
+                                        # 1x128 / 128x128 scales applied by the tensor core), weight gradients in bf16;
+                                        # hidden and intermediate must be multiples of 512
     overlap_shared_expert: bool = False # run the shared expert on a side stream next to dispatch / routed experts / combine
     fuse_combine: bool = False          # the second expert GEMM stores the rows of single-row tokens straight into their
                                         # owners' combine landing slots (over NVLink, tile by tile); combine sends the rest
@@ -105,6 +108,7 @@ class MoELayer(nn.Module):
         self._handle: Optional[EPHandle] = None
         self._backward_route_used = False
         self._side_stream = None
+        self._fp8_cache = None
 
     def destroy(self) -> None:
         if self._own_buffer and self.buffer is not None:
@@ -128,6 +132,13 @@ class MoELayer(nn.Module):
                 self.buffer.barrier()
                 self._backward_route_used = True
             backward_route = (route, barrier_then_mark)
+        if self.config.fp8_training:
+            from ..ops.fp8_training import Fp8WeightCache, grouped_swiglu_ffn_fp8_training
+            if self._fp8_cache is None:
+                self._fp8_cache = Fp8WeightCache()
+            return grouped_swiglu_ffn_fp8_training(recv_x, self.w_gate_up, self.w_down, handle.psum_num_recv_tokens_per_expert,
+                                                   handle.num_unaligned_recv_tokens_per_expert, self.config.expert_alignment,
+                                                   self._fp8_cache, row_scale=recv_w, route=route, backward_route=backward_route)
         return grouped_swiglu_ffn(recv_x, self.w_gate_up, self.w_down, handle.psum_num_recv_tokens_per_expert,
                                   handle.num_unaligned_recv_tokens_per_expert, handle.num_recv_tokens_per_expert_list,
                                   self.config.expert_alignment, backend=self.config.expert_backend, row_scale=recv_w,
