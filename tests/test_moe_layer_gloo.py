@@ -48,3 +48,53 @@ def _moe_cpu_worker(rank, world_size):
 
 def test_moe_layer_two_cpu_ranks(master_port):
     run_distributed(_moe_cpu_worker, 2, master_port, 'gloo', timeout_s=180)
+
+
+def _moe_fp8_training_cpu_worker(rank, world_size):
+    """`MoEConfig.fp8_training` through the layer on CPU ranks (PyTorch emulation of the FP8 kernels)."""
+    import torch.distributed as dist
+    from deep_ep.models.moe_layer import MoEConfig, MoELayer
+    torch.manual_seed(6)
+    num_tokens, hidden, inter, num_experts, num_topk = 40, 512, 512, 4, 2
+    cfg = MoEConfig(hidden=hidden, intermediate=inter, num_experts=num_experts, num_topk=num_topk,
+                    num_max_tokens_per_rank=num_tokens, expert_alignment=128, fp8_training=True)
+    gate = torch.randn(num_experts, hidden) * 0.5
+    w1 = (torch.randn(num_experts, 2 * inter, hidden) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(num_experts, hidden, inter) * 0.05).to(torch.bfloat16)
+    layer = MoELayer(dist.group.WORLD, cfg)
+    local = num_experts // world_size
+    with torch.no_grad():
+        layer.gate.copy_(gate)
+        layer.w_gate_up.copy_(w1[rank * local:(rank + 1) * local])
+        layer.w_down.copy_(w2[rank * local:(rank + 1) * local])
+    torch.manual_seed(200 + rank)
+    x = torch.randn(num_tokens, hidden).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(num_tokens, hidden).to(torch.bfloat16)
+    y = layer(x)
+    y.backward(dy)
+
+    xr = x.detach().clone().requires_grad_()
+    w1r, w2r = w1.clone().requires_grad_(), w2.clone().requires_grad_()
+    ref = _dense_reference(xr, gate, w1r, w2r, num_topk)
+    ref.backward(dy.float())
+    g1, g2 = w1r.grad.float(), w2r.grad.float()
+    dist.all_reduce(g1), dist.all_reduce(g2)
+    sl = slice(rank * local, (rank + 1) * local)
+
+    def rel(a, b):
+        return ((a.float() - b.float()).norm() / b.float().norm()).item()
+    for name, got, want in (('forward', y, ref.detach()), ('input gradient', x.grad, xr.grad),
+                            ('gate/up gradient', layer.w_gate_up.grad, g1[sl]), ('down gradient', layer.w_down.grad, g2[sl])):
+        assert rel(got, want) < 0.12, f'{name}: {rel(got, want)}'
+    # a second step reuses the quantised weights; an in-place update refreshes them
+    first = layer._fp8_cache.get(layer.w_gate_up)[0]
+    layer(x.detach())
+    assert layer._fp8_cache.get(layer.w_gate_up)[0] is first
+    with torch.no_grad():
+        layer.w_gate_up.mul_(0.5)
+    assert layer._fp8_cache.get(layer.w_gate_up)[0] is not first
+    layer.destroy()
+
+
+def test_moe_layer_fp8_training_two_cpu_ranks(master_port):
+    run_distributed(_moe_fp8_training_cpu_worker, 2, master_port, 'gloo', timeout_s=180)

@@ -157,6 +157,22 @@ def _new_paths_worker(rank, world_size):
     torch.cuda.synchronize()
     layer8.buffer.runtime.check_status()
     assert torch.equal(plain8, fused8), 'fused combine route changes the FP8 result'
+
+    # FP8 training of the routed experts against the bf16 layer: output, input gradient and weight gradients
+    results8 = []
+    for fp8 in (False, True):
+        layer8.config.fuse_combine, layer8.config.fp8_training = False, fp8
+        for p in layer8.parameters():
+            p.grad = None
+        xt = x.clone().requires_grad_()
+        yt = layer8(xt)
+        yt.backward(torch.ones_like(yt))
+        torch.cuda.synchronize()
+        results8.append((yt.detach().float(), xt.grad.float(), layer8.w_gate_up.grad.float(), layer8.w_down.grad.float()))
+    for name, a, b in zip(('y', 'dx', 'dw_gate_up', 'dw_down'), results8[1], results8[0]):
+        rel = ((a - b).norm() / b.norm().clamp(min=1e-12)).item()
+        assert torch.isfinite(a).all() and rel < 0.12, f'FP8 training {name} deviates from bf16 by {rel}'
+    layer8.config.fp8_training = False
     layer8.destroy()
 
     # weights applied inside the combine kernel against weights applied by the caller (one rounding less, so not bitwise)
