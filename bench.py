@@ -316,9 +316,15 @@ def main():
         # Input pipeline as a training or serving loop would run it: two device-side input sets; the copy of step i + 1
         # (pinned host memory -> device, on a copy stream) overlaps the kernels of step i. Every step's copy and every
         # step's device -> host read of the result happen inside the timed region.
-        dev_inputs = [(torch.empty_like(x), torch.empty_like(topk_idx), torch.empty_like(topk_w)) for _ in range(2)]
+        # The activations cross PCIe in the form the dispatch takes them: e4m3 rows plus their 1x128 scales (the headline
+        # configuration), or bf16 rows that the dispatch kernel quantises itself (`--dispatch-input bf16-fused`).
+        if fused:
+            host_inputs = (x_host, topk_idx_host, topk_w_host)
+        else:
+            host_inputs = (x_fp8.view(torch.uint8).cpu().pin_memory(), sf_packs.cpu().pin_memory(), topk_idx_host, topk_w_host)
+        dev_inputs = [tuple(torch.empty(t.shape, dtype=t.dtype, device=dev) for t in host_inputs) for _ in range(2)]
         result_host = torch.empty(2, dtype=torch.float32).pin_memory()
-        h2d_bytes = x_host.nbytes + topk_idx_host.nbytes + topk_w_host.nbytes
+        h2d_bytes = sum(t.nbytes for t in host_inputs)
         d2h_bytes = result_host.nbytes
         copy_stream = torch.cuda.Stream()
         copy_done = [torch.cuda.Event() for _ in range(2)]
@@ -328,7 +334,7 @@ def main():
             b = i % 2
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(inputs_free[b])          # the step that last read this set has finished
-                for dst, src in zip(dev_inputs[b], (x_host, topk_idx_host, topk_w_host)):
+                for dst, src in zip(dev_inputs[b], host_inputs):
                     dst.copy_(src, non_blocking=True)
                 copy_done[b].record(copy_stream)
 
@@ -336,11 +342,12 @@ def main():
             issue_copy(0)
             for i in range(steps):
                 b = i % 2
-                x_dev, idx_dev, w_dev = dev_inputs[b]
+                *x_dev, idx_dev, w_dev = dev_inputs[b]
+                x_dev = x_dev[0] if fused else (x_dev[0].view(torch.float8_e4m3fn), x_dev[1])
                 torch.cuda.current_stream().wait_event(copy_done[b])
                 if i + 1 < steps:
                     issue_copy(i + 1)
-                ev_d = buffer.dispatch(x_dev, topk_idx=idx_dev, topk_weights=w_dev, fused_fp8_quant=True, **common)
+                ev_d = buffer.dispatch(x_dev, topk_idx=idx_dev, topk_weights=w_dev, fused_fp8_quant=fused, **common)
                 (rx, rsf), _, w_out, h = ev_d.current_stream_wait()
                 ev_c = buffer.combine(y[:rx.size(0)], h, topk_weights=w_out, num_sms=num_sms, async_with_compute_stream=True,
                                       defer_epilogue=True)
@@ -398,7 +405,8 @@ def main():
         if e2e_ms is not None:
             step_bytes = sum_dispatch_bytes + sum_combine_bytes
             line['e2e'] = {'value': round(sum_dispatch_bytes / (e2e_ms_max * 1e6), 2),
-                           'unit': 'GB/s of dispatch bytes over the whole end-to-end step (H2D + fused-quant dispatch + expand + combine + reduce + D2H)',
+                           'unit': 'GB/s of dispatch bytes over the whole end-to-end step (H2D + dispatch + expand + combine + reduce + D2H)',
+                           'h2d_inputs': 'bf16 rows, quantised by the dispatch kernel' if fused else 'e4m3 rows + 1x128 fp32 scales (what the dispatch sends)',
                            'step_ms': round(e2e_ms_max, 4), 'step_gbs_dispatch_plus_combine': round(step_bytes / (e2e_ms_max * 1e6), 2),
                            'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': d2h_bytes,
                            'input_pipeline': 'pinned host buffers on the NUMA node of the GPU (node %s of rank 0); the copy of step i + 1 '
