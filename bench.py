@@ -357,13 +357,19 @@ def main():
                 result_host.copy_(result, non_blocking=True)
                 torch.cuda.current_stream().synchronize()      # the step's result is on the host
 
-        e2e_loop(3)
+        e2e_error = None
+        try:
+            e2e_loop(3)
+        except (TypeError, ValueError, AssertionError, RuntimeError) as exc:
+            # a host-side argument error is the same on every rank: report it instead of losing the device-timed numbers
+            e2e_error = f'{type(exc).__name__}: {exc}'[:300]
         dist.barrier()
         torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        e2e_loop(args.steps)
-        torch.cuda.synchronize()
-        e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        if e2e_error is None:
+            t0 = time.perf_counter()
+            e2e_loop(args.steps)
+            torch.cuda.synchronize()
+            e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
 
     # ---- reduce over ranks: maximum time, sum of bytes
     stats = torch.tensor([total_ms, dispatch_ms, combine_ms, e2e_ms or 0.0, float(dispatch_bytes), float(combine_bytes)],
@@ -411,6 +417,8 @@ def main():
                            'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': d2h_bytes,
                            'input_pipeline': 'pinned host buffers on the NUMA node of the GPU (node %s of rank 0); the copy of step i + 1 '
                                              'overlaps the kernels of step i' % numa_node}
+        elif not args.skip_e2e and e2e_error is not None:
+            line['e2e_error'] = e2e_error
         print(json.dumps(line))
     buffer.destroy()
     dist.destroy_process_group()
