@@ -9,6 +9,8 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <chrono>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <filesystem>
@@ -51,14 +53,21 @@ class Compiler {
     std::vector<CUmodule> modules;
     std::mutex mutex;
 
-    std::string cache_dir() const {
-        auto dir = get_env("CACHE_DIR");
-        if (dir.empty()) {
+    // `EP_JIT_CACHE_DIR` may name several roots separated by colons: all are searched in order, misses are compiled
+    // into the first (a read-only cache shipped with an image can sit behind a writable one).
+    std::vector<std::string> cache_roots() const {
+        auto dirs = get_env("CACHE_DIR");
+        if (dirs.empty()) {
             const char* home = std::getenv("HOME");
-            dir = std::string(home != nullptr ? home : "/tmp") + "/.deep_ep_b200/cache";
+            dirs = std::string(home != nullptr ? home : "/tmp") + "/.deep_ep_b200/cache";
         }
-        std::filesystem::create_directories(dir);
-        return dir;
+        std::vector<std::string> roots;
+        std::stringstream stream(dirs);
+        for (std::string item; std::getline(stream, item, ':');)
+            if (not item.empty()) roots.push_back(item);
+        EP_HOST_ASSERT_MSG(not roots.empty(), "EP_JIT_CACHE_DIR names no directory");
+        std::filesystem::create_directories(roots.front());
+        return roots;
     }
 
 public:
@@ -69,6 +78,7 @@ public:
 
     void init(const std::string& dir) { package_dir = dir; }
     const std::string& get_package_dir() const { return package_dir; }
+    std::vector<std::string> get_cache_roots() const { return cache_roots(); }
     std::string include_dir() const { return package_dir + "/include"; }
 
     std::string nvcc_path() const {
@@ -88,9 +98,15 @@ public:
         flags += " -gencode arch=compute_" + arch_num + ",code=" + arch + " -I" + include_dir();
         std::ostringstream key;
         key << std::hex << fnv1a(source, fnv1a(flags));
-        const auto dir = cache_dir() + "/" + name + "-" + key.str();
+        const auto roots = cache_roots();
+        const auto entry = name + "-" + key.str();
+        for (const auto& root : roots) {
+            const auto hit = root + "/" + entry + "/kernel.cubin";
+            std::error_code ignored;
+            if (std::filesystem::exists(hit, ignored)) return hit;
+        }
+        const auto dir = roots.front() + "/" + entry;
         const auto cubin = dir + "/kernel.cubin";
-        if (std::filesystem::exists(cubin)) return cubin;
         std::filesystem::create_directories(dir);
         {
             std::ofstream out(dir + "/kernel.cu");
@@ -117,7 +133,12 @@ public:
         auto it = loaded.find(key);
         if (it != loaded.end()) return it->second;
         CUmodule module;
+        const auto t0 = std::chrono::steady_clock::now();
         DRV_CHECK(driver::cuModuleLoad()(&module, cubin.c_str()));
+        if (get_env_flag("PRINT_LOAD_TIME") or get_env_flag("DEBUG")) {
+            const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+            std::fprintf(stderr, "[deep_ep jit] loaded %s in %.2f ms\n", cubin.c_str(), ms);
+        }
         modules.push_back(module);
         CUfunction fn;
         DRV_CHECK(driver::cuModuleGetFunction()(&fn, module, symbol.c_str()));
@@ -145,6 +166,11 @@ inline void register_python_api(pybind11::module_& m) {
         return Compiler::get().compile(name, source, arch);
     }, pybind11::arg("name"), pybind11::arg("source"), pybind11::arg("arch") = "sm_100a");
     m.def("jit_include_dir", [] { return Compiler::get().include_dir(); });
+    m.def("jit_cache_roots", [] { return Compiler::get().get_cache_roots(); });
+    // `EP_JIT_LAUNCH_TIMEOUT` (seconds, default 300, 0 = none) is read for compatibility with the reference's launcher.
+    // CUDA has no per-launch execution limit: what bounds a kernel here is the buffer's `num_gpu_timeout_secs`, after
+    // which every device-side wait gives up and reports through the status word.
+    m.def("jit_launch_timeout_secs", [] { return std::atoi(get_env("LAUNCH_TIMEOUT", "300").c_str()); });
     // Launch `symbol` of a compiled cubin on the current CUDA stream. Each argument is a `(kind, value)` pair with
     // kind in {"ptr", "i64", "i32", "f32"}; pointers are raw device addresses.
     m.def("jit_launch", [](const std::string& cubin, const std::string& symbol, int grid, int block, int smem_bytes,

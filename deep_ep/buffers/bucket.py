@@ -9,6 +9,7 @@ from .. import comm
 from .._C_loader import _C
 from ..utils.event import EventOverlap
 from ..utils.math import align
+from ..utils.semantic import nvtx_range
 from .allocator import BufferAllocator
 from .base import BufferBase, connect_peers, sync_group
 
@@ -203,6 +204,7 @@ class BucketBuffer(BufferBase):
         setattr(handle, 'num_sms', used_sms)
         return handle
 
+    @nvtx_range('deep_ep.BucketBuffer.reduce_scatter')
     def reduce_scatter(self, srcs, comm_precision: str = 'fp32', scale: float = 1.0,
                        group: Optional[dist.ProcessGroup] = None, num_sms: Optional[int] = None) -> EventOverlap:
         """Launch a batched in-place reduce-scatter of up to 64 registered tensors on the communication stream.
@@ -217,6 +219,7 @@ class BucketBuffer(BufferBase):
         assert comm_precision == 'fp32', 'sums are accumulated in fp32; other precisions are not offered'
         return self._reduce(srcs, scale, group, num_sms, all_reduce=False)
 
+    @nvtx_range('deep_ep.BucketBuffer.all_reduce')
     def all_reduce(self, srcs, scale: float = 1.0, group: Optional[dist.ProcessGroup] = None,
                    num_sms: Optional[int] = None) -> EventOverlap:
         """Launch a batched in-place all-reduce of up to 64 registered tensors on the communication stream.
@@ -227,6 +230,7 @@ class BucketBuffer(BufferBase):
         """
         return self._reduce(srcs, scale, group, num_sms, all_reduce=True)
 
+    @nvtx_range('deep_ep.BucketBuffer.all_gather')
     def all_gather(self, srcs: Union[torch.Tensor, Sequence[torch.Tensor]],
                    dsts: Optional[Union[torch.Tensor, Sequence[torch.Tensor]]] = None,
                    group: Optional[dist.ProcessGroup] = None, num_sms: Optional[int] = None) -> EventOverlap:

@@ -15,7 +15,7 @@ import torch.distributed as dist
 from .. import comm
 from .._C_loader import _C
 from ..utils.event import EventHandle, EventOverlap
-from ..utils.semantic import value_or
+from ..utils.semantic import nvtx_range, value_or
 from .allocator import BufferAllocator
 from .base import BufferBase, connect_peers, sync_group
 
@@ -207,6 +207,7 @@ class EPBuffer(BufferBase):
         return 0
 
     # ------------------------------------------------------------------------------------------
+    @nvtx_range('deep_ep.EPBuffer.dispatch')
     def dispatch(self, x: Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]],
                  topk_idx: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None,
                  cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
@@ -312,6 +313,7 @@ class EPBuffer(BufferBase):
         return *finalize(result, async_with_compute_stream), event_overlap
 
     # ------------------------------------------------------------------------------------------
+    @nvtx_range('deep_ep.EPBuffer.combine')
     def combine(self, x: torch.Tensor, handle: EPHandle, topk_weights: Optional[torch.Tensor] = None,
                 bias: Union[None, torch.Tensor, Tuple[torch.Tensor, torch.Tensor]] = None,
                 num_sms: int = 0, num_qps: int = 0, previous_event: Optional[EventHandle] = None,

@@ -6,6 +6,7 @@ import torch.distributed as dist
 
 from .. import comm
 from .._C_loader import _C
+from ..utils.semantic import nvtx_range
 from .base import BufferBase, connect_peers, sync_group
 
 
@@ -44,10 +45,12 @@ class PPBuffer(BufferBase):
         self.storage = self.runtime.storage
         sync_group(group)
 
+    @nvtx_range('deep_ep.PPBuffer.send')
     def send(self, x: torch.Tensor, dst_rank_idx: int, num_sms: Optional[int] = None) -> None:
         """Send contiguous `x` (at most `num_max_tensor_bytes`) to the previous or next rank of the ring."""
         self.runtime.send(x, dst_rank_idx, 0 if num_sms is None else num_sms)
 
+    @nvtx_range('deep_ep.PPBuffer.recv')
     def recv(self, x: torch.Tensor, src_rank_idx: int, num_sms: Optional[int] = None) -> None:
         """Receive into contiguous `x` from the previous or next rank of the ring."""
         self.runtime.recv(x, src_rank_idx, 0 if num_sms is None else num_sms)

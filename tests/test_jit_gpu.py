@@ -35,3 +35,26 @@ def test_jit_cache_key_and_errors(tmp_path):
     assert c != a
     with pytest.raises(deep_ep.EPException):
         deep_ep._C.jit_compile('broken', 'this is not CUDA')
+
+
+def test_jit_cache_searches_every_root_and_writes_the_first(tmp_path):
+    """`EP_JIT_CACHE_DIR=a:b`: a hit in any root is used, a miss is compiled into the first root."""
+    import deep_ep
+    first, second = tmp_path / 'first', tmp_path / 'second'
+    src = 'extern "C" __global__ void k2(int* p) { if (p) p[0] = 2; }\n'
+    saved = os.environ.get('EP_JIT_CACHE_DIR')
+    try:
+        os.environ['EP_JIT_CACHE_DIR'] = str(second)
+        in_second = deep_ep._C.jit_compile('roots', src)
+        assert in_second.startswith(str(second))
+        os.environ['EP_JIT_CACHE_DIR'] = f'{first}:{second}'
+        assert deep_ep._C.jit_cache_roots() == [str(first), str(second)]
+        assert deep_ep._C.jit_compile('roots', src) == in_second                 # found behind the first root
+        fresh = deep_ep._C.jit_compile('roots', src + '// other\n')
+        assert fresh.startswith(str(first))                                       # misses go to the first root
+        assert deep_ep._C.jit_launch_timeout_secs() == 300
+    finally:
+        if saved is None:
+            os.environ.pop('EP_JIT_CACHE_DIR', None)
+        else:
+            os.environ['EP_JIT_CACHE_DIR'] = saved

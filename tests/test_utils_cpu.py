@@ -161,3 +161,22 @@ def test_descriptor_exchange_between_processes_of_a_node():
     """The file-descriptor hand-over that the virtual-memory-management route of the symmetric allocation relies on."""
     import deep_ep
     assert deep_ep._C.fd_exchange_selftest()
+
+
+def test_nvtx_range_decorator_is_transparent(monkeypatch):
+    """Off: the function itself comes back. On: the call still returns its value and propagates exceptions (on a machine
+    without CUDA the wrapper calls straight through)."""
+    from deep_ep.utils.semantic import nvtx_range
+
+    def f(a, b=2):
+        return a + b
+    monkeypatch.delenv('EP_NVTX', raising=False)
+    assert nvtx_range('x')(f) is f
+    monkeypatch.setenv('EP_NVTX', '1')
+    wrapped = nvtx_range('x')(f)
+    assert wrapped is not f and wrapped(1, b=3) == 4 and wrapped.__name__ == 'f'
+
+    def boom():
+        raise ValueError('boom')
+    with pytest.raises(ValueError):
+        nvtx_range('y')(boom)()
