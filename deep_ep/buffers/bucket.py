@@ -1,6 +1,6 @@
 """`BucketBuffer` and `BucketSession`: batched all-gather over registered storage
 (reference: `deep_ep/buffers/bucket.py:19-356`)."""
-from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple, Union
+from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 import torch.distributed as dist

@@ -1,7 +1,7 @@
 """Expert load balancing over redundant expert slots (API of the reference's `deep_ep/buffers/ep.py:594-649`,
 whose native side is unimplemented). Redundant slots live in the LB region of an `EPBuffer`, which is part of the
 peer-visible allocation, so owners push weights into them and pull gradients out of them directly over NVLink."""
-from typing import Optional, Sequence, Union
+from typing import Sequence, Union
 
 import torch
 

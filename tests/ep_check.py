@@ -6,7 +6,6 @@ padding, master top-k index, bitwise combine (with 0/1/2 biases, with and withou
 replays with new payloads/weights, and run-to-run determinism of the layout.
 """
 import torch
-import torch.distributed as dist
 
 import deep_ep
 from deep_ep.utils import refs
