@@ -114,3 +114,66 @@ def test_dispatch_combine_identity(num_ranks, num_experts, num_topk, num_bias):
         expected = sum((b.float() for b in bias if b is not None), torch.zeros(t, hidden))
         expected = expected + (inp.x.float().unsqueeze(1) * inp.topk_weights.unsqueeze(2)).sum(1)
         assert torch.allclose(combined.float(), expected, atol=0.08, rtol=0.03)
+
+
+# ------------------------------------------------------------------------------------------ property tests
+try:
+    from hypothesis import given, settings, strategies as st
+    _have_hypothesis = True
+except ImportError:                                   # pragma: no cover
+    _have_hypothesis = False
+
+
+if _have_hypothesis:
+    @st.composite
+    def _shapes(draw):
+        num_ranks = draw(st.sampled_from([1, 2, 3, 4, 8]))
+        per_rank = draw(st.integers(1, 5))
+        num_experts = num_ranks * per_rank
+        num_topk = draw(st.integers(1, min(num_experts, 9)))
+        num_tokens = draw(st.integers(1, 17))
+        alignment = draw(st.sampled_from([1, 2, 8, 16, 128]))
+        masked = draw(st.sampled_from([0.0, 0.2, 0.6, 1.0]))
+        seed = draw(st.integers(0, 10_000))
+        return num_ranks, num_experts, num_topk, num_tokens, alignment, masked, seed
+
+    @settings(max_examples=60, deadline=None)
+    @given(_shapes())
+    def test_random_shapes_conserve_tokens_and_round_trip(shape):
+        """For arbitrary small shapes: every (token, destination rank) pair becomes exactly one received row, every valid
+        (token, expert) selection exactly one expanded row inside that expert's region, and combine(dispatch(x) * w)
+        returns sum_k w_k x together with the original weights."""
+        num_ranks, num_experts, num_topk, num_tokens, alignment, masked, seed = shape
+        hidden, max_tokens = 16, num_tokens
+        inputs = make_inputs(num_ranks, num_tokens, hidden, num_experts, num_topk, masked, seed)
+        per_rank = num_experts // num_ranks
+        layouts = [sim.receiver_layout([i.topk_idx for i in inputs], r, num_experts, alignment, max_tokens)
+                   for r in range(num_ranks)]
+        for r, lay in enumerate(layouts):
+            lo, hi = r * per_rank, (r + 1) * per_rank
+            hits = [((i.topk_idx >= lo) & (i.topk_idx < hi)) for i in inputs]
+            assert lay.recv_src_metadata.size(0) == sum(int(h.any(1).sum()) for h in hits)
+            selections = torch.zeros(per_rank, dtype=torch.long)
+            for i, h in zip(inputs, hits):
+                selections += torch.bincount((i.topk_idx[h] - lo).long(), minlength=per_rank)
+            assert lay.num_unaligned_recv_tokens_per_expert.tolist() == selections.tolist()
+            assert lay.num_expanded_tokens == sum(align(int(c), alignment) for c in selections.tolist())
+            assert lay.num_expanded_tokens % alignment == 0
+        outs = []
+        for r in range(num_ranks):
+            recv_x, _, recv_w = sim.expand(layouts[r], inputs, layouts[r].num_expanded_tokens, True)
+            y = (recv_x.float() * recv_w.unsqueeze(1)).to(torch.bfloat16)
+            outs.append(sim.combine_partials(y, recv_w, layouts[r].recv_src_metadata, num_topk))
+        for s, inp in enumerate(inputs):
+            t = inp.x.size(0)
+            partials, weights = [], []
+            for d in range(num_ranks):
+                p, w = torch.zeros(t, hidden, dtype=torch.bfloat16), torch.zeros(t, num_topk)
+                src = layouts[d].recv_src_metadata[:, -2].long()
+                mine = (src // max_tokens) == s
+                p[src[mine] % max_tokens], w[src[mine] % max_tokens] = outs[d][0][mine], outs[d][1][mine]
+                partials.append(p), weights.append(w)
+            combined, combined_w = sim.combine_reduce(partials, weights, inp.topk_idx, num_experts, (None, None), True)
+            assert torch.equal(combined_w, inp.topk_weights)
+            expected = (inp.x.float().unsqueeze(1) * inp.topk_weights.unsqueeze(2)).sum(1)
+            assert torch.allclose(combined.float(), expected, atol=0.1, rtol=0.04)
