@@ -40,6 +40,9 @@ def main():
     p.add_argument('--skip-torch', action='store_true')
     p.add_argument('--skip-fp8', action='store_true')
     p.add_argument('--only', type=str, default='', help='comma-separated case names to run')
+    p.add_argument('--fp8-training', action='store_true',
+                   help='also time the pieces of the FP8 training path: data-gradient GEMMs on transposed FP8 weights and the '
+                        'three quantiser kernels (reported in GB/s of bytes read + written)')
     args = p.parse_args()
     dev = torch.device('cuda')
     torch.manual_seed(0)
@@ -108,6 +111,24 @@ def main():
                                                                                      quantize_output=True), None, 2 * useful * h * 2 * i),
             'fp8hw_gemm2_forward': (lambda: gg.grouped_gemm_fp8_forward(a8h, a8h_sf, w2_8h, w2h_sf, psum, count), None, 2 * useful * h * i),
         })
+    bandwidth_cases = {}
+    if args.fp8_training:
+        from deep_ep.ops import fp8_training as ft
+        _, _, w1t_8, w1t_sf = ft.block_quant(w1, transposed=True)
+        _, _, w2t_8, w2t_sf = ft.block_quant(w2, transposed=True)
+        dy = torch.randn(rows, h, device=dev, dtype=torch.bfloat16)
+        dy8, dy8_sf = ft.row_quant(dy)
+        dh8, dh8_sf = ft.row_quant(dy1)
+        cases.update({
+            'fp8hw_gemm2_dgrad': (lambda: ft.fp8_gemm(dy8, dy8_sf, w2t_8, w2t_sf, psum, count, 128), None, 2 * useful * h * i),
+            'fp8hw_gemm1_dgrad': (lambda: ft.fp8_gemm(dh8, dh8_sf, w1t_8, w1t_sf, psum, count, 128), None, 2 * useful * h * 2 * i),
+        })
+        bandwidth_cases = {
+            'row_quant_hidden': (lambda: ft.row_quant(x), rows * h * 3 + rows * h // 128),
+            'row_quant_2inter': (lambda: ft.row_quant(dy1), rows * 2 * i * 3 + rows * 2 * i // 128),
+            'swiglu_quant': (lambda: ft.swiglu_quant(dy1, None), rows * 2 * i * 2 + rows * i * 3 + rows * i // 128),
+            'block_quant_w1_with_transpose': (lambda: ft.block_quant(w1, transposed=True), g * 2 * i * h * 4),
+        }
     out = {'bench': 'grouped_gemm', 'experts': g, 'rows_total': rows, 'rows_useful': useful, 'hidden': h, 'inter': i,
            'peak_tflops_measured': peak, 'results': {}}
     for name, (ours, ref, flops) in cases.items():
@@ -128,6 +149,15 @@ def main():
             except Exception as e:      # not available for this architecture / build
                 entry['torch_grouped_mm_error'] = str(e).splitlines()[0][:200]
         out['results'][name] = entry
+    hbm = 6543.7
+    if os.path.exists(path):
+        hbm = json.load(open(path)).get('hbm_gbs', hbm)
+    for name, (fn, num_bytes) in bandwidth_cases.items():
+        if args.only and name not in args.only.split(','):
+            continue
+        t_min, t_avg = bench(fn, args.iters)
+        out['results'][name] = {'ours_ms': round(t_avg, 4), 'gbs': round(num_bytes / (t_avg * 1e6), 1),
+                                'frac_of_measured_copy_bandwidth': round(num_bytes / (t_avg * 1e6) / hbm, 3)}
     print(json.dumps(out))
 
 
