@@ -159,7 +159,13 @@ public:
                                "ranks disagree about the size or the multicast setting of the symmetric allocation");
             const int num_fds = (r == 0 and peer_multicast) ? 2 : 1;
             const auto fds = receive_fds(name, num_fds, num_cpu_timeout_secs);
-            vmm_peers.push_back(std::make_unique<VmmPeerMapping>(fds[0], peer_bytes, memory->vmm_granularity_bytes));
+            try {
+                // each mapping closes the descriptor it is given, whether or not the import succeeds
+                vmm_peers.push_back(std::make_unique<VmmPeerMapping>(fds[0], peer_bytes, memory->vmm_granularity_bytes));
+            } catch (...) {
+                if (num_fds == 2) ::close(fds[1]);
+                throw;
+            }
             peers.base[r] = reinterpret_cast<uint8_t*>(vmm_peers.back()->va);
             if (num_fds == 2)
                 multicast = std::make_unique<VmmPeerMapping>(fds[1], peer_bytes, memory->vmm_granularity_bytes, /*map_now=*/false);

@@ -197,23 +197,35 @@ public:
         prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
         prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE, prop.location.id = dev;
         prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
-        DRV_CHECK(driver::cuMemCreate()(&handle, size, &prop, 0));
-        DRV_CHECK(driver::cuMemAddressReserve()(&va, size, granularity, 0, 0));
-        DRV_CHECK(driver::cuMemMap()(va, size, 0, handle, 0));
-        const auto access = vmm_detail::read_write_access(dev);
-        DRV_CHECK(driver::cuMemSetAccess()(va, size, &access, 1));
-        CUDA_CHECK(cudaMemset(reinterpret_cast<void*>(va), 0, size));
-        CUDA_CHECK(cudaDeviceSynchronize());
-        DRV_CHECK(driver::cuMemExportToShareableHandle()(&fd, handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
+        try {
+            DRV_CHECK(driver::cuMemCreate()(&handle, size, &prop, 0));
+            DRV_CHECK(driver::cuMemAddressReserve()(&va, size, granularity, 0, 0));
+            DRV_CHECK(driver::cuMemMap()(va, size, 0, handle, 0));
+            mapped = true;
+            const auto access = vmm_detail::read_write_access(dev);
+            DRV_CHECK(driver::cuMemSetAccess()(va, size, &access, 1));
+            CUDA_CHECK(cudaMemset(reinterpret_cast<void*>(va), 0, size));
+            CUDA_CHECK(cudaDeviceSynchronize());
+            DRV_CHECK(driver::cuMemExportToShareableHandle()(&fd, handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
+        } catch (...) {
+            release();          // a constructor that throws runs no destructor
+            throw;
+        }
     }
     VmmAllocation(const VmmAllocation&) = delete;
-    ~VmmAllocation() {
-        if (fd >= 0) ::close(fd);
+    ~VmmAllocation() { release(); }
+
+private:
+    bool mapped = false;
+
+    void release() {
+        if (fd >= 0) ::close(fd), fd = -1;
         if (va != 0) {
-            driver::cuMemUnmap()(va, size);
+            if (mapped) driver::cuMemUnmap()(va, size);
             driver::cuMemAddressFree()(va, size);
+            va = 0, mapped = false;
         }
-        if (handle != 0) driver::cuMemRelease()(handle);
+        if (handle != 0) driver::cuMemRelease()(handle), handle = 0;
     }
 };
 
@@ -223,13 +235,22 @@ public:
     CUmemGenericAllocationHandle handle = 0;
     CUdeviceptr va = 0;
     size_t size = 0;
+    bool mapped = false;
 
-    // takes ownership of `fd` (closed after the import)
+    // takes ownership of `fd` (closed after the import, also when the import fails)
     VmmPeerMapping(int fd, size_t size, size_t granularity, bool map_now = true) : size(size) {
-        DRV_CHECK(driver::cuMemImportFromShareableHandle()(&handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
-                                                           CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
+        const auto result = driver::cuMemImportFromShareableHandle()(&handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+                                                                     CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
         ::close(fd);
-        if (map_now) map(granularity);
+        DRV_CHECK(result);
+        if (not map_now) return;
+        try {
+            map(granularity);
+        } catch (...) {
+            driver::cuMemRelease()(handle);
+            handle = 0;
+            throw;
+        }
     }
     // wraps a handle this process created itself (rank 0's multicast object)
     VmmPeerMapping(CUmemGenericAllocationHandle own_handle, size_t size) : handle(own_handle), size(size) {}
@@ -238,16 +259,22 @@ public:
     void map(size_t granularity) {
         EP_HOST_ASSERT(va == 0);
         DRV_CHECK(driver::cuMemAddressReserve()(&va, size, granularity, 0, 0));
-        DRV_CHECK(driver::cuMemMap()(va, size, 0, handle, 0));
-        const auto access = vmm_detail::read_write_access(vmm_detail::current_device());
-        DRV_CHECK(driver::cuMemSetAccess()(va, size, &access, 1));
+        try {
+            DRV_CHECK(driver::cuMemMap()(va, size, 0, handle, 0));
+            mapped = true;
+            const auto access = vmm_detail::read_write_access(vmm_detail::current_device());
+            DRV_CHECK(driver::cuMemSetAccess()(va, size, &access, 1));
+        } catch (...) {
+            unmap();
+            throw;
+        }
     }
 
     void unmap() {
         if (va == 0) return;
-        driver::cuMemUnmap()(va, size);
+        if (mapped) driver::cuMemUnmap()(va, size);
         driver::cuMemAddressFree()(va, size);
-        va = 0;
+        va = 0, mapped = false;
     }
 
     ~VmmPeerMapping() {
