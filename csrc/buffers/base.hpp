@@ -21,9 +21,13 @@ protected:
                                  "freed without a final barrier\n", name);
             release_without_barrier();
         } else {
+            // destructors must not throw: a failed final barrier is reported and the memory is released anyway
             try { destroy(); } catch (const std::exception& e) {
                 std::fprintf(stderr, "[deep_ep] WARNING: destroying %s buffer failed: %s\n", name, e.what());
+            } catch (...) {
+                std::fprintf(stderr, "[deep_ep] WARNING: destroying %s buffer failed\n", name);
             }
+            if (not destroyed) release_without_barrier();
         }
     }
     virtual void release_without_barrier() {}
@@ -32,7 +36,7 @@ public:
     std::shared_ptr<comm::Context> main_context;
 
     explicit BufferBase(bool explicitly_destroy) : explicitly_destroy(explicitly_destroy) {}
-    virtual ~BufferBase() noexcept(false) = default;
+    virtual ~BufferBase() = default;
     virtual void destroy() = 0;
 
     void print_memory_usage() const {

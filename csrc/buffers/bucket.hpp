@@ -59,7 +59,7 @@ public:
                                    torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, c10::cuda::current_device()));
     }
 
-    ~BucketBuffer() noexcept(false) override { destroy_on_destruction("bucket"); }
+    ~BucketBuffer() override { destroy_on_destruction("bucket"); }
 
     void destroy() override {
         EP_HOST_ASSERT(not destroyed);

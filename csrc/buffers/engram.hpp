@@ -40,7 +40,7 @@ public:
         context->set_common_signals(&static_cast<layout::EngramSignals*>(context->workspace)->common);
     }
 
-    ~EngramBuffer() noexcept(false) override { destroy_on_destruction("Engram"); }
+    ~EngramBuffer() override { destroy_on_destruction("Engram"); }
 
     void destroy() override {
         EP_HOST_ASSERT(not destroyed);

@@ -102,7 +102,7 @@ public:
             : torch::empty({0}, options);
     }
 
-    ~EPBuffer() noexcept(false) override { destroy_on_destruction("EP"); }
+    ~EPBuffer() override { destroy_on_destruction("EP"); }
 
     void destroy() override {
         EP_HOST_ASSERT(not destroyed);

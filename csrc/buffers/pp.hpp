@@ -69,7 +69,7 @@ public:
                                    torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, c10::cuda::current_device()));
     }
 
-    ~PPBuffer() noexcept(false) override { destroy_on_destruction("PP"); }
+    ~PPBuffer() override { destroy_on_destruction("PP"); }
 
     void destroy() override {
         EP_HOST_ASSERT(not destroyed);
