@@ -255,6 +255,38 @@ class SimEPRuntime:
         dist.all_gather_object(out, obj, self.group)
         return out
 
+    # ---- expert load balancing: `redundancy_mapping[r, c]` is the global expert held by redundant slot c of rank r (-1: free)
+    def lb_prefetch_weights(self, redundant_expert_weights, expert_weights, redundancy_mapping, num_sms, previous_event):
+        """Every redundant slot of this rank receives the weights of the expert the mapping assigns to it."""
+        from ..utils.event import EventHandle
+        assert not self.destroyed and len(redundant_expert_weights) == len(expert_weights) > 0
+        mapping = redundancy_mapping.view(self.num_ranks, -1)
+        for dst, src in zip(redundant_expert_weights, expert_weights):
+            assert dst.size(0) == mapping.size(1) and dst.shape[1:] == src.shape[1:] and dst.dtype == src.dtype
+            everyone = torch.cat([t for t in self._gather(src.detach().clone())])        # [num_ranks * local, ...]
+            for c in range(mapping.size(1)):
+                e = int(mapping[self.rank_idx, c])
+                if e >= 0:
+                    dst[c].copy_(everyone[e])
+        dist.barrier(self.group)
+        return EventHandle()
+
+    def lb_reduce_grads(self, redundant_expert_grads, expert_grads, redundancy_mapping, num_sms, previous_event):
+        """The owner of an expert adds the fp32 gradients of all its redundant copies, in slot order."""
+        from ..utils.event import EventHandle
+        assert not self.destroyed and expert_grads.dtype == torch.float32 and redundant_expert_grads.dtype == torch.float32
+        mapping = redundancy_mapping.view(self.num_ranks, -1)
+        num_local = expert_grads.size(0)
+        assert redundant_expert_grads.shape == (mapping.size(1), expert_grads.size(1))
+        everyone = self._gather(redundant_expert_grads.detach().clone())
+        for r in range(self.num_ranks):
+            for c in range(mapping.size(1)):
+                e = int(mapping[r, c])
+                if e >= 0 and e // num_local == self.rank_idx:
+                    expert_grads[e % num_local] += everyone[r][c]
+        dist.barrier(self.group)
+        return EventHandle()
+
     def dispatch(self, x, sf, topk_idx, topk_weights, stats,
                  cached_num_recv_tokens, cached_num_expanded_tokens, cached_list,
                  cached_psum_rank, cached_psum_expert, cached_num_unaligned,

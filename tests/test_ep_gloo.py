@@ -111,3 +111,37 @@ def _worker(rank, world_size, deterministic):
 @pytest.mark.parametrize('deterministic', [False, True])
 def test_ep_api_two_cpu_ranks(master_port, deterministic):
     run_distributed(_worker, 2, master_port, 'gloo', (deterministic,))
+
+
+def _lb_worker(rank, world):
+    """Expert load balancing on CPU ranks: redundant slots receive their experts' weights, owners collect the gradients."""
+    import torch.distributed as dist
+    import deep_ep
+    num_local, num_redundant, hidden = 3, 2, 32
+    plan = deep_ep.BufferAllocator()
+    red_w = plan.allocate((num_redundant, 4, hidden), torch.bfloat16)
+    red_g = plan.allocate((num_redundant, hidden), torch.float32)
+    ep = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=8, hidden=hidden, num_topk=2,
+                          lb_allocation_plan_or_num_bytes=plan, explicitly_destroy=True)
+    assert ep.is_simulated
+    torch.manual_seed(0)                                                   # the same mapping on every rank
+    mapping = torch.randint(-1, world * num_local, (world, num_redundant), dtype=torch.int32)
+    weights = torch.stack([torch.full((4, hidden), float(rank * num_local + e)) for e in range(num_local)]).to(torch.bfloat16)
+    red_w.fill_(-5)
+    ep.lb_prefetch_weights(red_w, weights, mapping).current_stream_wait()
+    for c in range(num_redundant):
+        e = int(mapping[rank, c])
+        assert torch.all(red_w[c] == (e if e >= 0 else -5)), f'slot {c} expected expert {e}'
+
+    red_g.copy_(torch.arange(num_redundant).view(-1, 1).float() + 10 * rank + 1)
+    grads = torch.ones(num_local, hidden)
+    ep.lb_reduce_grads(red_g, grads, mapping).current_stream_wait()
+    for e in range(num_local):
+        expect = 1.0 + sum(c + 10 * r + 1 for r in range(world) for c in range(num_redundant)
+                           if int(mapping[r, c]) == rank * num_local + e)
+        assert torch.all(grads[e] == expect), f'expert {e}: {grads[e, 0]} vs {expect}'
+    ep.destroy()
+
+
+def test_lb_two_cpu_ranks(master_port):
+    run_distributed(_lb_worker, 2, master_port, 'gloo')
