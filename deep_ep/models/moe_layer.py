@@ -1,6 +1,8 @@
 """An expert-parallel MoE layer built on `EPBuffer`: gate -> dispatch -> per-expert SwiGLU FFN -> combine,
 with a backward pass that reuses the routing handle (the gradient of dispatch is a combine and the
-gradient of combine is a cached dispatch). This is the "one model" of a communication library: the
+gradient of combine is a cached dispatch). The router trains too: the expert FFN returns the gradient of every
+expanded row's routing weight, and the combine that is the backward of dispatch carries those scalars back to their
+(token, top-k position) through its positional weight channel, from where autograd reaches the gate matrix. This is the "one model" of a communication library: the
 layer shape follows the DeepSeek-V3 expert FFN (hidden 7168, intermediate 2048, 256 routed experts,
 top-8, one shared expert), cf. the usage sketch in the reference's `README.md:178-194`.
 """
@@ -40,7 +42,9 @@ class MoEConfig:
 
 
 class _Dispatch(torch.autograd.Function):
-    """y = dispatch(x). Backward: grad_x = combine(grad_y) with the same handle."""
+    """recv_x, recv_w = dispatch(x, topk_weights). Backward: one combine with the same handle returns both gradients:
+    grad_x is the sum of the rows' gradients, and the gradient of every expanded row's routing weight travels back to
+    its (token, top-k position) through the combine's positional weight channel."""
 
     @staticmethod
     def forward(ctx, x, topk_idx, topk_weights, layer):
@@ -51,17 +55,18 @@ class _Dispatch(torch.autograd.Function):
             do_cpu_sync=True)
         ctx.layer, ctx.handle = layer, handle
         layer._handle = handle
-        ctx.mark_non_differentiable(recv_w)
         return recv_x, recv_w
 
     @staticmethod
-    def backward(ctx, grad_recv_x, _grad_w):
+    def backward(ctx, grad_recv_x, grad_recv_w):
         # with `fuse_combine` the data-gradient GEMM that produced `grad_recv_x` has already stored the rows of
         # single-row tokens into their owners' landing slots
-        grad_x, _, _ = ctx.layer.buffer.combine(grad_recv_x.contiguous(), ctx.handle,
-                                                fused_single_rows=ctx.layer._backward_route_used)
+        want_w = grad_recv_w is not None and ctx.needs_input_grad[2]
+        grad_x, grad_topk_w, _ = ctx.layer.buffer.combine(
+            grad_recv_x.contiguous(), ctx.handle, topk_weights=grad_recv_w.float().contiguous() if want_w else None,
+            fused_single_rows=ctx.layer._backward_route_used)
         ctx.layer._backward_route_used = False
-        return grad_x, None, None, None
+        return grad_x, None, (grad_topk_w if want_w else None), None
 
 
 class _Combine(torch.autograd.Function):

@@ -23,7 +23,7 @@ import torch
 
 from .._C_loader import _C
 from .grouped_gemm import (_ranges, _wgrad, grouped_gemm_fp8_forward, per_block_cast_to_fp8_ue8m0,
-                           per_token_cast_to_fp8_ue8m0, ue8m0_to_float)
+                           per_token_cast_to_fp8_ue8m0, row_scale_grad, ue8m0_to_float)
 
 
 # --------------------------------------------------------------------------------------------- quantisers
@@ -146,6 +146,7 @@ class GroupedSwiGLUFFNFp8(torch.autograd.Function):
         dy_q, dy_sf = row_quant(dy)
         dact = fp8_gemm(dy_q, dy_sf, w2t_q, w2t_sf, psum, count, ctx.alignment)
         dw_down = _wgrad(dy, act, w_down, psum, count, wgrad_alignment) if ctx.needs_input_grad[2] else None
+        d_row_scale = row_scale_grad(dact, act, row_scale) if row_scale is not None and ctx.needs_input_grad[3] else None
         dh = _swiglu_backward(h, dact, row_scale)
         dx = None
         if ctx.needs_input_grad[0]:
@@ -156,7 +157,7 @@ class GroupedSwiGLUFFNFp8(torch.autograd.Function):
             dh_q, dh_sf = row_quant(dh)
             dx = fp8_gemm(dh_q, dh_sf, w1t_q, w1t_sf, psum, count, ctx.alignment, route=table)
         dw_gate_up = _wgrad(dh, x, w_gate_up, psum, count, wgrad_alignment) if ctx.needs_input_grad[1] else None
-        return dx, dw_gate_up, dw_down, None, None, None, None, None, None, None
+        return dx, dw_gate_up, dw_down, d_row_scale, None, None, None, None, None, None
 
 
 def grouped_swiglu_ffn_fp8_training(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, psum: torch.Tensor,

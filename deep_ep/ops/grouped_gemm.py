@@ -77,6 +77,13 @@ def _wgrad(dy, x, w, psum, count, alignment):
     return None if main_grad is not None else (acc if acc.dtype == w.dtype else acc.to(w.dtype))
 
 
+def row_scale_grad(dact: torch.Tensor, act: torch.Tensor, row_scale: torch.Tensor) -> torch.Tensor:
+    """Gradient of the per-row scale `s` of `act = s * silu(gate) * up` given `dact = dL/dact`: `<dact, act> / s` per row
+    (rows with `s == 0`, i.e. padding, get 0). This is what carries the loss back to the routing weights."""
+    dot = (dact.float() * act.float()).sum(dim=1)
+    return torch.where(row_scale != 0, dot / row_scale, torch.zeros_like(dot))
+
+
 class GroupedSwiGLUFFN(torch.autograd.Function):
     """Whole expert FFN as one autograd node: `y = (silu(x Wg^T) * (x Wu^T) * row_scale) Wd^T` per expert.
 
@@ -103,6 +110,7 @@ class GroupedSwiGLUFFN(torch.autograd.Function):
         dy = dy.contiguous()
         dact = grouped_gemm_dgrad(dy, w_down, psum, count, alignment=ctx.alignment)
         dw_down = _wgrad(dy, act, w_down, psum, count, ctx.alignment) if ctx.needs_input_grad[2] else None
+        d_row_scale = row_scale_grad(dact, act, row_scale) if row_scale is not None and ctx.needs_input_grad[3] else None
         dh = _C.swiglu_backward(h, dact, row_scale)
         dx = None
         if ctx.needs_input_grad[0]:
@@ -112,7 +120,7 @@ class GroupedSwiGLUFFN(torch.autograd.Function):
                 barrier()
             dx = grouped_gemm_dgrad(dh, w_gate_up, psum, count, alignment=ctx.alignment, route=table)
         dw_gate_up = _wgrad(dh, x, w_gate_up, psum, count, ctx.alignment) if ctx.needs_input_grad[1] else None
-        return dx, dw_gate_up, dw_down, None, None, None, None, None, None
+        return dx, dw_gate_up, dw_down, d_row_scale, None, None, None, None, None
 
 
 def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, dw: torch.Tensor, psum: torch.Tensor, count: torch.Tensor,

@@ -32,8 +32,11 @@ def _moe_cpu_worker(rank, world_size):
 
     xr = x.detach().clone().requires_grad_()
     w1r, w2r = w1.clone().requires_grad_(), w2.clone().requires_grad_()
-    ref = _dense_reference(xr, gate, w1r, w2r, num_topk)
+    gate_r = gate.clone().requires_grad_()
+    ref = _dense_reference(xr, gate_r, w1r, w2r, num_topk)
     ref.backward(dy.float())
+    gate_rel = ((layer.gate.grad - gate_r.grad).norm() / gate_r.grad.norm()).item()
+    assert gate_rel < 0.03, f'gate gradient (through the routing weights) deviates by {gate_rel}'
     scale = ref.abs().max().item()
     assert torch.allclose(y.float(), ref.detach(), atol=3e-2 * scale, rtol=3e-2), f'forward: {(y.float() - ref).abs().max()} of {scale}'
     gscale = xr.grad.abs().max().item()
@@ -75,8 +78,11 @@ def _moe_fp8_training_cpu_worker(rank, world_size):
 
     xr = x.detach().clone().requires_grad_()
     w1r, w2r = w1.clone().requires_grad_(), w2.clone().requires_grad_()
-    ref = _dense_reference(xr, gate, w1r, w2r, num_topk)
+    gate_r = gate.clone().requires_grad_()
+    ref = _dense_reference(xr, gate_r, w1r, w2r, num_topk)
     ref.backward(dy.float())
+    gate_rel = ((layer.gate.grad - gate_r.grad).norm() / gate_r.grad.norm()).item()
+    assert gate_rel < 0.12, f'gate gradient (through the routing weights) deviates by {gate_rel}'
     g1, g2 = w1r.grad.float(), w2r.grad.float()
     dist.all_reduce(g1), dist.all_reduce(g2)
     sl = slice(rank * local, (rank + 1) * local)

@@ -11,7 +11,8 @@ from dist_utils import run_distributed
 def _dense_reference(x, gate, w_gate_up, w_down, num_topk):
     """fp32 MoE FFN with every expert available locally: `sum_k weight_k * FFN_{expert_k}(x)`."""
     import torch.nn.functional as F
-    scores = torch.softmax(F.linear(x.detach().float(), gate.float()), dim=-1)     # routing carries no gradient
+    # routing reads a detached copy of x: the gate matrix receives a gradient (through the routing weights), x does not
+    scores = torch.softmax(F.linear(x.detach().float(), gate.float()), dim=-1)
     topk_w, topk_idx = scores.topk(num_topk, dim=-1)
     topk_w = topk_w / topk_w.sum(dim=-1, keepdim=True)
     out = torch.zeros_like(x, dtype=torch.float32)
@@ -52,8 +53,13 @@ def _moe_worker(rank, world_size, num_tokens, hidden, inter, num_experts, num_to
 
     xr = x.detach().clone().requires_grad_()
     w1r, w2r = w1.to(dev).requires_grad_(), w2.to(dev).requires_grad_()
-    ref = _dense_reference(xr, gate.to(dev), w1r, w2r, num_topk)
+    gate_r = gate.to(dev).requires_grad_()
+    ref = _dense_reference(xr, gate_r, w1r, w2r, num_topk)
     ref.backward(dy.float())
+    # router: the gradient of the routing weights comes back through the combine's weight channel
+    assert layer.gate.grad is not None and torch.isfinite(layer.gate.grad).all()
+    gate_rel = ((layer.gate.grad - gate_r.grad).norm() / gate_r.grad.norm().clamp(min=1e-12)).item()
+    assert gate_rel < 0.1, f'gate gradient deviates by {gate_rel}'
     scale = ref.abs().max().item()
     assert torch.allclose(y.float(), ref, atol=2e-2 * scale, rtol=2e-2), f'forward: {(y.float() - ref).abs().max()} of {scale}'
     gscale = xr.grad.abs().max().item()
