@@ -157,6 +157,9 @@ def main():
     p.add_argument('--fp8-training', action='store_true',
                    help='also time forward + backward with the routed experts\' forward and data-gradient GEMMs in FP8 '
                         '(power-of-two block scales applied by the tensor core; weight gradients stay bf16)')
+    p.add_argument('--decode-graph', type=int, default=0, metavar='TOKENS',
+                   help='also time a decode-sized inference forward (this many tokens per rank, FP8 with power-of-two scales, '
+                        'no host synchronisation) launched eagerly and replayed as ONE CUDA graph of the whole layer')
     p.add_argument('--forward-fp8', action='store_true',
                    help='also time the inference forward: BF16 path against the FP8 path (e4m3 dispatch + block-scaled FP8 GEMMs)')
     args = p.parse_args()
@@ -222,6 +225,51 @@ def main():
                 y8h = ours.forward_fp8(x)
             result['fp8_ue8m0_forward_rel_diff_vs_bf16'] = round(((y8h.float() - y16.float()).norm() / y16.float().norm()).item(), 5)
             result['forward_fp8_ue8m0_ms'] = round(time_forward(ours.forward_fp8, x, args.steps, args.warmup), 3)
+    if args.decode_graph > 0:
+        # decode: route -> FP8 dispatch -> FP8 expert GEMMs -> combine (+ shared expert) without touching the host, so the
+        # whole layer is one CUDA graph; the weights are shared with the layer above, only the buffer is decode-sized
+        assert args.hidden % 512 == 0 and args.intermediate % 512 == 0
+        tokens = args.decode_graph
+        dcfg = MoEConfig(hidden=args.hidden, intermediate=args.intermediate, num_experts=args.num_experts, num_topk=args.num_topk,
+                         num_shared_experts=1, num_max_tokens_per_rank=tokens, expert_alignment=128, fp8_scales='ue8m0',
+                         host_sync=False)
+        ours.config.fp8_scales = 'ue8m0'
+        ours.quantize_weights()
+        decode_buffer = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=tokens, hidden=args.hidden,
+                                         num_topk=args.num_topk, explicitly_destroy=True)
+        saved = ours.config, ours.buffer
+        ours.config, ours.buffer = dcfg, decode_buffer
+        xd = torch.randn(tokens, args.hidden, device=dev, dtype=torch.bfloat16)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                y_eager = ours.forward_fp8(xd)
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                y_graph = ours.forward_fp8(xd)
+        torch.cuda.synchronize()
+        dist.barrier()
+
+        def timed(fn):
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps + 3)]
+            for a, b in ev:
+                a.record()
+                fn()
+                b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([sum(a.elapsed_time(b) for a, b in ev[3:]) / args.steps], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return round(t.item() * 1e3, 1)
+        result['decode_tokens_per_rank'] = tokens
+        result['decode_forward_fp8_eager_us'] = timed(lambda: ours.forward_fp8(xd))
+        result['decode_forward_fp8_one_graph_us'] = timed(graph.replay)
+        decode_buffer.runtime.check_status()
+        result['decode_graph_matches_eager'] = bool(torch.equal(y_graph, y_eager))
+        ours.config, ours.buffer = saved
+        ours.config.fp8_scales, ours._w1_fp8 = 'fp32', None         # the next section quantises for itself
+        decode_buffer.destroy()
     if 'baseline_ms' in result:
         result['speedup'] = round(result['baseline_ms'] / result['ours_ms'], 3)
     if rank == 0:

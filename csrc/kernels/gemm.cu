@@ -68,13 +68,27 @@ int* failure_word_checked() {
 
 }  // namespace
 
+namespace {
+
+// The tensor-map encoder is a driver entry point and wants a current context on the calling thread; autograd worker
+// threads may not have touched the runtime yet. Done once per thread, so that later launches (for instance inside a
+// CUDA-graph capture, where memory-management calls are not allowed) make no such call.
+void ensure_context_once_per_thread() {
+    static thread_local bool ready = false;
+    if (ready) return;
+    CUDA_CHECK(cudaFree(nullptr));
+    ready = true;
+}
+
+}  // namespace
+
 void grouped_gemm_fp8(kernels::GroupedGemmFp8Args args, const void* a, int64_t a_rows, const void* b, int64_t b_rows,
                       int num_sms, cudaStream_t stream) {
     using namespace kernels;
     EP_HOST_ASSERT(args.num_groups > 0 and args.num_groups <= kMaxLocalExperts);
     EP_HOST_ASSERT_MSG(args.k > 0 and args.k % kFp8BlockK == 0, "K must be a multiple of 128");
     EP_HOST_ASSERT(a_rows > 0);
-    CUDA_CHECK(cudaFree(nullptr));       // the driver call below needs a current context
+    ensure_context_once_per_thread();
     args.status = failure_word_checked();
     if (args.epilogue != kEpilogueStore) {
         EP_HOST_ASSERT_MSG(args.epilogue == kEpilogueSwiGLU and args.n % 256 == 0, "SwiGLU needs N (gate + up) to be a multiple of 256");
@@ -115,8 +129,7 @@ void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, 
                   const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream, bool use_pairs) {
     using namespace kernels;
     EP_HOST_ASSERT(args.num_groups > 0 and args.num_groups <= kMaxLocalExperts);
-    // the driver call below needs a current context; autograd worker threads may not have touched the runtime yet
-    CUDA_CHECK(cudaFree(nullptr));
+    ensure_context_once_per_thread();
     args.status = failure_word_checked();
     if (args.epilogue != kEpilogueStore) {
         EP_HOST_ASSERT(args.mode == kModeForward and args.n % 256 == 0);

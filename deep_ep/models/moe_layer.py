@@ -33,6 +33,10 @@ class MoEConfig:
     fp8_training: bool = False          # training: forward and data-gradient GEMMs of the routed experts in FP8 (e4m3, power-of-two
                                         # 1x128 / 128x128 scales applied by the tensor core), weight gradients in bf16;
                                         # hidden and intermediate must be multiples of 512
+    host_sync: bool = True              # dispatch waits on the host for the received-token counts and sizes its outputs exactly;
+                                        # False: outputs get their worst-case size and nothing touches the host, so a whole
+                                        # forward pass can be captured in one CUDA graph (decode); consumers read the counts
+                                        # from the handle's device tensors, as the grouped GEMMs do
     overlap_shared_expert: bool = False # run the shared expert on a side stream next to dispatch / routed experts / combine
     fuse_combine: bool = False          # the second expert GEMM stores the rows of single-row tokens straight into their
                                         # owners' combine landing slots (over NVLink, tile by tile); combine sends the rest
@@ -52,7 +56,7 @@ class _Dispatch(torch.autograd.Function):
         recv_x, _, recv_w, handle, _ = layer.buffer.dispatch(
             x, topk_idx=topk_idx, topk_weights=topk_weights, num_experts=cfg.num_experts,
             expert_alignment=cfg.expert_alignment, num_sms=cfg.num_sms, do_expand=True, do_zero_padding=True,
-            do_cpu_sync=True)
+            do_cpu_sync=cfg.host_sync)
         ctx.layer, ctx.handle = layer, handle
         layer._handle = handle
         return recv_x, recv_w
@@ -173,7 +177,7 @@ class MoELayer(nn.Module):
         (recv_x, recv_sf), _, recv_w, handle, _ = self.buffer.dispatch(
             x, topk_idx=topk_idx, topk_weights=topk_weights.float().contiguous(), num_experts=cfg.num_experts,
             expert_alignment=cfg.expert_alignment, num_sms=cfg.num_sms, do_expand=True, do_zero_padding=True,
-            do_cpu_sync=True, fused_fp8_quant='ue8m0' if cfg.fp8_scales == 'ue8m0' else True)
+            do_cpu_sync=cfg.host_sync, fused_fp8_quant='ue8m0' if cfg.fp8_scales == 'ue8m0' else True)
         route = None
         if cfg.fuse_combine and cfg.fp8_scales == 'ue8m0':
             route = self.buffer.build_combine_route(handle, cfg.hidden)

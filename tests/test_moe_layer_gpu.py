@@ -179,6 +179,27 @@ def _new_paths_worker(rank, world_size):
         rel = ((a - b).norm() / b.norm().clamp(min=1e-12)).item()
         assert torch.isfinite(a).all() and rel < 0.12, f'FP8 training {name} deviates from bf16 by {rel}'
     layer8.config.fp8_training = False
+
+    # the whole inference layer as ONE CUDA graph: the dispatch does not wait on the host (`host_sync=False`), outputs have
+    # their worst-case size, the grouped GEMMs read the counts on the device
+    layer8.config.host_sync = False
+    eager = layer8.forward_fp8(x)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            layer8.forward_fp8(x)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            captured = layer8.forward_fp8(x)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph.replay()
+    torch.cuda.synchronize()
+    layer8.buffer.runtime.check_status()
+    assert torch.equal(eager, plain8), 'the layer without host synchronisation differs from the synchronised one'
+    assert torch.equal(captured, eager), 'graph replay of the whole layer differs from the eager run'
     layer8.destroy()
 
     # weights applied inside the combine kernel against weights applied by the caller (one rounding less, so not bitwise)
