@@ -75,14 +75,24 @@ def main():
         for s, o in zip(shards, nccl_out):
             dist.all_gather_into_tensor(o, s)
 
+    # the most NCCL can do for this job: ONE all-gather of all shards laid end to end (the result is rank-major over the
+    # whole batch, so a real user would still have to re-slice it per tensor; that pass is not charged)
+    flat_shard = torch.cat(shards)
+    flat_out = torch.empty(flat_shard.numel() * world, device=dev, dtype=torch.bfloat16)
+
+    def nccl_flat():
+        dist.all_gather_into_tensor(flat_out, flat_shard)
+
     ours()
     torch.cuda.synchronize()
     for d, s in zip(dsts[:4] + dsts[-4:], shards[:4] + shards[-4:]):       # spot check against the local shard
         assert torch.equal(d.view(world, -1)[rank], s)
-    ours_ms, nccl_ms = timed(ours, args.iters), timed(nccl, args.iters)
+    ours_ms, nccl_ms, nccl_flat_ms = timed(ours, args.iters), timed(nccl, args.iters), timed(nccl_flat, args.iters)
+    del flat_out
     recv_bytes = total * world
     result = {'bench': 'bucket_all_gather+pp_overlap', 'n_gpus': world, 'num_tensors': len(sizes), 'bytes_per_rank_shards': total,
               'all_gather': {'ours_ms': round(ours_ms, 3), 'nccl_ms': round(nccl_ms, 3),
+                             'nccl_one_flat_call_ms': round(nccl_flat_ms, 3),
                              'ours_recv_gbs': round(recv_bytes / ours_ms / 1e6, 1), 'nccl_recv_gbs': round(recv_bytes / nccl_ms / 1e6, 1),
                              'ours_bus_gbs': round(recv_bytes * (world - 1) / world / ours_ms / 1e6, 1)}}
 
@@ -107,9 +117,13 @@ def main():
         d.zero_()                                    # keep values finite over the timed repetitions
     for o in nccl_out:
         o.zero_()
+    flat_ar = torch.zeros(sum(o.numel() for o in nccl_out), device=dev, dtype=torch.bfloat16)
     ar_ms, nccl_ar_ms = timed(ours_ar, args.iters), timed(nccl_ar, args.iters)
+    nccl_ar_flat_ms = timed(lambda: dist.all_reduce(flat_ar), args.iters)      # one call over the same number of bytes
+    del flat_ar
     ar_bytes = total * world
     result['all_reduce'] = {'bytes_per_rank': ar_bytes, 'ours_ms': round(ar_ms, 3), 'nccl_ms': round(nccl_ar_ms, 3),
+                            'nccl_one_flat_call_ms': round(nccl_ar_flat_ms, 3),
                             'ours_bus_gbs': round(2 * ar_bytes * (world - 1) / world / ar_ms / 1e6, 1),
                             'nccl_bus_gbs': round(2 * ar_bytes * (world - 1) / world / nccl_ar_ms / 1e6, 1)}
     bucket.destroy()
