@@ -80,7 +80,9 @@ def _wgrad(dy, x, w, psum, count, alignment):
 def row_scale_grad(dact: torch.Tensor, act: torch.Tensor, row_scale: torch.Tensor) -> torch.Tensor:
     """Gradient of the per-row scale `s` of `act = s * silu(gate) * up` given `dact = dL/dact`: `<dact, act> / s` per row
     (rows with `s == 0`, i.e. padding, get 0). This is what carries the loss back to the routing weights."""
-    dot = (dact.float() * act.float()).sum(dim=1)
+    # products in the tensors' own precision (one rounding each, errors average out over the row), fp32 accumulation:
+    # two passes over [rows, I] instead of the four that an fp32 copy of both operands would cost
+    dot = torch.sum(dact * act, dim=1, dtype=torch.float32)
     return torch.where(row_scale != 0, dot / row_scale, torch.zeros_like(dot))
 
 

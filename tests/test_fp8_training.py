@@ -128,3 +128,19 @@ def test_fp8_training_ffn_on_gpu():
         assert torch.isfinite(g.float()).all(), name
         assert _rel(g.cpu(), e) < 0.03, f'{name} against the emulation: {_rel(g.cpu(), e)}'
         assert _rel(g, r) < 0.1, f'{name} against fp32: {_rel(g, r)}'
+
+
+def test_row_scale_grad_matches_fp32():
+    """`<dact, act> / s` per row with products in bf16 and fp32 accumulation against a pure fp32 evaluation."""
+    from deep_ep.ops.grouped_gemm import row_scale_grad
+    torch.manual_seed(4)
+    dact = torch.randn(200, 2048).to(torch.bfloat16)
+    act = (torch.randn(200, 2048) * 0.3).to(torch.bfloat16)
+    scale = torch.rand(200) + 0.1
+    scale[::17] = 0                                         # padding rows
+    got = row_scale_grad(dact, act, scale)
+    ref = (dact.double() * act.double()).sum(1) / scale.double()
+    live = scale != 0
+    assert got.dtype == torch.float32 and bool((got[~live] == 0).all())
+    err = (got[live].double() - ref[live]).abs().max() / ref[live].abs().max()
+    assert err < 2e-3, err
