@@ -1,6 +1,7 @@
 """FP8 training path of the expert FFN (`deep_ep.ops.fp8_training`): the composition (quantisers, transposed weight
 copies, autograd wiring, weight cache) on CPU through the PyTorch emulation, and, on a GPU, the CUDA quantisers bit for
-bit against that emulation and the whole FFN against it within FP8 tolerance."""
+bit against that emulation and the whole FFN against it within FP8 tolerance. Also here: the autograd wiring of the
+bf16 FFN node with its kernels emulated, and the routing-weight gradient both nodes share."""
 import os
 
 import pytest
@@ -144,3 +145,57 @@ def test_row_scale_grad_matches_fp32():
     assert got.dtype == torch.float32 and bool((got[~live] == 0).all())
     err = (got[live].double() - ref[live]).abs().max() / ref[live].abs().max()
     assert err < 2e-3, err
+
+
+def test_bf16_ffn_autograd_wiring_with_emulated_kernels(monkeypatch):
+    """`GroupedSwiGLUFFN` (the bf16 training node) with its CUDA kernels replaced by PyTorch stand-ins: every returned
+    gradient, the routing-weight gradient included, must match autograd on the plain formula."""
+    from deep_ep.ops import grouped_gemm as gg
+    from deep_ep.ops.fp8_training import _swiglu_backward
+
+    def forward(x, w, psum, count, swiglu=False, num_sms=0, alignment=1, row_scale=None, keep_preactivation=False, route=None):
+        y = torch.zeros(x.size(0), w.size(1), dtype=torch.float32)
+        for e, (s, c) in enumerate(gg._ranges(psum, count)):
+            y[s:s + c] = x[s:s + c].float() @ w[e].float().t()
+        if not swiglu:
+            return y.to(torch.bfloat16)
+        h = y.to(torch.bfloat16)
+        g, u = h.float().chunk(2, dim=-1)
+        act = F.silu(g) * u * (1.0 if row_scale is None else row_scale[:, None])
+        return (act.to(torch.bfloat16), h) if keep_preactivation else act.to(torch.bfloat16)
+
+    def dgrad(dy, w, psum, count, num_sms=0, alignment=1, route=None):
+        dx = torch.zeros(dy.size(0), w.size(2), dtype=torch.float32)
+        for e, (s, c) in enumerate(gg._ranges(psum, count)):
+            dx[s:s + c] = dy[s:s + c].float() @ w[e].float()
+        return dx.to(torch.bfloat16)
+
+    class FakeC:
+        swiglu_backward = staticmethod(_swiglu_backward)
+
+    monkeypatch.setattr(gg, 'grouped_gemm_forward', forward)
+    monkeypatch.setattr(gg, 'grouped_gemm_dgrad', dgrad)
+    monkeypatch.setattr(gg, '_wgrad', lambda dy, x, w, psum, count, alignment, _orig=gg._wgrad: _orig(dy, x, w, psum, count, 1))
+    monkeypatch.setattr(gg, '_C', FakeC)
+
+    torch.manual_seed(8)
+    counts, alignment, hidden, inter = [50, 0, 77], 128, 128, 128
+    psum, count, rows, starts, x, dy, w1, w2, row_scale = _problem(counts, alignment, hidden, inter, torch.device('cpu'))
+    for s, c in zip(starts, counts):                       # padding rows carry weight 0, as the dispatch delivers them
+        row_scale[s + c:(s + c + alignment - 1) // alignment * alignment] = 0
+    xr, w1r, w2r, sr = x.clone().requires_grad_(), w1.clone().requires_grad_(), w2.clone().requires_grad_(), \
+        row_scale.clone().requires_grad_()
+    y = gg.GroupedSwiGLUFFN.apply(xr, w1r, w2r, sr, psum, count, alignment)
+    y.backward(dy)
+
+    x32, w1f, w2f, s32 = x.float().requires_grad_(), w1.float().requires_grad_(), w2.float().requires_grad_(), \
+        row_scale.clone().requires_grad_()
+    out = torch.zeros(rows, hidden)
+    for e, (s, c) in enumerate(zip(starts, counts)):
+        if c:
+            g, u = (x32[s:s + c] @ w1f[e].t()).chunk(2, dim=-1)
+            out[s:s + c] = (F.silu(g) * u * s32[s:s + c, None]) @ w2f[e].t()
+    out.backward(dy.float())
+    for name, got, want in (('y', y, out), ('dx', xr.grad, x32.grad), ('dw_gate_up', w1r.grad, w1f.grad),
+                            ('dw_down', w2r.grad, w2f.grad), ('d_row_scale', sr.grad, s32.grad)):
+        assert got is not None and _rel(got, want.detach()) < 0.02, f'{name}: {_rel(got, want.detach())}'
