@@ -2,9 +2,10 @@
 with a backward pass that reuses the routing handle (the gradient of dispatch is a combine and the
 gradient of combine is a cached dispatch). The router trains too: the expert FFN returns the gradient of every
 expanded row's routing weight, and the combine that is the backward of dispatch carries those scalars back to their
-(token, top-k position) through its positional weight channel, from where autograd reaches the gate matrix. This is the "one model" of a communication library: the
-layer shape follows the DeepSeek-V3 expert FFN (hidden 7168, intermediate 2048, 256 routed experts,
-top-8, one shared expert), cf. the usage sketch in the reference's `README.md:178-194`.
+(token, top-k position) through its positional weight channel, from where autograd reaches the gate matrix.
+This is the "one model" of a communication library: the layer shape follows the DeepSeek-V3 expert FFN (hidden 7168,
+intermediate 2048, 256 routed experts, top-8, one shared expert), cf. the usage sketch in the reference's
+`README.md:178-194`.
 """
 from dataclasses import dataclass
 from typing import Optional
