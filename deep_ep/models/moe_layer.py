@@ -27,10 +27,10 @@ class MoEConfig:
     num_shared_experts: int = 0
     num_max_tokens_per_rank: int = 4096
     expert_alignment: int = 128
-    fp8_dispatch: bool = False          # inference (`forward_fp8`): e4m3 dispatch (1x128 scales, quantised inside the
-                                        # dispatch kernel) feeding block-scaled FP8 expert GEMMs
-    fp8_scales: str = 'fp32'            # 'fp32': scales amax / 448, promoted in registers by the GEMM; 'ue8m0': powers of two,
-                                        # applied by the tensor core (hidden and intermediate must be multiples of 512)
+    fp8_scales: str = 'fp32'            # inference (`forward_fp8`: e4m3 dispatch quantised inside the dispatch kernel feeding
+                                        # block-scaled FP8 expert GEMMs). 'fp32': scales amax / 448, promoted in registers by the
+                                        # GEMM; 'ue8m0': powers of two, applied by the tensor core (hidden and intermediate
+                                        # must be multiples of 512)
     fp8_training: bool = False          # training: forward and data-gradient GEMMs of the routed experts in FP8 (e4m3, power-of-two
                                         # 1x128 / 128x128 scales applied by the tensor core), weight gradients in bf16;
                                         # hidden and intermediate must be multiples of 512
