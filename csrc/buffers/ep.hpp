@@ -238,7 +238,8 @@ public:
         if (num_sms <= 0) num_sms = Runtime::get().get_num_sms();
 
         if (do_cpu_sync) {
-            host_counts->num_recv_tokens = 0, host_counts->num_expanded_tokens = 0;
+            host_counts->num_recv_tokens = 0;
+            host_counts->num_expanded_tokens = 0;
             std::atomic_thread_fence(std::memory_order_seq_cst);
         }
 
