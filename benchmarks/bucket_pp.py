@@ -177,6 +177,28 @@ def main():
                                          'nccl_p2p_gbs': round(act.nbytes / nccl_ms / 1e6, 1)})
         except Exception as e:
             result['pp_overlap']['nccl_p2p_error'] = str(e).splitlines()[0][:200]
+        # `PPBuffer(transport='nccl')`: the same buffered API on top of NCCL point-to-point (staging slots, two process
+        # groups for the two directions of a pair)
+        try:
+            pp_lib = deep_ep.PPBuffer(group_a, act.nbytes, 2, explicitly_destroy=True, transport='nccl')
+
+            def lib_only():
+                pp_lib.send(act, nxt)
+                pp_lib.recv(recv, prv)
+
+            def lib_overlapped():
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    lib_only()
+                torch.mm(act, w)
+                torch.cuda.current_stream().wait_stream(side)
+
+            lib_ms, lib_both_ms = timed(lib_only, args.iters), timed(lib_overlapped, args.iters)
+            result['pp_overlap'].update({'ppbuffer_nccl_transport_ms': round(lib_ms, 3),
+                                         'ppbuffer_nccl_transport_overlapped_ms': round(lib_both_ms, 3)})
+            pp_lib.destroy()
+        except Exception as e:
+            result['pp_overlap']['ppbuffer_nccl_transport_error'] = str(e).splitlines()[0][:200]
     if rank == 0:
         print(json.dumps(result))
     pp.destroy()

@@ -1,6 +1,8 @@
 """`PPBuffer`: buffered send/recv between ring neighbours (reference: `deep_ep/buffers/pp.py:13-86`)."""
 from typing import Optional
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -18,6 +20,10 @@ class PPBuffer(BufferBase):
     between a pair are FIFO and carry no header: sender and receiver agree on sizes by convention.
 
     Stream usage: every operation runs on the current stream.
+
+    `transport` (keyword, or `EP_PP_TRANSPORT` in the environment): `'nvlink'` (default) is this library's own ring of
+    landing slots in peer memory, written and drained by its kernels; `'nccl'` moves the payload with the process group's
+    point-to-point calls on the library's streams (`deep_ep/buffers/pp_p2p.py`), with the same buffered semantics.
     """
 
     barrier = comm.barrier
@@ -25,16 +31,23 @@ class PPBuffer(BufferBase):
 
     def __init__(self, group: dist.ProcessGroup, num_max_tensor_bytes: int, num_max_inflight_tensors: int,
                  sl_idx: Optional[int] = None, num_gpu_timeout_secs: int = 100, explicitly_destroy: bool = False,
-                 *, use_huge1g_page: bool = True):
+                 *, use_huge1g_page: bool = True, transport: Optional[str] = None):
         if sl_idx is not None:
             raise NotImplementedError('RDMA service levels do not exist on NVLink')
         assert num_max_tensor_bytes > 0 and num_max_inflight_tensors > 0 and num_gpu_timeout_secs > 0
+        transport = transport or os.environ.get('EP_PP_TRANSPORT', 'nvlink')
+        assert transport in ('nvlink', 'nccl'), f'unknown PPBuffer transport {transport!r}'
+        self.transport = transport
         self.group = group
         self.rank_idx, self.num_ranks = group.rank(), group.size()
         self.comm_handle = comm.get_comm_handle(group)
         super().__init__(explicitly_destroy)
         self.is_simulated = not torch.cuda.is_available()
-        if self.is_simulated:
+        if transport == 'nccl':
+            from .pp_p2p import LibraryP2PRuntime
+            device = torch.device('cpu') if self.is_simulated else torch.device('cuda', torch.cuda.current_device())
+            self.runtime = LibraryP2PRuntime(group, num_max_tensor_bytes, num_max_inflight_tensors, device)
+        elif self.is_simulated:
             from ..sim.buffers import SimPPRuntime
             self.runtime = SimPPRuntime(group, num_max_tensor_bytes, num_max_inflight_tensors)
         else:

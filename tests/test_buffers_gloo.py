@@ -82,11 +82,11 @@ def _bucket_worker(rank, world):
     bucket.destroy()
 
 
-def _pp_worker(rank, world):
+def _pp_worker(rank, world, transport='nvlink'):
     import torch.distributed as dist
     import deep_ep
-    pp = deep_ep.PPBuffer(dist.group.WORLD, 1 << 16, 3, explicitly_destroy=True)
-    assert pp.is_simulated
+    pp = deep_ep.PPBuffer(dist.group.WORLD, 1 << 16, 3, explicitly_destroy=True, transport=transport)
+    assert pp.is_simulated and pp.transport == transport
     nxt, prv = (rank + 1) % world, (rank - 1) % world
     # several sends run ahead of their receives (up to the in-flight limit), FIFO per pair
     for i in range(3):
@@ -166,6 +166,13 @@ def test_bucket_buffer_two_cpu_ranks(master_port):
 @pytest.mark.parametrize('world', [2, 4])
 def test_pp_buffer_cpu_ranks(master_port, world):
     run_distributed(_pp_worker, world, master_port, 'gloo', timeout_s=120)
+
+
+@pytest.mark.parametrize('world', [2, 3])
+def test_pp_buffer_library_transport_cpu_ranks(master_port, world):
+    """`transport='nccl'`: the process group's own send / recv behind staging slots (over gloo on CPU ranks), with the
+    same buffered semantics: sends run ahead of their receives, also when both ranks of a pair send first."""
+    run_distributed(_pp_worker, world, master_port, 'gloo', ('nccl',), timeout_s=120)
 
 
 @pytest.mark.parametrize('use_fp8', [False, True])
