@@ -41,6 +41,7 @@ class LibraryP2PRuntime:
         self._slots = self.storage.view(2, num_max_inflight_tensors, slot_bytes)
         self._pending: Dict[int, List[Tuple[object, int]]] = {0: [], 1: []}      # per direction: (work, slot)
         self._sent = [0, 0]
+        self._loopback: List[torch.Tensor] = []      # a ring of one rank: staged messages waiting for their recv
         self.destroyed = False
 
     def _neighbours(self) -> Tuple[int, int]:
@@ -63,12 +64,23 @@ class LibraryP2PRuntime:
         while pending and (len(pending) >= self.num_max_inflight or any(s == slot for _, s in pending)):
             pending.pop(0)[0].wait()                                  # the send that last read this slot is over
         staged = self._slots[direction, slot, :x.nbytes]
+        if self.num_ranks == 1:
+            assert len(self._loopback) < self.num_max_inflight, 'more sends in flight than `num_max_inflight_tensors`'
+            staged.copy_(x.view(-1).view(torch.uint8))
+            self._loopback.append(staged)
+            return
         staged.copy_(x.view(-1).view(torch.uint8))
         work = dist.isend(staged, dist.get_global_rank(self.group, dst), group=self._group_for(self.rank_idx, dst))
         pending.append((work, slot))
 
     def recv(self, x: torch.Tensor, src: int, num_sms: int) -> None:
         self._check(x, src)
+        if self.num_ranks == 1:
+            assert self._loopback, 'recv without a matching send'
+            staged = self._loopback.pop(0)
+            assert staged.numel() == x.nbytes, 'send and recv sizes must match'
+            x.view(-1).view(torch.uint8).copy_(staged)
+            return
         work = dist.irecv(x.view(-1).view(torch.uint8), dist.get_global_rank(self.group, src),
                           group=self._group_for(src, self.rank_idx))
         work.wait()                      # NCCL: the current stream waits; gloo: the host waits

@@ -28,6 +28,9 @@ class SimContext:
     def has_multicast(self) -> bool:
         return False
 
+    def status_code(self) -> int:
+        return 0
+
 
 class _NoEvent:
     """Stands where a CUDA event would be: everything has already happened when a CPU call returns."""

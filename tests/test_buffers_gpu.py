@@ -319,12 +319,13 @@ def test_bucket_reduce_scatter_all_reduce(master_port):
     run_distributed(_reduce_worker, _world(), master_port, 'nccl')
 
 
-def _pp_worker(rank, world):
+def _pp_worker(rank, world, transport='nvlink'):
     import random
     import torch.distributed as dist
     import deep_ep
     inflight = 3
-    pp = deep_ep.PPBuffer(dist.group.WORLD, 1 << 20, inflight, explicitly_destroy=True, num_gpu_timeout_secs=10)
+    pp = deep_ep.PPBuffer(dist.group.WORLD, 1 << 20, inflight, explicitly_destroy=True, num_gpu_timeout_secs=10,
+                          transport=transport)
     nxt, prv = (rank + 1) % world, (rank + world - 1) % world
     # ring: everybody sends `inflight` messages ahead to the next rank, then receives them from the previous one
     msgs = [torch.full((1000 + 37 * i,), float(rank * 10 + i), device='cuda') for i in range(inflight)]
@@ -372,6 +373,14 @@ def _pp_worker(rank, world):
 def test_pp_send_recv(master_port):
     world = _world()
     run_distributed(_pp_worker, world, master_port, 'nccl')
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(__import__('os').environ.get('EP_TEST_NEW_PATHS', '0') != '1',
+                    reason='path that has not run on a GPU yet; set EP_TEST_NEW_PATHS=1 to try it')
+def test_pp_send_recv_over_nccl_point_to_point(master_port):
+    """The same schedule through `PPBuffer(transport='nccl')`."""
+    run_distributed(_pp_worker, _world(), master_port, 'nccl', ('nccl',), timeout_s=120)
 
 
 # ---------------------------------------------------------------------------------------------------- engram
