@@ -157,6 +157,9 @@ def main():
     p.add_argument('--fp8-training', action='store_true',
                    help='also time forward + backward with the routed experts\' forward and data-gradient GEMMs in FP8 '
                         '(power-of-two block scales applied by the tensor core; weight gradients stay bf16)')
+    p.add_argument('--main-grad', action='store_true',
+                   help='expert weight gradients accumulate in persistent fp32 `main_grad` buffers (read-modify-write in the '
+                        'weight-gradient kernel) instead of being stored once in bf16')
     p.add_argument('--decode-graph', type=int, default=0, metavar='TOKENS',
                    help='also time a decode-sized inference forward (this many tokens per rank, FP8 with power-of-two scales, '
                         'no host synchronisation) launched eagerly and replayed as ONE CUDA graph of the whole layer')
@@ -189,6 +192,10 @@ def main():
         result['baseline_ms'] = round(time_layer(base, x, args.steps, args.warmup), 3)
         del base
         torch.cuda.empty_cache()
+    if args.main_grad:
+        for w in (ours.w_gate_up, ours.w_down):
+            w.main_grad = torch.zeros(w.shape, dtype=torch.float32, device=dev)
+        result['wgrad'] = 'fp32 accumulation into main_grad'
     result['ours_ms'] = round(time_layer(ours, x, args.steps, args.warmup), 3)
     # useful FLOPs: 3 GEMMs (gate, up, down) x (fwd + dgrad + wgrad) over routed + shared expert rows
     rows = args.num_tokens * (args.num_topk + 1)
