@@ -39,11 +39,16 @@ class BaselineMoELayer(nn.Module):
         self.w_down = nn.Parameter(ours.w_down.detach().clone())
         self.shared_gate_up = nn.Parameter(ours.shared_gate_up.detach().clone()) if ours.config.num_shared_experts else None
         self.shared_down = nn.Parameter(ours.shared_down.detach().clone()) if ours.config.num_shared_experts else None
-        self.route = ours.route
+
+    def route(self, x):
+        # library GEMM (cuBLAS) for the router of the baseline, same arithmetic as the layer's own kernel
+        logits = F.linear(x, self.gate.to(torch.bfloat16)).float() if x.dtype == torch.bfloat16 else F.linear(x.float(), self.gate)
+        topk_weights, topk_idx = torch.softmax(logits, dim=-1).topk(self.config.num_topk, dim=-1)
+        return topk_idx, topk_weights / topk_weights.sum(dim=-1, keepdim=True)
 
     def forward(self, x):
         cfg = self.config
-        topk_idx, topk_w = self.route(x.detach())
+        topk_idx, topk_w = self.route(x)
         t, k = topk_idx.shape
         flat_expert = topk_idx.reshape(-1)
         order = torch.argsort(flat_expert, stable=True)                      # (token, slot) pairs grouped by expert

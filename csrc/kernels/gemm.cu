@@ -1,6 +1,7 @@
 // Launcher of the grouped tcgen05 GEMM: builds the two TMA tensor maps (128-byte swizzle) and starts one
 // persistent CTA per SM.
 #include <algorithm>
+#include <cstdlib>
 
 #include <deep_ep/common/exception.hpp>
 #include <deep_ep/kernels/grouped_gemm.cuh>
@@ -125,6 +126,17 @@ void grouped_gemm_fp8(kernels::GroupedGemmFp8Args args, const void* a, int64_t a
     CUDA_CHECK(cudaGetLastError());
 }
 
+namespace {
+// EP_GEMM_L2_PREFETCH=<K blocks>: look-ahead of the producer's L2 prefetches in the bf16 kernel (0 switches them off)
+int l2_prefetch_distance() {
+    static const int distance = [] {
+        const char* text = std::getenv("EP_GEMM_L2_PREFETCH");
+        return text != nullptr ? std::max(0, std::atoi(text)) : 0;
+    }();
+    return distance;
+}
+}  // namespace
+
 void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, int64_t a_cols,
                   const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream, bool use_pairs) {
     using namespace kernels;
@@ -148,7 +160,7 @@ void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, 
     const int64_t budget = 200 * 1024;
 
     // CTA pairs (256 x 256 tiles) whenever the shape allows it; the single-CTA kernel covers the rest
-    const bool pair = use_pairs and args.block_n == 256 and grid >= 2 and (args.mode != kModeWgrad or args.m % 256 == 0);
+    const bool pair = use_pairs and args.block_n == 256 and grid >= 2 and not args.out_fp32 and (args.mode != kModeWgrad or args.m % 256 == 0);
     if (pair) {
         grid -= grid % 2;
         args.num_stages = static_cast<int>(std::min<int64_t>(kGemmMaxStages, (budget - 1024) / (2 * 128 * kGemmBlockK * 2)));
@@ -168,6 +180,7 @@ void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, 
     // B: K-major weights (box 64 x 128) for forward, MN-major (box 64 x 64) otherwise
     const CUtensorMap map_b = args.mode == kModeForward ? make_map_2d(b, b_rows, b_cols, 64, 128) : make_map_2d(b, b_rows, b_cols, 64, 64);
     const auto smem = grouped_gemm_smem_bytes(args.block_n, args.num_stages);
+    args.l2_prefetch = l2_prefetch_distance();
     CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     grouped_gemm_kernel<<<grid, 192, smem, stream>>>(map_a, map_b, args);
     CUDA_CHECK(cudaGetLastError());

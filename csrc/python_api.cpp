@@ -96,7 +96,11 @@ void grouped_gemm(const torch::Tensor& a, const torch::Tensor& b, const torch::T
         args.n = static_cast<int>(b.size(1)), args.k = static_cast<int>(a.size(1));
         b_rows = g * b.size(1), b_cols = b.size(2);
         const int64_t n_out = epilogue != kEpilogueStore ? args.n / 2 : args.n;
-        EP_HOST_ASSERT(d.scalar_type() == torch::kBFloat16 and d.dim() == 2 and d.size(0) == rows and d.size(1) == n_out);
+        EP_HOST_ASSERT(d.dim() == 2 and d.size(0) == rows and d.size(1) == n_out);
+        // fp32 output (the accumulator as it is) only from the plain-store epilogue without a destination table
+        EP_HOST_ASSERT(d.scalar_type() == torch::kBFloat16 or
+                       (d.scalar_type() == torch::kFloat32 and epilogue == kEpilogueStore and not route.has_value()));
+        args.out_fp32 = d.scalar_type() == torch::kFloat32;
         EP_HOST_ASSERT(args.k % 8 == 0);
     } else if (mode == kModeDgrad) {
         EP_HOST_ASSERT(b.size(0) == g and b.size(1) == a.size(1) and epilogue == kEpilogueStore);

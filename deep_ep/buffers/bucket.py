@@ -39,6 +39,8 @@ class BucketSession:
         for name in ('all_gather', 'reduce_scatter', 'all_reduce'):
             self._saved[name] = getattr(self.buffer, name)
         self.buffer.all_gather = self._all_gather
+        self.buffer.reduce_scatter = self._reduce_scatter
+        self.buffer.all_reduce = self._all_reduce
         return self
 
     def __exit__(self, exc_type, exc_val, exc_tb) -> None:
@@ -108,6 +110,64 @@ class BucketSession:
                 user_dst.view(-1).copy_(gathered[i].view(-1))
                 gathered[i] = user_dst
             return gathered[0] if is_packed else gathered
+        handle.register_hook_after_wait(hook)
+        return handle
+
+
+    def _stage_sources(self, srcs) -> Tuple[List[torch.Tensor], Dict[int, torch.Tensor]]:
+        """Registered stand-ins for the sources of a reduction: tensors inside the storage are used as they are, others
+        are copied (on the current stream) into a carved region. Every rank must stage the same tensors in the same
+        order, so that the regions sit at the same storage offsets everywhere."""
+        inner: List[torch.Tensor] = []
+        staged: Dict[int, torch.Tensor] = {}
+        for i, src in enumerate(srcs):
+            if self._inside(src):
+                assert src.is_contiguous(), 'a registered source must be contiguous'
+                inner.append(src)
+                continue
+            region = self._carve(src.nbytes).view(src.dtype).view(src.shape)
+            region.copy_(src)
+            inner.append(region)
+            staged[i] = src
+        return inner, staged
+
+    def _reduce_scatter(self, srcs, comm_precision: str = 'fp32', scale: float = 1.0,
+                        group: Optional[dist.ProcessGroup] = None, num_sms: Optional[int] = None):
+        """`BucketBuffer.reduce_scatter` that also takes tensors outside the storage: those are staged in a registered
+        region first. The handle returns this rank's reduced shards, which for staged tensors are views of the region
+        (valid until the storage is reused), as in the reference's session (`deep_ep/buffers/bucket.py:103-181`)."""
+        group = self._bind_group(group)
+        is_packed, srcs = BucketBuffer._pack_tensors(srcs)
+        inner, _ = self._stage_sources(srcs)
+        handle = self._saved['reduce_scatter'](inner, comm_precision=comm_precision, scale=scale, group=group, num_sms=num_sms)
+        inner_hook = handle.hook_after_wait
+        handle.hook_after_wait = None
+
+        def hook():
+            shards = inner_hook()
+            shards = [shards] if isinstance(shards, torch.Tensor) else list(shards)
+            return shards[0] if is_packed else shards
+        handle.register_hook_after_wait(hook)
+        return handle
+
+    def _all_reduce(self, srcs, scale: float = 1.0, group: Optional[dist.ProcessGroup] = None, num_sms: Optional[int] = None):
+        """`BucketBuffer.all_reduce` that also takes tensors outside the storage: those are staged in a registered region,
+        reduced there, and copied back into the caller's tensor inside the wait hook, so the call stays in place for
+        the caller. The handle returns the caller's tensors."""
+        group = self._bind_group(group)
+        is_packed, srcs = BucketBuffer._pack_tensors(srcs)
+        inner, staged = self._stage_sources(srcs)
+        handle = self._saved['all_reduce'](inner, scale=scale, group=group, num_sms=num_sms)
+        inner_hook = handle.hook_after_wait
+        handle.hook_after_wait = None
+
+        def hook():
+            reduced = inner_hook()
+            reduced = [reduced] if isinstance(reduced, torch.Tensor) else list(reduced)
+            for i, user in staged.items():
+                user.copy_(reduced[i].view(user.shape))
+                reduced[i] = user
+            return reduced[0] if is_packed else reduced
         handle.register_hook_after_wait(hook)
         return handle
 

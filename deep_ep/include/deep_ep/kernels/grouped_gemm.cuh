@@ -57,6 +57,38 @@ EP_DEVICE Tile locate_tile(const GroupedGemmArgs& a, const int* prefix, int tile
     return t;
 }
 
+// TMA boxes of one K block of a tile: into the shared-memory stage (`sa`, `sb`, completion on `bar`) or, with
+// `kPrefetch`, into L2 only.
+template <bool kPrefetch>
+EP_DEVICE void load_k_block(const GroupedGemmArgs& a, const CUtensorMap& map_a, const CUtensorMap& map_b, const Tile& t, int kb,
+                            int BN, uint8_t* sa, uint8_t* sb, uint64_t* bar) {
+    auto box = [&](uint8_t* dst, const CUtensorMap* map, int x, int y) {
+        if constexpr (kPrefetch) tc::tma_prefetch_2d(map, x, y);
+        else tc::tma_load_2d(dst, map, x, y, bar);
+    };
+    const int k0 = kb * kGemmBlockK;
+    if (a.mode == kModeWgrad) {
+        // A = dY^T: source rows are K, columns (contiguous) are M
+        for (int i = 0; i < kGemmBlockM / 64; ++i) box(sa + i * 8192, &map_a, t.m0 + 64 * i, t.row_base + k0);
+        for (int i = 0; i < BN / 64; ++i) box(sb + i * 8192, &map_b, t.n0 + 64 * i, t.row_base + k0);
+        return;
+    }
+    box(sa, &map_a, k0, t.row_base + t.m0);
+    if (a.mode == kModeForward) {
+        // K-major weights [G * N, K]; with SwiGLU the tile pairs 128 gate rows with 128 up rows
+        const int row = t.expert * a.n;
+        if (a.epilogue != kEpilogueStore) {
+            box(sb, &map_b, k0, row + t.n0);
+            box(sb + 128 * 128, &map_b, k0, row + a.n / 2 + t.n0);
+        } else {
+            for (int i = 0; i < BN / 128; ++i) box(sb + i * 128 * 128, &map_b, k0, row + t.n0 + 128 * i);
+        }
+    } else {
+        // MN-major weights [G * K, N]
+        for (int i = 0; i < BN / 64; ++i) box(sb + i * 8192, &map_b, t.n0 + 64 * i, t.expert * a.k + k0);
+    }
+}
+
 }  // namespace gemm_detail
 
 __global__ void __launch_bounds__(192, 1)
@@ -122,36 +154,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t phase = 0;
             for (int tile = blockIdx.x; tile < num_tiles and not error_flag; tile += gridDim.x) {
                 const Tile t = locate_tile(a, tile_prefix, tile);
+                // optional look-ahead: K blocks that the ring will ask for `l2_prefetch` blocks from now (of this tile or
+                // of this CTA's next one) are pulled into L2 already, so that the ring's own loads do not wait for DRAM
+                const bool has_next = a.l2_prefetch > 0 and tile + int(gridDim.x) < num_tiles;
+                const Tile next = has_next ? locate_tile(a, tile_prefix, tile + gridDim.x) : t;
                 for (int kb = 0; kb < t.num_k_blocks; ++kb, s = (s + 1 == S ? 0 : s + 1), phase ^= (s == 0)) {
+                    if (a.l2_prefetch > 0) {
+                        const int ahead = kb + a.l2_prefetch;
+                        if (ahead < t.num_k_blocks) load_k_block<true>(a, map_a, map_b, t, ahead, BN, nullptr, nullptr, nullptr);
+                        else if (has_next and ahead - t.num_k_blocks < next.num_k_blocks)
+                            load_k_block<true>(a, map_a, map_b, next, ahead - t.num_k_blocks, BN, nullptr, nullptr, nullptr);
+                    }
                     if (not ptx::mbarrier_wait(&empty_bar[s], phase ^ 1)) { error_flag = 1; break; }
                     ptx::mbarrier_arrive_expect_tx(&full_bar[s], a_bytes + b_bytes);
-                    uint8_t* sa = smem_a + size_t(s) * a_bytes;
-                    uint8_t* sb = smem_b + size_t(s) * b_bytes;
-                    const int k0 = kb * kGemmBlockK;
-                    if (a.mode == kModeWgrad) {
-                        // A = dY^T: source rows are K, columns (contiguous) are M
-                        for (int i = 0; i < kGemmBlockM / 64; ++i)
-                            tc::tma_load_2d(sa + i * 8192, &map_a, t.m0 + 64 * i, t.row_base + k0, &full_bar[s]);
-                        for (int i = 0; i < BN / 64; ++i)
-                            tc::tma_load_2d(sb + i * 8192, &map_b, t.n0 + 64 * i, t.row_base + k0, &full_bar[s]);
-                    } else {
-                        tc::tma_load_2d(sa, &map_a, k0, t.row_base + t.m0, &full_bar[s]);
-                        if (a.mode == kModeForward) {
-                            // K-major weights [G * N, K]; with SwiGLU the tile pairs 128 gate rows with 128 up rows
-                            const int row = t.expert * a.n;
-                            if (a.epilogue != kEpilogueStore) {
-                                tc::tma_load_2d(sb, &map_b, k0, row + t.n0, &full_bar[s]);
-                                tc::tma_load_2d(sb + 128 * 128, &map_b, k0, row + a.n / 2 + t.n0, &full_bar[s]);
-                            } else {
-                                for (int i = 0; i < BN / 128; ++i)
-                                    tc::tma_load_2d(sb + i * 128 * 128, &map_b, k0, row + t.n0 + 128 * i, &full_bar[s]);
-                            }
-                        } else {
-                            // MN-major weights [G * K, N]
-                            for (int i = 0; i < BN / 64; ++i)
-                                tc::tma_load_2d(sb + i * 8192, &map_b, t.n0 + 64 * i, t.expert * a.k + k0, &full_bar[s]);
-                        }
-                    }
+                    load_k_block<false>(a, map_a, map_b, t, kb, BN, smem_a + size_t(s) * a_bytes, smem_b + size_t(s) * b_bytes, &full_bar[s]);
                 }
             }
         }
@@ -278,11 +294,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (target != 0) out = reinterpret_cast<__nv_bfloat16*>(target) + t.n0, stored_remotely = true;
                 }
                 const bool written = row < t.rows_written;
+                float* out32 = reinterpret_cast<float*>(a.d) + size_t(t.row_base + t.m0 + row) * a.n_out + t.n0;
                 for (int c = 0; c < BN; c += 32) {
                     uint32_t r[32];
                     tc::tmem_ld_32x32(taddr + c, r);
                     tc::wait_ld();
                     if (not written) continue;
+                    if (a.out_fp32) {
+                        // fp32 result (router logits): the accumulator is stored as it is
+                        #pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            *reinterpret_cast<uint4*>(out32 + c + 4 * v) =
+                                valid ? make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]) : make_uint4(0, 0, 0, 0);
+                        continue;
+                    }
                     #pragma unroll
                     for (int v = 0; v < 4; ++v) {
                         int4 packed;

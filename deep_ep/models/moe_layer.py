@@ -126,7 +126,13 @@ class MoELayer(nn.Module):
         self.buffer = None
 
     def route(self, x: torch.Tensor):
-        logits = F.linear(x.float(), self.gate)
+        """Top-k routing of `x`. The logits are an fp32-accumulated product of the bf16 activations with the gate matrix
+        rounded to bf16 (the fp32 parameter stays the master copy), computed by the layer's own tensor-core kernel."""
+        from ..ops.dense import dense_linear
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            logits = dense_linear(x, self.gate.to(torch.bfloat16), out_fp32=True)
+        else:
+            logits = F.linear(x.float(), self.gate)
         scores = torch.softmax(logits, dim=-1)
         topk_weights, topk_idx = scores.topk(self.config.num_topk, dim=-1)
         topk_weights = topk_weights / topk_weights.sum(dim=-1, keepdim=True)
@@ -188,13 +194,12 @@ class MoELayer(nn.Module):
                                    alignment=cfg.expert_alignment, row_scale=recv_w, route=route)
         out, _, _ = self.buffer.combine(y, handle, fused_single_rows=route is not None)
         if cfg.num_shared_experts > 0:
-            g, u = F.linear(x, self.shared_gate_up).chunk(2, dim=-1)
-            out = out + F.linear(F.silu(g) * u, self.shared_down)
+            out = out + self._shared_expert(x)
         return out
 
     def _shared_expert(self, x: torch.Tensor) -> torch.Tensor:
-        g, u = F.linear(x, self.shared_gate_up).chunk(2, dim=-1)
-        return F.linear(F.silu(g) * u, self.shared_down)
+        from ..ops.dense import dense_swiglu_ffn
+        return dense_swiglu_ffn(x, self.shared_gate_up, self.shared_down)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shared = None
@@ -205,7 +210,7 @@ class MoELayer(nn.Module):
             self._side_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self._side_stream):
                 shared = self._shared_expert(x)
-        topk_idx, topk_weights = self.route(x.detach())
+        topk_idx, topk_weights = self.route(x)
         recv_x, recv_w = _Dispatch.apply(x, topk_idx, topk_weights.float().contiguous(), self)
         handle = self._handle
         route = None

@@ -134,6 +134,12 @@ def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, dw: torch.Tensor, psum
     return dw
 
 
+def _zero_padding_rows(t: torch.Tensor, psum: torch.Tensor, count: torch.Tensor, alignment: int) -> torch.Tensor:
+    """`t` with the alignment padding rows forced to zero when the tensor-core weight gradient is going to read them
+    (an upstream gradient may hold anything there, and NaN x 0 is NaN)."""
+    return mask_padding_rows(t, psum, count) if alignment % 64 == 0 else t
+
+
 def _ranges(psum: torch.Tensor, count: torch.Tensor):
     return [(e - c, c) for e, c in zip(psum.tolist(), count.tolist())]
 
@@ -151,14 +157,17 @@ class GroupedLinear(torch.autograd.Function):
     def forward(ctx, x, w, psum, count, alignment):
         ctx.save_for_backward(x, w, psum, count)
         ctx.alignment = alignment
-        return grouped_gemm_forward(x, w, psum, count)
+        # the alignment reaches the kernels so that the padding rows of every expert's region are written as zeros: the
+        # tensor-core weight-gradient GEMM reads whole 64-row blocks, padding included
+        return grouped_gemm_forward(x, w, psum, count, alignment=alignment)
 
     @staticmethod
     def backward(ctx, dy):
         x, w, psum, count = ctx.saved_tensors
         dy = dy.contiguous()
-        dx = grouped_gemm_dgrad(dy, w, psum, count) if ctx.needs_input_grad[0] else None
-        dw = _wgrad(dy, x, w, psum, count, ctx.alignment) if ctx.needs_input_grad[1] else None
+        dx = grouped_gemm_dgrad(dy, w, psum, count, alignment=ctx.alignment) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(_zero_padding_rows(dy, psum, count, ctx.alignment), x, w, psum, count, ctx.alignment) \
+            if ctx.needs_input_grad[1] else None
         return dx, dw, None, None, None
 
 

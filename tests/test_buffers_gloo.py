@@ -77,8 +77,21 @@ def _bucket_worker(rank, world):
         keep = torch.ones(t.numel(), dtype=torch.bool)
         keep[rank * m:(rank + 1) * m] = False
         assert torch.equal(t[keep], mine[keep])
-        with pytest.raises(AssertionError):
-            bucket.all_reduce(torch.zeros(world * 16), group=group)      # not registered
+        # inside a session tensors outside the storage are staged: all-reduce stays in place for the caller,
+        # reduce-scatter hands back the reduced shard
+        user = mine.clone()
+        out = bucket.all_reduce(user, scale=0.5, group=group).wait()
+        assert out is user and torch.equal(user, (expect * 0.5).to(torch.bfloat16))
+        user2, user3 = mine.clone(), mine.clone().float()
+        expect3 = torch.zeros(t.numel())
+        for r in range(world):
+            expect3 += (torch.arange(t.numel()).float() * 0.01 + r).to(torch.bfloat16).float()
+        shards = bucket.reduce_scatter([user2, user3], group=group).wait()
+        assert torch.equal(shards[0], expect.to(torch.bfloat16)[rank * m:(rank + 1) * m])
+        assert torch.equal(shards[1], expect3[rank * m:(rank + 1) * m])
+        assert torch.equal(user2, mine)                                  # the caller's tensor is only read
+    with pytest.raises((AssertionError, deep_ep.EPException)):
+        bucket.all_reduce(torch.zeros(world * 16), group=group)          # outside a session: not registered
     bucket.destroy()
 
 

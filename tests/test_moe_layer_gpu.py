@@ -8,11 +8,13 @@ import torch
 from dist_utils import run_distributed
 
 
-def _dense_reference(x, gate, w_gate_up, w_down, num_topk):
+def _dense_reference(x, gate, w_gate_up, w_down, num_topk, bf16_gate=True):
     """fp32 MoE FFN with every expert available locally: `sum_k weight_k * FFN_{expert_k}(x)`."""
     import torch.nn.functional as F
-    # routing reads a detached copy of x: the gate matrix receives a gradient (through the routing weights), x does not
-    scores = torch.softmax(F.linear(x.detach().float(), gate.float()), dim=-1)
+    # on a GPU the layer multiplies the bf16 activations by the gate matrix rounded to bf16 (fp32 accumulation), on CPU
+    # ranks by the fp32 matrix; the router is part of the graph, so both the gate matrix and x receive a gradient
+    # through the routing weights
+    scores = torch.softmax(F.linear(x.float(), gate.to(torch.bfloat16).float() if bf16_gate else gate.float()), dim=-1)
     topk_w, topk_idx = scores.topk(num_topk, dim=-1)
     topk_w = topk_w / topk_w.sum(dim=-1, keepdim=True)
     out = torch.zeros_like(x, dtype=torch.float32)
