@@ -5,6 +5,8 @@
 
 #include <cuda_runtime.h>
 
+#include <functional>
+
 #include <deep_ep/kernels/ep_args.hpp>
 #include <deep_ep/kernels/ep_layout_args.hpp>
 #include <deep_ep/kernels/grouped_gemm_args.hpp>
@@ -22,6 +24,15 @@ struct PipelineConfig {
 PipelineConfig choose_dispatch_config(int token_bytes, int src_row_bytes, int num_topk, int num_experts);
 PipelineConfig choose_expand_config(int token_bytes, int num_topk, int num_local_experts);
 PipelineConfig choose_combine_config(int token_bytes);
+
+// Shape-specialised variants of the four EP kernels (optional): when a provider is installed and returns a driver function
+// (`CUfunction`, passed as `void*`) for a kernel name ("dispatch", "expand", "combine", "reduce") and shape, the launchers
+// below start that function instead of the generic kernel linked into this library; the argument block is the same.
+struct EPShape {
+    int num_ranks, num_topk, hidden_bytes, num_experts;
+};
+using SpecializedKernelProvider = std::function<void*(const char* kernel, const EPShape& shape)>;
+void set_specialized_kernel_provider(SpecializedKernelProvider provider);
 
 void dispatch(kernels::DispatchArgs args, int num_sms, cudaStream_t stream);
 void dispatch_expand(kernels::ExpandArgs args, int num_sms, cudaStream_t stream);

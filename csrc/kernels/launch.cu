@@ -12,11 +12,39 @@
 #include <deep_ep/kernels/ep_route.cuh>
 #include <deep_ep/kernels/misc.cuh>
 
+#include "../runtime/driver.hpp"
 #include "api.hpp"
 
 namespace deep_ep::launch {
 
 namespace {
+
+SpecializedKernelProvider& specialized_provider() {
+    static SpecializedKernelProvider provider;
+    return provider;
+}
+
+// Launch of a run-time compiled kernel that takes the same by-value argument block as its generic counterpart.
+template <typename Args>
+void launch_function(void* function, const Args& args, int grid, int block, int64_t smem, bool cooperative, cudaStream_t stream) {
+    const auto fn = static_cast<CUfunction>(function);
+    if (smem > 48 * 1024)
+        DRV_CHECK(driver::cuFuncSetAttribute()(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, static_cast<int>(smem)));
+    CUlaunchConfig config = {};
+    config.gridDimX = grid, config.gridDimY = 1, config.gridDimZ = 1;
+    config.blockDimX = block, config.blockDimY = 1, config.blockDimZ = 1;
+    config.sharedMemBytes = static_cast<unsigned>(smem), config.hStream = stream;
+    CUlaunchAttribute attr[1];
+    attr[0].id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE, attr[0].value.cooperative = cooperative ? 1 : 0;
+    config.attrs = attr, config.numAttrs = 1;
+    void* params[1] = {const_cast<Args*>(&args)};
+    DRV_CHECK(driver::cuLaunchKernelEx()(&config, fn, params, nullptr));
+}
+
+// The generic kernel, or its shape-specialised variant when a provider offers one.
+template <typename Kernel, typename Args>
+void launch_ep_kernel(const char* name, const EPShape& shape, Kernel kernel, const Args& args, int grid, int block, int64_t smem,
+                      bool cooperative, cudaStream_t stream);
 
 constexpr int64_t kSmemBudget = 200 * 1024;   // of the 227 KiB a CTA may opt into
 
@@ -34,6 +62,14 @@ void launch_kernel(Kernel kernel, const Args& args, int grid, int block, int64_t
     CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, args));
 }
 
+template <typename Kernel, typename Args>
+void launch_ep_kernel(const char* name, const EPShape& shape, Kernel kernel, const Args& args, int grid, int block, int64_t smem,
+                      bool cooperative, cudaStream_t stream) {
+    void* function = specialized_provider() ? specialized_provider()(name, shape) : nullptr;
+    if (function != nullptr) launch_function(function, args, grid, block, smem, cooperative, stream);
+    else launch_kernel(kernel, args, grid, block, smem, cooperative, stream);
+}
+
 int clamp_sms(int num_sms) {
     int device = 0, count = 0;
     CUDA_CHECK(cudaGetDevice(&device));
@@ -42,6 +78,8 @@ int clamp_sms(int num_sms) {
 }
 
 }  // namespace
+
+void set_specialized_kernel_provider(SpecializedKernelProvider provider) { specialized_provider() = std::move(provider); }
 
 PipelineConfig choose_dispatch_config(int token_bytes, int src_row_bytes, int num_topk, int num_experts) {
     for (int stages : {3, 2}) {
@@ -79,24 +117,24 @@ void dispatch(kernels::DispatchArgs args, int num_sms, cudaStream_t stream) {
     const auto config = choose_dispatch_config(tl.num_bytes(), args.fused_quant ? args.hidden_bytes * 2 : 0,
                                                args.num_topk, args.num_experts);
     args.num_warps = config.num_warps, args.num_stages = config.num_stages;
-    launch_kernel(kernels::ep_dispatch_kernel, args, clamp_sms(num_sms), 32 * (config.num_warps + 1),
-                  config.smem_bytes, true, stream);
+    launch_ep_kernel("dispatch", {args.peers.num_ranks, args.num_topk, args.hidden_bytes, args.num_experts}, kernels::ep_dispatch_kernel,
+                     args, clamp_sms(num_sms), 32 * (config.num_warps + 1), config.smem_bytes, true, stream);
 }
 
 void dispatch_expand(kernels::ExpandArgs args, int num_sms, cudaStream_t stream) {
     const layout::DispatchTokenLayout tl(args.hidden_bytes, args.sf_bytes, args.num_topk);
     const auto config = choose_expand_config(tl.num_bytes(), args.num_topk, args.num_experts / args.num_ranks);
     args.num_warps = config.num_warps, args.num_stages = config.num_stages;
-    launch_kernel(kernels::ep_dispatch_expand_kernel, args, clamp_sms(num_sms), 32 * config.num_warps,
-                  config.smem_bytes, true, stream);
+    launch_ep_kernel("expand", {args.num_ranks, args.num_topk, args.hidden_bytes, args.num_experts}, kernels::ep_dispatch_expand_kernel,
+                     args, clamp_sms(num_sms), 32 * config.num_warps, config.smem_bytes, true, stream);
 }
 
 void combine(kernels::CombineArgs args, int num_sms, cudaStream_t stream) {
     const layout::CombineTokenLayout tl(args.hidden_bytes, args.num_topk);
     const auto config = choose_combine_config(tl.num_bytes());
     args.num_warps = config.num_warps, args.num_stages = config.num_stages;
-    launch_kernel(kernels::ep_combine_kernel, args, clamp_sms(num_sms), 32 * config.num_warps,
-                  config.smem_bytes, true, stream);
+    launch_ep_kernel("combine", {args.peers.num_ranks, args.num_topk, args.hidden_bytes, 0}, kernels::ep_combine_kernel,
+                     args, clamp_sms(num_sms), 32 * config.num_warps, config.smem_bytes, true, stream);
 }
 
 void combine_route(const kernels::CombineRouteArgs& args, cudaStream_t stream) {
@@ -106,7 +144,8 @@ void combine_route(const kernels::CombineRouteArgs& args, cudaStream_t stream) {
 
 void combine_reduce(kernels::CombineReduceArgs args, int num_sms, cudaStream_t stream) {
     // not cooperative: oversubscribe the SMs so that enough loads are in flight
-    launch_kernel(kernels::ep_combine_reduce_kernel, args, clamp_sms(num_sms) * 4, 256, 0, false, stream);
+    launch_ep_kernel("reduce", {args.num_ranks, args.num_topk, args.hidden_bytes, args.num_experts}, kernels::ep_combine_reduce_kernel,
+                     args, clamp_sms(num_sms) * 4, 256, 0, false, stream);
 }
 
 namespace {

@@ -19,8 +19,12 @@ using deep_ep::kernels::LayoutScratch;
 // name is only a handle for the runtime; the device address is obtained once per device below.
 static __device__ __align__(256) unsigned char g_layout_scratch[sizeof(LayoutScratch)];
 
+// How the most recent launch on this device ended (0, or the code of a device-side wait that ran out); same lifetime.
+static __device__ int g_layout_status;
+
 constexpr int kMaxDevices = 64;
 LayoutScratch* g_scratch_address[kMaxDevices] = {};
+int* g_status_address[kMaxDevices] = {};
 std::mutex g_setup_mutex;
 thread_local std::string g_last_error;
 
@@ -33,8 +37,8 @@ int fail(int code, const std::string& what) {
     return code;
 }
 
-// Device address of the scratch array on the current device; looked up on the first call per device.
-int scratch_for_current_device(LayoutScratch** out) {
+// Device addresses of the scratch array and of the status word on the current device; looked up on the first call per device.
+int scratch_for_current_device(LayoutScratch** out, int** status_out) {
     int device = 0;
     cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess) return fail(DEEP_EP_NOALLOC_CUDA_ERROR, std::string("cudaGetDevice: ") + cudaGetErrorString(err));
@@ -45,9 +49,15 @@ int scratch_for_current_device(LayoutScratch** out) {
         err = cudaGetSymbolAddress(&address, g_layout_scratch);
         if (err != cudaSuccess or address == nullptr)
             return fail(DEEP_EP_NOALLOC_CUDA_ERROR, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(err));
+        void* status_address = nullptr;
+        err = cudaGetSymbolAddress(&status_address, g_layout_status);
+        if (err != cudaSuccess or status_address == nullptr)
+            return fail(DEEP_EP_NOALLOC_CUDA_ERROR, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(err));
+        g_status_address[device] = static_cast<int*>(status_address);
         g_scratch_address[device] = static_cast<LayoutScratch*>(address);
     }
     *out = g_scratch_address[device];
+    *status_out = g_status_address[device];
     return DEEP_EP_NOALLOC_OK;
 }
 
@@ -70,11 +80,13 @@ int deep_ep_dispatch_layout_noalloc(const long long* topk_idx, int num_tokens, i
         return fail(DEEP_EP_NOALLOC_BAD_ARGUMENT, "num_experts must be in [1, 2048] and a multiple of num_ranks");
 
     LayoutScratch* scratch = nullptr;
-    if (const int rc = scratch_for_current_device(&scratch); rc != DEEP_EP_NOALLOC_OK) return rc;
+    int* device_status = nullptr;
+    if (const int rc = scratch_for_current_device(&scratch, &device_status); rc != DEEP_EP_NOALLOC_OK) return rc;
     const auto stream = static_cast<cudaStream_t>(stream_handle);
 
-    // every call starts from a clean scratch block, whatever the previous call left behind
+    // every call starts from a clean scratch block and a clean status word, whatever the previous call left behind
     cudaError_t err = cudaMemsetAsync(scratch, 0, sizeof(LayoutScratch), stream);
+    if (err == cudaSuccess) err = cudaMemsetAsync(device_status, 0, sizeof(int), stream);
     if (err != cudaSuccess) return fail(DEEP_EP_NOALLOC_CUDA_ERROR, std::string("cudaMemsetAsync: ") + cudaGetErrorString(err));
 
     LayoutArgs args = {};
@@ -82,7 +94,7 @@ int deep_ep_dispatch_layout_noalloc(const long long* topk_idx, int num_tokens, i
     args.num_tokens = num_tokens, args.num_topk = num_topk, args.num_experts = num_experts, args.num_ranks = num_ranks;
     args.dst_slot_idx = dst_slot_idx, args.num_tokens_per_rank = num_tokens_per_rank;
     args.num_tokens_per_expert = num_tokens_per_expert;
-    args.scratch = scratch, args.timeout_ns = 10ll * 1000000000ll, args.status = nullptr;
+    args.scratch = scratch, args.timeout_ns = 10ll * 1000000000ll, args.status = device_status;
 
     int grid = (num_tokens + 255) / 256;
     grid = grid < 1 ? 1 : (grid > deep_ep::kernels::kLayoutMaxCtas ? deep_ep::kernels::kLayoutMaxCtas : grid);
@@ -93,6 +105,23 @@ int deep_ep_dispatch_layout_noalloc(const long long* topk_idx, int num_tokens, i
     config.attrs = attr, config.numAttrs = 1;
     err = cudaLaunchKernelEx(&config, ep_layout_noalloc_kernel, args);
     if (err != cudaSuccess) return fail(DEEP_EP_NOALLOC_CUDA_ERROR, std::string("kernel launch: ") + cudaGetErrorString(err));
+    return DEEP_EP_NOALLOC_OK;
+}
+
+extern "C" __attribute__((visibility("default")))
+int deep_ep_noalloc_wait_status(void* stream_handle, int* device_status_out) {
+    g_last_error.clear();
+    if (device_status_out == nullptr) return fail(DEEP_EP_NOALLOC_BAD_ARGUMENT, "null pointer argument");
+    LayoutScratch* scratch = nullptr;
+    int* device_status = nullptr;
+    if (const int rc = scratch_for_current_device(&scratch, &device_status); rc != DEEP_EP_NOALLOC_OK) return rc;
+    const auto stream = static_cast<cudaStream_t>(stream_handle);
+    cudaError_t err = cudaMemcpyAsync(device_status_out, device_status, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+    if (err != cudaSuccess) return fail(DEEP_EP_NOALLOC_CUDA_ERROR, std::string("reading the status word: ") + cudaGetErrorString(err));
+    if (*device_status_out != 0)
+        g_last_error = "the layout kernel gave up waiting for its own thread blocks (device status " +
+                       std::to_string(*device_status_out) + "); its outputs are incomplete";
     return DEEP_EP_NOALLOC_OK;
 }
 

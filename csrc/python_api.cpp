@@ -12,6 +12,7 @@
 #include "comm/stream.hpp"
 #include "runtime/device.hpp"
 #include "runtime/jit.hpp"
+#include "runtime/specialize.hpp"
 #include "utils/event.hpp"
 
 namespace py = pybind11;
@@ -287,6 +288,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("get_npu_arch", [] { return Runtime::get().get_arch(); });
     m.def("set_npu_arch", [](const std::string& a) { Runtime::get().set_arch(a); });
     jit::register_python_api(m);
+    jit::register_specialization_api(m);
     // Host-only self-test of the descriptor exchange used by the virtual-memory-management route: a pipe's two ends travel
     // through `FdServer` / `receive_fds` inside this process and must still be connected to each other afterwards.
     m.def("fd_exchange_selftest", [] {

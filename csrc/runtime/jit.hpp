@@ -19,13 +19,19 @@
 #include <map>
 #include <mutex>
 #include <sstream>
+#include <fcntl.h>
+#include <spawn.h>
+#include <sys/wait.h>
 #include <unistd.h>
+#include <cerrno>
 #include <string>
 #include <vector>
 
 #include <deep_ep/common/exception.hpp>
 
 #include "driver.hpp"
+
+extern char** environ;
 
 namespace deep_ep::jit {
 
@@ -45,6 +51,26 @@ inline bool get_env_flag(const std::string& name) {
 inline uint64_t fnv1a(const std::string& s, uint64_t h = 1469598103934665603ull) {
     for (const unsigned char c : s) h = (h ^ c) * 1099511628211ull;
     return h;
+}
+
+// Runs `argv` (argv[0] = program path, looked up in PATH when it has no slash) as a child process, standard output and
+// error appended to `log_path`; returns the exit code, or -1 when the process could not be started or was killed.
+inline int run_process(const std::vector<std::string>& argv_text, const std::string& log_path) {
+    std::vector<char*> argv;
+    for (const auto& word : argv_text) argv.push_back(const_cast<char*>(word.c_str()));
+    argv.push_back(nullptr);
+    posix_spawn_file_actions_t actions;
+    posix_spawn_file_actions_init(&actions);
+    posix_spawn_file_actions_addopen(&actions, 1, log_path.c_str(), O_WRONLY | O_CREAT | O_TRUNC, 0644);
+    posix_spawn_file_actions_adddup2(&actions, 1, 2);
+    pid_t pid = 0;
+    const int err = posix_spawnp(&pid, argv[0], &actions, nullptr, argv.data(), environ);
+    posix_spawn_file_actions_destroy(&actions);
+    if (err != 0) return -1;
+    int status = 0;
+    while (waitpid(pid, &status, 0) < 0)
+        if (errno != EINTR) return -1;
+    return WIFEXITED(status) ? WEXITSTATUS(status) : -1;
 }
 
 class Compiler {
@@ -95,9 +121,9 @@ public:
         std::string flags = "-std=c++20 -O3 --expt-relaxed-constexpr -cubin";
         if (get_env_flag("KERNEL_DEBUG_INFO")) flags += " -lineinfo";
         const std::string arch_num = arch.substr(3);
-        flags += " -gencode arch=compute_" + arch_num + ",code=" + arch + " -I" + include_dir();
+        flags += " -gencode arch=compute_" + arch_num + ",code=" + arch;
         std::ostringstream key;
-        key << std::hex << fnv1a(source, fnv1a(flags));
+        key << std::hex << fnv1a(source, fnv1a(flags + " -I" + include_dir()));
         const auto roots = cache_roots();
         const auto entry = name + "-" + key.str();
         for (const auto& root : roots) {
@@ -113,14 +139,28 @@ public:
             out << source;
         }
         const auto tmp = cubin + ".tmp." + std::to_string(::getpid());
-        const auto command = nvcc_path() + " " + flags + " " + dir + "/kernel.cu -o " + tmp + " > " + dir + "/nvcc.log 2>&1";
-        if (get_env_flag("PRINT_COMPILER_COMMAND") or get_env_flag("DEBUG")) std::fprintf(stderr, "[deep_ep jit] %s\n", command.c_str());
-        const int rc = std::system(command.c_str());
+        // the compiler runs as a child process with an argument vector (no shell: paths from the environment may hold
+        // spaces or shell metacharacters), its output goes to `nvcc.log`
+        std::vector<std::string> argv_text = {nvcc_path()};
+        {
+            std::stringstream words(flags);
+            for (std::string word; words >> word;) argv_text.push_back(word);
+        }
+        argv_text.push_back("-I" + include_dir());
+        argv_text.push_back(dir + "/kernel.cu");
+        argv_text.push_back("-o");
+        argv_text.push_back(tmp);
+        if (get_env_flag("PRINT_COMPILER_COMMAND") or get_env_flag("DEBUG")) {
+            std::string line;
+            for (const auto& word : argv_text) line += word + " ";
+            std::fprintf(stderr, "[deep_ep jit] %s\n", line.c_str());
+        }
+        const int rc = run_process(argv_text, dir + "/nvcc.log");
         if (rc != 0) {
             std::ifstream log(dir + "/nvcc.log");
             std::stringstream text;
             text << log.rdbuf();
-            throw EPException("JIT compile", __FILE__, __LINE__, name + ": nvcc failed\n" + text.str());
+            throw EPException("JIT compile", __FILE__, __LINE__, name + ": nvcc failed (" + std::to_string(rc) + ")\n" + text.str());
         }
         std::filesystem::rename(tmp, cubin);     // atomic publish: concurrent ranks may race on the same key
         return cubin;

@@ -424,12 +424,14 @@ class EPBuffer(BufferBase):
         `expert_weights[i]` is `[num_local_experts, *shape]`, `redundancy_mapping [num_ranks, num_redundant]`
         int32 holds the global expert id wanted in each slot (-1 = empty) and is identical on all ranks.
         """
-        from ..ops.lb import lb_prefetch_weights
-        return lb_prefetch_weights(self, redundant_expert_weights, expert_weights, redundancy_mapping, num_sms, previous_event)
+        as_list = lambda t: [t] if isinstance(t, torch.Tensor) else list(t)
+        redundant, local = as_list(redundant_expert_weights), as_list(expert_weights)
+        assert redundant and len(redundant) == len(local) and all(t is not None for t in redundant + local)
+        return EventOverlap(self.runtime.lb_prefetch_weights(redundant, local, redundancy_mapping, num_sms, previous_event))
 
     def lb_reduce_grads(self, redundant_expert_grads: torch.Tensor, expert_grads: torch.Tensor,
                         redundancy_mapping: torch.Tensor, num_sms: int = 0,
                         previous_event: Optional[EventHandle] = None) -> EventOverlap:
         """Add the gradients of redundant expert copies held by peers into this rank's `expert_grads` (collective)."""
-        from ..ops.lb import lb_reduce_grads
-        return lb_reduce_grads(self, redundant_expert_grads, expert_grads, redundancy_mapping, num_sms, previous_event)
+        return EventOverlap(self.runtime.lb_reduce_grads(redundant_expert_grads, expert_grads, redundancy_mapping, num_sms,
+                                                         previous_event))

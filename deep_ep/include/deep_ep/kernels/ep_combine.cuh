@@ -175,18 +175,22 @@ EP_DEVICE void reduce_token(const uint8_t* const (&part)[kParts], const uint8_t*
 
 }  // namespace combine_detail
 
-__global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_constant__ CombineArgs a) {
+// Kernel body; non-zero template arguments replace the corresponding run-time shape values by compile-time constants
+// (see `ep_dispatch_body`): zeros for the ahead-of-time kernel below, the shapes in use for run-time specialised kernels.
+template <int kNumRanks, int kNumTopk, int kHiddenBytes>
+EP_DEVICE void ep_combine_body(const CombineArgs& a) {
     using namespace combine_detail;
     extern __shared__ uint8_t smem_raw[];
     __shared__ int psum_rank_smem[kMaxRanks];
 
-    const int num_ranks = a.peers.num_ranks, rank = a.peers.rank;
+    const int num_ranks = kNumRanks > 0 ? kNumRanks : a.peers.num_ranks, rank = a.peers.rank;
+    const int hidden_bytes = kHiddenBytes > 0 ? kHiddenBytes : a.hidden_bytes;
     const int num_ctas = gridDim.x, cta = blockIdx.x;
     const int warp = threadIdx.x / 32, lane = ptx::lane_id();
-    const int W = a.num_warps, S = a.num_stages, k = a.num_topk;
+    const int W = a.num_warps, S = a.num_stages, k = kNumTopk > 0 ? kNumTopk : a.num_topk;
     layout::CommonSignals* cs = &a.ws->common;
     layout::HostStatus* hs = a.host ? &a.host->status : nullptr;
-    const layout::CombineTokenLayout tl(a.hidden_bytes, k);
+    const layout::CombineTokenLayout tl(hidden_bytes, k);
     const int token_bytes = tl.num_bytes();
     const int num_groups = min(k, num_ranks);
     const layout::BufferLayout bl(token_bytes, num_groups, a.num_max_tokens);
@@ -214,7 +218,7 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
 
     const int gw = cta * W + warp, num_gw = num_ctas * W;
     const int meta_cols = k + 2;
-    const int chunks = a.hidden_bytes / 16;
+    const int chunks = hidden_bytes / 16;
     int n = 0;            // rows processed by this warp (stage / parity counter)
     int num_loads[4] = {0, 0, 0, 0};   // bulk loads issued per stage (mbarrier parity)
     bool failed = false;
@@ -278,10 +282,10 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
                 if (part == 0) dispatch_detail::wait_read_pending(S - 1);     // the store issued S rows ago has read the stage
                 ptx::named_barrier(bar_id, bar_threads);
                 if (a.weighted and a.topk_weights != nullptr)
-                    reduce_rows_weighted(a.x, a.hidden_bytes, c_begin, c_end, my_slot, my_slot >= 0 ? a.topk_weights[my_slot] : 0.f,
+                    reduce_rows_weighted(a.x, hidden_bytes, c_begin, c_end, my_slot, my_slot >= 0 ? a.topk_weights[my_slot] : 0.f,
                                          valid, count, stage, lane);
                 else
-                    reduce_rows(a.x, a.hidden_bytes, c_begin, c_end, my_slot, valid, count, stage, lane);
+                    reduce_rows(a.x, hidden_bytes, c_begin, c_end, my_slot, valid, count, stage, lane);
                 if (part == 0 and lane < k)
                     reinterpret_cast<float*>(stage + tl.weight_offset())[lane] =
                         (my_slot >= 0 and a.topk_weights != nullptr) ? a.topk_weights[my_slot] : 0.f;
@@ -348,14 +352,14 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
             if (single_copy) {
                 const int slot = __shfl_sync(0xffffffffu, my_slot, __ffs(valid) - 1);
                 if (lane == 0) {
-                    ptx::mbarrier_arrive_expect_tx(&mbar[stage_idx], a.hidden_bytes);
-                    ptx::bulk_load(stage, a.x + int64_t(slot) * a.hidden_bytes, a.hidden_bytes, &mbar[stage_idx]);
+                    ptx::mbarrier_arrive_expect_tx(&mbar[stage_idx], hidden_bytes);
+                    ptx::bulk_load(stage, a.x + int64_t(slot) * hidden_bytes, hidden_bytes, &mbar[stage_idx]);
                 }
             } else if (weighted) {
-                reduce_rows_weighted(a.x, a.hidden_bytes, 0, chunks, my_slot, my_slot >= 0 ? a.topk_weights[my_slot] : 0.f, valid,
+                reduce_rows_weighted(a.x, hidden_bytes, 0, chunks, my_slot, my_slot >= 0 ? a.topk_weights[my_slot] : 0.f, valid,
                                      count, stage, lane);
             } else {
-                reduce_rows(a.x, a.hidden_bytes, 0, chunks, my_slot, valid, count, stage, lane);
+                reduce_rows(a.x, hidden_bytes, 0, chunks, my_slot, valid, count, stage, lane);
             }
             if (lane < k)
                 reinterpret_cast<float*>(stage + tl.weight_offset())[lane] =
@@ -411,17 +415,27 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
     }
 }
 
-__global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_constant__ CombineReduceArgs a) {
+__global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_constant__ CombineArgs a) {
+    ep_combine_body<0, 0, 0>(a);
+}
+
+// Kernel body; non-zero template arguments replace the corresponding run-time shape values by compile-time constants
+// (see `ep_dispatch_body`): zeros for the ahead-of-time kernel below, the shapes in use for run-time specialised kernels.
+template <int kNumRanks, int kNumTopk, int kHiddenBytes, int kNumExperts>
+EP_DEVICE void ep_combine_reduce_body(const CombineReduceArgs& a) {
     using namespace combine_detail;
-    const int num_local_experts = a.num_experts / a.num_ranks;
+    const int num_ranks = kNumRanks > 0 ? kNumRanks : a.num_ranks;
+    const int num_experts = kNumExperts > 0 ? kNumExperts : a.num_experts;
+    const int hidden_bytes = kHiddenBytes > 0 ? kHiddenBytes : a.hidden_bytes;
+    const int num_local_experts = num_experts / num_ranks;
     const int warps_per_cta = blockDim.x / 32;
     const int warp = threadIdx.x / 32, lane = ptx::lane_id();
-    const int k = a.num_topk;
+    const int k = kNumTopk > 0 ? kNumTopk : a.num_topk;
     layout::CommonSignals* cs = &a.ws->common;
     layout::HostStatus* hs = a.host ? &a.host->status : nullptr;
-    const layout::CombineTokenLayout tl(a.hidden_bytes, k);
+    const layout::CombineTokenLayout tl(hidden_bytes, k);
     const int token_bytes = tl.num_bytes();
-    const layout::BufferLayout bl(token_bytes, min(k, a.num_ranks), a.num_max_tokens);
+    const layout::BufferLayout bl(token_bytes, min(k, num_ranks), a.num_max_tokens);
 
     if (not dev::healthy(cs)) return;
     const unsigned epoch = a.ws->combine_epoch;
@@ -429,7 +443,7 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
     if (tracer) dev::trace_point(a.trace, kTrRedStart);
     if (a.wait_arrival and warp == 0) {
         const dev::Deadline deadline(a.timeout_ns);
-        for (int s = lane; s < a.num_ranks; s += 32) {
+        for (int s = lane; s < num_ranks; s += 32) {
             unsigned long long w = 0;
             if (not dev::spin_until(deadline, [&]() { return (w = ptx::ld_acquire_sys(&a.ws->combine_done[s])) == epoch; }))
                 dev::report_status(cs, hs, kStatusArrivalTimeout, a.rank, s, kSiteArrival, epoch, w);
@@ -439,7 +453,7 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
     if (not dev::healthy(cs)) return;
     if (tracer) dev::trace_point(a.trace, kTrRedArrived);
 
-    const int chunks = a.hidden_bytes / 16;
+    const int chunks = hidden_bytes / 16;
     // With `coop` and fewer tokens than warps, P consecutive warps share a token (1 / P of the chunks each).
     const int total_warps = gridDim.x * warps_per_cta;
     int P = 1;
@@ -452,7 +466,7 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
         int r = -1;
         if (lane < k) {
             const int64_t e = a.topk_idx[int64_t(t) * k + lane];
-            if (e >= 0 and e < a.num_experts) r = int(e) / num_local_experts;
+            if (e >= 0 and e < num_experts) r = int(e) / num_local_experts;
         }
         // master position of a rank = last top-k position that selects it
         bool is_master = r >= 0;
@@ -460,7 +474,7 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
             const int other = __shfl_down_sync(0xffffffffu, r, d);
             if (lane + d < k and other == r) is_master = false;
         }
-        const int group = a.num_ranks >= k ? lane : r;
+        const int group = num_ranks >= k ? lane : r;
         const unsigned masters = __ballot_sync(0xffffffffu, is_master);
         const int count = __popc(masters);
 
@@ -470,9 +484,9 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
             const int g = __shfl_sync(0xffffffffu, group, u < count ? nth_set_bit(masters, u) : 0);
             part[u] = u < count ? a.buffer + bl.offset(g, t) : nullptr;
         }
-        const uint8_t* b0 = a.bias_0 != nullptr ? a.bias_0 + int64_t(t) * a.hidden_bytes : nullptr;
-        const uint8_t* b1 = a.bias_1 != nullptr ? a.bias_1 + int64_t(t) * a.hidden_bytes : nullptr;
-        uint8_t* out = a.combined_x + int64_t(t) * a.hidden_bytes;
+        const uint8_t* b0 = a.bias_0 != nullptr ? a.bias_0 + int64_t(t) * hidden_bytes : nullptr;
+        const uint8_t* b1 = a.bias_1 != nullptr ? a.bias_1 + int64_t(t) * hidden_bytes : nullptr;
+        uint8_t* out = a.combined_x + int64_t(t) * hidden_bytes;
         if (count <= 4) {
             const uint8_t* p4[4] = {part[0], part[1], part[2], part[3]};
             reduce_token<4, 4>(p4, b0, b1, out, c_begin, c_end, lane);
@@ -510,6 +524,10 @@ __global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_
     // CTA 0's share is done (the other CTAs work on as many tokens each, give or take one)
     __syncthreads();
     if (tracer) dev::trace_point(a.trace, kTrRedEnd);
+}
+
+__global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_constant__ CombineReduceArgs a) {
+    ep_combine_reduce_body<0, 0, 0, 0>(a);
 }
 
 }  // namespace deep_ep::kernels

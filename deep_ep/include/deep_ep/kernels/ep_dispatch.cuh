@@ -110,24 +110,32 @@ EP_DEVICE void quantize_row(const uint8_t* src, uint8_t* dst_fp8, float* dst_sf,
 
 }  // namespace dispatch_detail
 
-__global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
+// Kernel body. Non-zero template arguments replace the corresponding run-time values (`a.peers.num_ranks`, `a.num_topk`,
+// `a.hidden_bytes`, `a.num_experts`) by compile-time constants: the ahead-of-time kernel below passes zeros, kernels
+// specialised at run time for the shapes in use (`csrc/runtime/specialize.hpp`) pass the shapes, which unrolls the top-k
+// and per-rank loops and folds the message layout into constants (the reference instantiates its kernels the same way,
+// `csrc/kernels/ep/dispatch.hpp:52-81`). The host guarantees that the arguments match the constants.
+template <int kNumRanks, int kNumTopk, int kHiddenBytes, int kNumExperts>
+EP_DEVICE void ep_dispatch_body(const DispatchArgs& a) {
     using namespace dispatch_detail;
     extern __shared__ uint8_t smem_raw[];
 
-    const int num_ranks = a.peers.num_ranks, rank = a.peers.rank;
-    const int num_local_experts = a.num_experts / num_ranks;
+    const int num_ranks = kNumRanks > 0 ? kNumRanks : a.peers.num_ranks, rank = a.peers.rank;
+    const int num_experts = kNumExperts > 0 ? kNumExperts : a.num_experts;
+    const int num_local_experts = num_experts / num_ranks;
     const int num_ctas = gridDim.x, cta = blockIdx.x;
     const int warp = threadIdx.x / 32, lane = ptx::lane_id();
-    const int W = a.num_warps, S = a.num_stages, k = a.num_topk;
+    const int W = a.num_warps, S = a.num_stages, k = kNumTopk > 0 ? kNumTopk : a.num_topk;
+    const int hidden_bytes = kHiddenBytes > 0 ? kHiddenBytes : a.hidden_bytes;
     const bool is_aux = warp == W;
     const int num_pushers = W * 32;
     layout::CommonSignals* cs = &a.ws->common;
     layout::HostStatus* hs = a.host ? &a.host->status : nullptr;
 
-    const layout::DispatchTokenLayout tl(a.hidden_bytes, a.sf_bytes, k);
+    const layout::DispatchTokenLayout tl(hidden_bytes, a.sf_bytes, k);
     const int token_bytes = tl.num_bytes();
-    const int hidden = a.fused_quant ? a.hidden_bytes : 0;               // fp8 elements when quantising
-    const int src_row_bytes = a.fused_quant ? a.hidden_bytes * 2 : 0;
+    const int hidden = a.fused_quant ? hidden_bytes : 0;               // fp8 elements when quantising
+    const int src_row_bytes = a.fused_quant ? hidden_bytes * 2 : 0;
     const Smem sm = carve(smem_raw, a, token_bytes, src_row_bytes);
 
     if (not dev::healthy(cs)) return;
@@ -139,7 +147,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
         for (int i = 0; i < W * (S + 2); ++i) ptx::mbarrier_init(&sm.mbar[i], 1);
         ptx::fence_mbarrier_init();
     }
-    for (int i = threadIdx.x; i < a.num_experts; i += blockDim.x) sm.expert_hist[i] = 0;
+    for (int i = threadIdx.x; i < num_experts; i += blockDim.x) sm.expert_hist[i] = 0;
     for (int i = threadIdx.x; i < W * kMaxRanks; i += blockDim.x) sm.warp_rank[i] = 0, sm.hit[i] = 0;
     __syncthreads();
 
@@ -160,7 +168,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
             if (t < warp_end) {
                 for (int j = 0; j < k; ++j) {
                     const int64_t e = a.topk_idx[int64_t(t) * k + j];
-                    if (e >= 0 and e < a.num_experts) {
+                    if (e >= 0 and e < num_experts) {
                         atomicOr(&hit[int(e) / num_local_experts], 1u << lane);
                         atomicAdd(&sm.expert_hist[e], 1);
                     }
@@ -178,7 +186,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
             for (int w = 0; w < W; ++w) total += sm.warp_rank[w * kMaxRanks + r];
             a.ws->cta_rank_count[cta][r] = total;
         }
-        for (int e = threadIdx.x; e < a.num_experts; e += blockDim.x)
+        for (int e = threadIdx.x; e < num_experts; e += blockDim.x)
             if (sm.expert_hist[e] != 0) atomicAdd(&a.ws->send_expert_count[e], sm.expert_hist[e]);
     }
 
@@ -213,7 +221,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
             ptx::st_relaxed_sys(&a.peers.sym(&a.ws->recv_rank_count[rank], r)[0], layout::pack_tagged(epoch, total));
         }
         // expert counts -> owners (and clean the local histogram for the next call)
-        for (int e = lane; e < a.num_experts; e += 32) {
+        for (int e = lane; e < num_experts; e += 32) {
             const int v = __ldcg(&a.ws->send_expert_count[e]);
             a.ws->send_expert_count[e] = 0;
             ptx::st_relaxed_sys(a.peers.sym(&a.ws->recv_expert_count[rank][e % num_local_experts], e / num_local_experts),
@@ -316,7 +324,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
     uint8_t* stages = sm.stages + int64_t(warp) * S * token_bytes;
     uint8_t* src_stages = sm.src_stages + int64_t(warp) * 2 * src_row_bytes;
     int* slots = sm.slots + warp * 32 * k;
-    const int load_bytes = a.fused_quant ? src_row_bytes : a.hidden_bytes;
+    const int load_bytes = a.fused_quant ? src_row_bytes : hidden_bytes;
     bool failed = false;
 
     auto issue_load = [&](int i) {   // token index i of this warp's range; executed by lane 0
@@ -327,7 +335,12 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
         ptx::bulk_load(dst, a.x + int64_t(i) * load_bytes, load_bytes, bar);
     };
 
-    if (warp_begin < warp_end and lane == 0) issue_load(warp_begin);
+    // Look-ahead of the row loads: with quantisation one row (two source stages), otherwise S - 1 rows, so that S - 1
+    // loads are in flight while the oldest row is being sent. Row n + D goes into the stage that row n + D - S used, whose
+    // store must have read it: at most S - D - 1 of the committed groups may still be reading.
+    const int D = a.fused_quant ? 1 : S - 1;
+    if (lane == 0)
+        for (int i = warp_begin; i < min(warp_begin + D, warp_end); ++i) issue_load(i);
 
     for (int i = warp_begin; i < warp_end; ++i) {
         const int n = i - warp_begin, tl_idx = n & 31;
@@ -341,7 +354,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
                 if (t < warp_end) {
                     for (int j = 0; j < k; ++j) {
                         const int64_t e = a.topk_idx[int64_t(t) * k + j];
-                        if (e >= 0 and e < a.num_experts) atomicOr(&hit[int(e) / num_local_experts], 1u << lane);
+                        if (e >= 0 and e < num_experts) atomicOr(&hit[int(e) / num_local_experts], 1u << lane);
                     }
                 }
                 __syncwarp();
@@ -350,7 +363,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
                     for (int j = k - 1; j >= 0; --j) {
                         const int64_t e = a.topk_idx[int64_t(t) * k + j];
                         int slot = -1;
-                        if (e >= 0 and e < a.num_experts) {
+                        if (e >= 0 and e < num_experts) {
                             const int r = int(e) / num_local_experts;
                             if (not((seen >> r) & 1)) slot = run[r] + __popc(hit[r] & ptx::lanemask_lt());
                             seen |= 1ull << r;
@@ -366,15 +379,15 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
         }
 
         // ---- prefetch the next row
-        if (i + 1 < warp_end) {
+        if (i + D < warp_end) {
             if (a.fused_quant) {
                 // the source stage was read with ordinary loads two tokens ago
                 ptx::fence_proxy_async_smem();
             } else {
-                wait_read_pending(S - 2);
+                wait_read_pending(S - D - 1);
             }
             __syncwarp();
-            if (lane == 0) issue_load(i + 1);
+            if (lane == 0) issue_load(i + D);
         }
 
         // ---- assemble the message
@@ -393,7 +406,7 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
         int my_slot = -1, my_rank = 0;
         if (lane < k) {
             const int64_t e = a.topk_idx[int64_t(i) * k + lane];
-            const bool valid = e >= 0 and e < a.num_experts;
+            const bool valid = e >= 0 and e < num_experts;
             reinterpret_cast<int*>(stage + tl.idx_offset())[lane] = valid ? int(e) : -1;
             reinterpret_cast<float*>(stage + tl.weight_offset())[lane] =
                 a.topk_weights != nullptr ? a.topk_weights[int64_t(i) * k + lane] : 0.f;
@@ -449,6 +462,10 @@ __global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_con
             if (lane == 0) dev::trace_point(a.trace, kTrDispEnd);       // the CTA that finished last
         }
     }
+}
+
+__global__ void __launch_bounds__(32 * 9, 1) ep_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
+    ep_dispatch_body<0, 0, 0, 0>(a);
 }
 
 }  // namespace deep_ep::kernels

@@ -7,6 +7,7 @@
 
 #include "../device/sync.cuh"
 #include "ep_args.hpp"
+#include "ep_dispatch.cuh"      // `dispatch_detail::wait_read_pending`
 
 namespace deep_ep::kernels {
 
@@ -25,21 +26,27 @@ EP_DEVICE void locate(const int* psum_rank_smem, int num_ranks, int i, int& src,
 
 }  // namespace expand_detail
 
-__global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __grid_constant__ ExpandArgs a) {
+// Kernel body; non-zero template arguments replace the corresponding run-time shape values by compile-time constants
+// (see `ep_dispatch_body`): zeros for the ahead-of-time kernel below, the shapes in use for run-time specialised kernels.
+template <int kNumRanks, int kNumTopk, int kHiddenBytes, int kNumExperts>
+EP_DEVICE void ep_dispatch_expand_body(const ExpandArgs& a) {
     using namespace expand_detail;
     extern __shared__ uint8_t smem_raw[];
     __shared__ int psum_rank_smem[kMaxRanks];
 
-    const int num_local_experts = a.num_experts / a.num_ranks;
+    const int num_ranks = kNumRanks > 0 ? kNumRanks : a.num_ranks;
+    const int num_experts = kNumExperts > 0 ? kNumExperts : a.num_experts;
+    const int hidden_bytes = kHiddenBytes > 0 ? kHiddenBytes : a.hidden_bytes;
+    const int num_local_experts = num_experts / num_ranks;
     const int expert_begin = a.rank * num_local_experts;
     const int num_ctas = gridDim.x, cta = blockIdx.x;
     const int warp = threadIdx.x / 32, lane = ptx::lane_id();
-    const int W = a.num_warps, S = a.num_stages, k = a.num_topk;
+    const int W = a.num_warps, S = a.num_stages, k = kNumTopk > 0 ? kNumTopk : a.num_topk;
     layout::CommonSignals* cs = &a.ws->common;
     layout::HostStatus* hs = a.host ? &a.host->status : nullptr;
-    const layout::DispatchTokenLayout tl(a.hidden_bytes, a.sf_bytes, k);
+    const layout::DispatchTokenLayout tl(hidden_bytes, a.sf_bytes, k);
     const int token_bytes = tl.num_bytes();
-    const layout::BufferLayout bl(token_bytes, a.num_ranks, a.num_max_tokens);
+    const layout::BufferLayout bl(token_bytes, num_ranks, a.num_max_tokens);
 
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     uint8_t* p = base;
@@ -72,19 +79,19 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
     // ---- wait until every source rank has finished pushing to this rank
     if (a.wait_arrival and warp == 0) {
         const dev::Deadline deadline(a.timeout_ns);
-        for (int s = lane; s < a.num_ranks; s += 32) {
+        for (int s = lane; s < num_ranks; s += 32) {
             unsigned long long w = 0;
             if (not dev::spin_until(deadline, [&]() { return (w = ptx::ld_acquire_sys(&a.ws->dispatch_done[s])) == epoch; }))
                 dev::report_status(cs, hs, kStatusArrivalTimeout, a.rank, s, kSiteArrival, epoch, w);
         }
     }
-    for (int s = threadIdx.x; s < a.num_ranks; s += blockDim.x) psum_rank_smem[s] = a.psum_rank[s];
+    for (int s = threadIdx.x; s < num_ranks; s += blockDim.x) psum_rank_smem[s] = a.psum_rank[s];
     for (int e = threadIdx.x; e < num_local_experts; e += blockDim.x) psum_sm[e] = a.psum_expert[e];
     __syncthreads();
     if (not dev::healthy(cs)) return;
     if (tracer) dev::trace_point(a.trace, kTrExpArrived);
 
-    const int num_recv = min(psum_rank_smem[a.num_ranks - 1], a.num_metadata_rows);
+    const int num_recv = min(psum_rank_smem[num_ranks - 1], a.num_metadata_rows);
     const int per_cta = math::ceil_div(num_recv, num_ctas);
     const int cta_begin = min(cta * per_cta, num_recv), cta_end = min(cta_begin + per_cta, num_recv);
     const int per_warp = math::ceil_div(cta_end - cta_begin, W);
@@ -100,7 +107,7 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
             const int i = g + lane;
             if (i < warp_end) {
                 int src, slot;
-                locate(psum_rank_smem, a.num_ranks, i, src, slot);
+                locate(psum_rank_smem, num_ranks, i, src, slot);
                 const int* idx = reinterpret_cast<const int*>(a.buffer + bl.offset(src, slot) + tl.idx_offset());
                 for (int j = 0; j < k; ++j) {
                     const int e = idx[j] - expert_begin;
@@ -147,11 +154,15 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
         ptx::bulk_load(stages + (n % S) * token_bytes, a.buffer + bl.offset(src, slot), token_bytes, &mbar[n % S]);
     };
 
-    if (warp_begin < warp_end and lane == 0) {
-        int src, slot;
-        locate(psum_rank_smem, a.num_ranks, warp_begin, src, slot);
-        issue_load(0, src, slot);
-    }
+    // S - 1 message loads are in flight while the oldest message is being copied out: message n + D reuses the stage of
+    // message n + D - S, whose stores must have read it (at most S - D - 1 = 0 committed groups may still be reading).
+    const int D = S - 1;
+    if (lane == 0)
+        for (int i = warp_begin; i < min(warp_begin + D, warp_end); ++i) {
+            int src, slot;
+            locate(psum_rank_smem, num_ranks, i, src, slot);
+            issue_load(i - warp_begin, src, slot);
+        }
 
     for (int i = warp_begin; i < warp_end; ++i) {
         const int n = i - warp_begin, tl_idx = n & 31;
@@ -160,7 +171,7 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
             int src = 0, slot = 0;
             const int* idx = nullptr;
             if (row < warp_end) {
-                locate(psum_rank_smem, a.num_ranks, row, src, slot);
+                locate(psum_rank_smem, num_ranks, row, src, slot);
                 idx = reinterpret_cast<const int*>(a.buffer + bl.offset(src, slot) + tl.idx_offset());
             }
             if (a.cached) {
@@ -213,13 +224,13 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
         }
 
         // prefetch the next message
-        if (i + 1 < warp_end) {
-            dispatch_detail::wait_read_pending(S - 2);
+        if (i + D < warp_end) {
+            dispatch_detail::wait_read_pending(S - D - 1);
             __syncwarp();
             if (lane == 0) {
                 int src, slot;
-                locate(psum_rank_smem, a.num_ranks, i + 1, src, slot);
-                issue_load(n + 1, src, slot);
+                locate(psum_rank_smem, num_ranks, i + D, src, slot);
+                issue_load(n + D, src, slot);
             }
         }
 
@@ -233,13 +244,18 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
         // hidden row: one bulk store per expanded slot (lane j owns top-k position j)
         const int my_out = lane < k ? slots[tl_idx * (k + 1) + lane] : -1;
         if (my_out >= 0) {
-            ptx::bulk_store(a.recv_x + int64_t(my_out) * a.hidden_bytes, stage, a.hidden_bytes);
+            ptx::bulk_store(a.recv_x + int64_t(my_out) * hidden_bytes, stage, hidden_bytes);
             if (a.recv_topk_weights != nullptr)
                 a.recv_topk_weights[my_out] = reinterpret_cast<const float*>(stage + tl.weight_offset())[lane];
         }
+        // scale factors of a row-major destination: each row's packs are contiguous, one more bulk store per copy
+        const bool sf_rows_bulk = a.recv_sf != nullptr and a.recv_sf_pack_stride == 1 and a.sf_bytes % 16 == 0 and
+                                  (a.recv_sf_token_stride * 2) % 16 == 0;
+        if (sf_rows_bulk and my_out >= 0)
+            ptx::bulk_store(a.recv_sf + int64_t(my_out) * a.recv_sf_token_stride, stage + tl.sf_offset(), a.sf_bytes);
         ptx::bulk_commit();
-        // scale factors: strided 2-byte packs (row- or column-major destination)
-        if (a.recv_sf != nullptr) {
+        // otherwise: strided 2-byte packs (column-major destination, or rows that are no multiple of 16 bytes)
+        if (a.recv_sf != nullptr and not sf_rows_bulk) {
             const unsigned valid = __ballot_sync(0xffffffffu, my_out >= 0);
             const sf_pack_t* src_sf = reinterpret_cast<const sf_pack_t*>(stage + tl.sf_offset());
             for (unsigned m = valid; m != 0; m &= m - 1) {
@@ -259,8 +275,8 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
             const int end = psum_sm[e];
             const int pad_end = min(math::align(end, a.expert_alignment), a.num_expanded_rows);
             for (int row = end + gw; row < pad_end; row += num_gw) {
-                for (int c = lane; c < a.hidden_bytes / 16; c += 32)
-                    ptx::st_na_v4(a.recv_x + int64_t(row) * a.hidden_bytes + c * 16, zero);
+                for (int c = lane; c < hidden_bytes / 16; c += 32)
+                    ptx::st_na_v4(a.recv_x + int64_t(row) * hidden_bytes + c * 16, zero);
                 if (a.recv_sf != nullptr)
                     for (int q = lane; q < a.sf_bytes / 2; q += 32)
                         a.recv_sf[int64_t(row) * a.recv_sf_token_stride + int64_t(q) * a.recv_sf_pack_stride] = 0;
@@ -271,6 +287,10 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __g
     // CTA 0's share is done (every CTA copies the same number of messages, give or take one)
     __syncthreads();
     if (tracer) dev::trace_point(a.trace, kTrExpEnd);
+}
+
+__global__ void __launch_bounds__(32 * 8, 1) ep_dispatch_expand_kernel(const __grid_constant__ ExpandArgs a) {
+    ep_dispatch_expand_body<0, 0, 0, 0>(a);
 }
 
 }  // namespace deep_ep::kernels

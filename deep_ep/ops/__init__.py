@@ -5,6 +5,6 @@
 * `fp8_training`: opt-in FP8 training path of the expert FFN (FP8 forward and data-gradient GEMMs, bf16 weight gradients).
 * `quant`, `jit`: run-time specialised kernels (per-token FP8 quantiser compiled for the hidden size in use).
 * `layout`: routing layout of a batch (`get_dispatch_layout`).
-* `lb`: expert load balancing over redundant expert slots.
+* `dense`: the router's and the shared expert's dense products on the same tcgen05 kernels (one group).
 """
-__all__ = ['fp8_training', 'grouped_gemm', 'jit', 'layout', 'lb', 'quant']
+__all__ = ['dense', 'fp8_training', 'grouped_gemm', 'jit', 'layout', 'quant']

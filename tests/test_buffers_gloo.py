@@ -191,3 +191,35 @@ def test_pp_buffer_library_transport_cpu_ranks(master_port, world):
 @pytest.mark.parametrize('use_fp8', [False, True])
 def test_engram_buffer_two_cpu_ranks(master_port, use_fp8):
     run_distributed(_engram_worker, 2, master_port, 'gloo', (use_fp8,), timeout_s=120)
+
+
+def _mesh_worker(rank, world):
+    import torch.distributed as dist
+    import deep_ep
+    from deep_ep.parallel import ParallelMesh
+    mesh = ParallelMesh(ep_size=2, pp_size=2)                    # 4 ranks: pp x dp x ep = 2 x 1 x 2, ep innermost
+    assert mesh.coords == {'pp': rank // 2, 'dp': 0, 'ep': rank % 2}
+    assert mesh.groups_of('ep') == [(0, 1), (2, 3)] and mesh.groups_of('pp') == [(0, 2), (1, 3)]
+    assert mesh.group('ep').size() == 2 and mesh.group('pp').size() == 2 and mesh.group('dp').size() == 1
+    assert mesh.pp_next() == (rank + 2) % 4 == mesh.pp_prev()
+    assert mesh.rank_of(ep=1 - rank % 2) == rank ^ 1
+    # an expert-parallel exchange inside each EP group and a pipeline hop across them
+    buffer = mesh.ep_buffer(num_max_tokens_per_rank=8, hidden=64, num_topk=2, explicitly_destroy=True)
+    x = torch.full((8, 64), float(rank)).to(torch.bfloat16)
+    idx = torch.stack([torch.arange(8) % 4, (torch.arange(8) + 1) % 4], dim=1)
+    recv_x, _, _, handle, _ = buffer.dispatch(x, topk_idx=idx, num_experts=4, expert_alignment=1, do_expand=True)
+    combined, _, _ = buffer.combine(recv_x, handle)
+    assert torch.equal(combined.float(), torch.full((8, 64), 2.0 * rank))
+    assert set(recv_x.float().unique().tolist()) <= {float(r) for r in mesh.axes['ep'].ranks}
+    buffer.destroy()
+    pp = mesh.pp_buffer(1 << 12, 2, explicitly_destroy=True)
+    peer = mesh.group('pp').rank() ^ 1                            # the other rank of this two-stage pipeline
+    pp.send(torch.full((16,), float(rank)), peer)
+    got = torch.empty(16)
+    pp.recv(got, peer)
+    assert torch.all(got == mesh.pp_next())
+    pp.destroy()
+
+
+def test_parallel_mesh_builds_groups_and_buffers(master_port):
+    run_distributed(_mesh_worker, 4, master_port, 'gloo', timeout_s=180)

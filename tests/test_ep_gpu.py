@@ -5,7 +5,7 @@ import torch
 from dist_utils import run_distributed
 
 
-def _ep_worker(rank, world_size, num_tokens, hidden, num_topk, num_experts, do_cpu_sync, defer, masked, ratio, num_sms):
+def _ep_worker(rank, world_size, num_tokens, hidden, num_topk, num_experts, do_cpu_sync, defer, masked, ratio, num_sms, quick=True):
     import torch.distributed as dist
     import deep_ep
     from deep_ep.utils.envs import init_seed
@@ -16,7 +16,7 @@ def _ep_worker(rank, world_size, num_tokens, hidden, num_topk, num_experts, do_c
                                   explicitly_destroy=True, num_gpu_timeout_secs=10, num_cpu_timeout_secs=30)
         assert not buffer.is_simulated
         check_dispatch_combine(buffer, num_tokens, hidden, num_topk, num_experts, do_cpu_sync=do_cpu_sync, defer=defer,
-                               masked_ratio=masked, unbalanced_ratio=ratio, quick=True, num_sms=num_sms)
+                               masked_ratio=masked, unbalanced_ratio=ratio, quick=quick, num_sms=num_sms)
         if hidden % 128 == 0:
             check_fused_quant(buffer, num_tokens, hidden, num_topk, num_experts)
         buffer.destroy()
@@ -45,6 +45,42 @@ def test_ep_multi_gpu(master_port, case):
     if case[3] % world:
         pytest.skip('experts not divisible')
     run_distributed(_ep_worker, world, master_port, 'nccl', case)
+
+
+@pytest.mark.gpu
+def test_ep_full_mode_matrix(master_port):
+    """Every mode of the reference's sweep (`tests/ep/test_ep.py:25-30`): alignment {128, 1} x FP8 / BF16 x 0, 1 or 2 biases x
+    row- or column-major scale factors, on all visible GPUs (an even number of them, or one)."""
+    world = min(torch.cuda.device_count(), 8)
+    world = world - world % 2 if world > 1 else 1
+    run_distributed(_ep_worker, world, master_port, 'nccl', (190, 512, 4, 8 * world, True, True, 0.1, 1.5, 0, False))
+
+
+def _recreate_worker(rank, world_size):
+    import torch.distributed as dist
+    import deep_ep
+    # buffers are created, used once and destroyed again and again: allocation, peer mapping and release must not leak
+    # or leave a stale mapping behind (the reference's pressure loop, `tests/ep/test_ep.py:538-547`)
+    free_before = torch.cuda.mem_get_info()[0]
+    for i in range(6):
+        buffer = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=64 + i, hidden=512, num_topk=2, explicitly_destroy=True,
+                                  num_gpu_timeout_secs=10, num_cpu_timeout_secs=30)
+        x = torch.full((32, 512), float(rank + i), device='cuda', dtype=torch.bfloat16)
+        idx = torch.rand(32, 4 * world_size, device='cuda').topk(2, dim=-1).indices
+        recv_x, _, _, handle, _ = buffer.dispatch(x, topk_idx=idx, num_experts=4 * world_size, expert_alignment=1, do_expand=True)
+        combined, _, _ = buffer.combine(recv_x, handle)
+        torch.cuda.synchronize()
+        # both copies of a token come back and are summed: small integers, exact in bf16 whatever the split over ranks
+        assert torch.equal(combined.float(), torch.full((32, 512), 2.0 * (rank + i), device='cuda')), i
+        buffer.destroy()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] >= free_before - (64 << 20), 'device memory leaked across buffer lifetimes'
+
+
+@pytest.mark.gpu
+def test_ep_buffer_recreation(master_port):
+    world = min(torch.cuda.device_count(), 2)
+    run_distributed(_recreate_worker, world, master_port, 'nccl')
 
 
 @pytest.mark.gpu

@@ -139,15 +139,6 @@ def test_ue8m0_casts():
     assert wq.shape == w.shape and wsf.shape == (2, 2, 1) and wsf.dtype == torch.uint8
 
 
-def test_parallel_namespace_lists_every_strategy():
-    import deep_ep
-    import deep_ep.parallel as par
-    assert par.EPBuffer is deep_ep.EPBuffer and par.PPBuffer is deep_ep.PPBuffer
-    assert par.BucketBuffer is deep_ep.BucketBuffer and par.EngramBuffer is deep_ep.EngramBuffer
-    assert {cls.__name__ for group in (par.ep, par.pp, par.dp, par.engram) for cls in group} >= {
-        'EPBuffer', 'PPBuffer', 'BucketBuffer', 'EngramBuffer', 'MoELayer'}
-
-
 def test_numa_binding_is_a_noop_without_a_gpu():
     import os
     from deep_ep.utils.envs import bind_to_device_numa_node

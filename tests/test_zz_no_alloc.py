@@ -15,6 +15,8 @@ def _library():
     fn.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                    ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     lib.deep_ep_noalloc_last_error.restype = ctypes.c_char_p
+    lib.deep_ep_noalloc_wait_status.restype = ctypes.c_int
+    lib.deep_ep_noalloc_wait_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
     return lib, fn
 
 
@@ -35,6 +37,10 @@ def test_no_alloc_layout_matches_regular_entry_point_twice():
         rc = fn(idx.data_ptr(), num_tokens, num_topk, num_experts, num_ranks, slots.data_ptr(), per_rank.data_ptr(),
                 per_expert.data_ptr(), stream.cuda_stream)
         assert rc == 0, lib.deep_ep_noalloc_last_error().decode()
+        # the kernel's own verdict: it ran to completion (a wait that gave up would leave a non-zero status word)
+        device_status = ctypes.c_int(-1)
+        assert lib.deep_ep_noalloc_wait_status(stream.cuda_stream, ctypes.byref(device_status)) == 0
+        assert device_status.value == 0, lib.deep_ep_noalloc_last_error().decode()
         ref_slots, ref_rank, ref_expert = get_dispatch_layout(idx, num_experts, num_ranks)
         torch.cuda.synchronize()
         assert torch.equal(slots, ref_slots)
@@ -55,3 +61,5 @@ def test_no_alloc_layout_rejects_oversized_requests():
     assert fn(buf.data_ptr(), 8, 4, 128, 128, *args) == 1                   # too many ranks
     assert fn(buf.data_ptr(), 8, 64, 16, 2, *args) == 1                     # too many top-k positions
     assert fn(None, 8, 4, 16, 2, *args) == 1                                # null input
+    assert fn(buf.data_ptr(), 0, 4, 16, 2, *args) == 1                      # an empty batch is rejected, outputs untouched
+    assert int(out.abs().sum()) == 0
