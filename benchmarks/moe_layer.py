@@ -42,7 +42,11 @@ class BaselineMoELayer(nn.Module):
 
     def route(self, x):
         # library GEMM (cuBLAS) for the router of the baseline, same arithmetic as the layer's own kernel
-        logits = F.linear(x, self.gate.to(torch.bfloat16)).float() if x.dtype == torch.bfloat16 else F.linear(x.float(), self.gate)
+        gate = self.gate.to(torch.bfloat16)
+        try:
+            logits = torch.mm(x, gate.t(), out_dtype=torch.float32)           # bf16 operands, fp32 result, as the layer's kernel
+        except (TypeError, RuntimeError):
+            logits = F.linear(x.float(), gate.float())
         topk_weights, topk_idx = torch.softmax(logits, dim=-1).topk(self.config.num_topk, dim=-1)
         return topk_idx, topk_weights / topk_weights.sum(dim=-1, keepdim=True)
 
@@ -156,6 +160,7 @@ def main():
     p.add_argument('--skip-baseline', action='store_true')
     p.add_argument('--baseline-grouped-mm', action='store_true',
                    help='baseline expert GEMMs through torch.nn.functional.grouped_mm instead of one cuBLAS call per expert')
+    p.add_argument('--baseline-both', action='store_true', help='time both baselines (per-expert loop and F.grouped_mm)')
     p.add_argument('--overlap-shared-expert', action='store_true', help='run the shared expert on a side stream')
     p.add_argument('--fuse-combine', action='store_true',
                    help='let the second expert GEMM store single-row tokens straight into the combine landing slots of their owners')
@@ -188,15 +193,19 @@ def main():
     result = {'bench': 'moe_layer_fwd_bwd', 'n_gpus': world, 'tokens_per_rank': args.num_tokens, 'hidden': args.hidden,
               'intermediate': args.intermediate, 'experts': args.num_experts, 'topk': args.num_topk, 'dtype': 'bf16', 'fuse_combine': args.fuse_combine}
     if not args.skip_baseline:
-        base = BaselineMoELayer(ours, use_grouped_mm=args.baseline_grouped_mm).to(dev)
-        result['baseline_gemm'] = 'F.grouped_mm' if args.baseline_grouped_mm else 'per-expert F.linear'
-        with torch.no_grad():                      # same function, different plumbing: outputs must agree
-            y_ours, y_base = ours(x), base(x)
-        rel = ((y_ours.float() - y_base.float()).norm() / y_base.float().norm()).item()
-        result['rel_diff_vs_baseline'] = round(rel, 5)
-        result['baseline_ms'] = round(time_layer(base, x, args.steps, args.warmup), 3)
-        del base
-        torch.cuda.empty_cache()
+        kinds = [False, True] if args.baseline_both else [args.baseline_grouped_mm]
+        for use_grouped_mm in kinds:
+            name = 'F.grouped_mm' if use_grouped_mm else 'per-expert F.linear'
+            key = 'baseline_grouped_mm_ms' if use_grouped_mm else 'baseline_loop_ms'
+            base = BaselineMoELayer(ours, use_grouped_mm=use_grouped_mm).to(dev)
+            with torch.no_grad():                      # same function, different plumbing: outputs must agree
+                y_ours, y_base = ours(x), base(x)
+            rel = ((y_ours.float() - y_base.float()).norm() / y_base.float().norm()).item()
+            result['rel_diff_vs_baseline'] = round(rel, 5)
+            result[key] = round(time_layer(base, x, args.steps, args.warmup), 3)
+            result['baseline_gemm'], result['baseline_ms'] = name, result[key]       # the last (strongest) one
+            del base
+            torch.cuda.empty_cache()
     if args.main_grad:
         for w in (ours.w_gate_up, ours.w_down):
             w.main_grad = torch.zeros(w.shape, dtype=torch.float32, device=dev)
@@ -284,6 +293,10 @@ def main():
         decode_buffer.destroy()
     if 'baseline_ms' in result:
         result['speedup'] = round(result['baseline_ms'] / result['ours_ms'], 3)
+        if 'ours_fp8_training_ms' in result:
+            result['speedup_fp8_training'] = round(result['baseline_ms'] / result['ours_fp8_training_ms'], 3)
+    if 'ours_fp8_training_ms' in result:
+        result['fp8_training_tflops_per_gpu'] = round(flops / (result['ours_fp8_training_ms'] * 1e-3) / 1e12, 1)
     if rank == 0:
         print(json.dumps(result))
     ours.destroy()

@@ -43,6 +43,29 @@ class LibraryP2PRuntime:
         self._sent = [0, 0]
         self._loopback: List[torch.Tensor] = []      # a ring of one rank: staged messages waiting for their recv
         self.destroyed = False
+        self._connect()
+
+    def _connect(self) -> None:
+        """Set up every neighbour connection of both direction groups now, with all ranks taking part. The library
+        opens a point-to-point connection at the first transfer between two ranks, and both of them have to be inside a
+        call on that group for it: two neighbours that each start with a send (on different groups) would otherwise wait
+        on the host for each other. One batched exchange per group (send and receive in a single library group call) with
+        both neighbours does it."""
+        if self.num_ranks == 1:
+            return
+        nxt, prv = self._neighbours()
+        for group in self.direction_groups:
+            out = torch.zeros(2, 4, dtype=torch.uint8, device=self.device)
+            got = torch.zeros(2, 4, dtype=torch.uint8, device=self.device)
+            ops = []
+            for i, peer in enumerate((nxt, prv) if nxt != prv else (nxt,)):
+                target = dist.get_global_rank(self.group, peer)
+                ops.append(dist.P2POp(dist.isend, out[i], target, group=group))
+                ops.append(dist.P2POp(dist.irecv, got[i], target, group=group))
+            for work in dist.batch_isend_irecv(ops):
+                work.wait()
+        if self.device.type == 'cuda':
+            torch.cuda.synchronize()
 
     def _neighbours(self) -> Tuple[int, int]:
         return (self.rank_idx + 1) % self.num_ranks, (self.rank_idx - 1) % self.num_ranks

@@ -10,8 +10,6 @@ import torch.nn.functional as F
 
 from test_grouped_gemm_gpu import make_layout
 
-new_paths = pytest.mark.skipif(os.environ.get('EP_TEST_NEW_PATHS', '0') != '1',
-                               reason='paths that have not run on a GPU yet; set EP_TEST_NEW_PATHS=1 to try them')
 
 
 def _rel(a, b):
@@ -83,7 +81,6 @@ def test_fp8_weight_cache_follows_parameter_versions():
 
 
 @pytest.mark.gpu
-@new_paths
 def test_cuda_quantisers_match_emulation():
     from deep_ep.ops import fp8_training as ft
     from deep_ep.ops.grouped_gemm import per_block_cast_to_fp8_ue8m0, per_token_cast_to_fp8_ue8m0, ue8m0_to_float
@@ -115,7 +112,6 @@ def test_cuda_quantisers_match_emulation():
 
 
 @pytest.mark.gpu
-@new_paths
 def test_fp8_training_ffn_on_gpu():
     torch.manual_seed(3)
     dev = torch.device('cuda')

@@ -235,8 +235,6 @@ def _new_paths_worker(rank, world_size):
 
 
 @pytest.mark.gpu
-@pytest.mark.skipif(os.environ.get('EP_TEST_NEW_PATHS', '0') != '1',
-                    reason='paths that have not run on a GPU yet; set EP_TEST_NEW_PATHS=1 to try them')
 def test_opt_in_paths_match_default_paths(master_port):
     world = max(1, min(torch.cuda.device_count(), 8))
     if world > 1:
