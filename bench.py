@@ -323,7 +323,12 @@ def main():
         del ref_x, ref_idx, ref_w, ref_src, valid, flat
 
     def step(events=None):
+        # Before each timed phase: the L2 flush keeps the device busy while the host queues the next launches, then a
+        # device-side barrier over the ranks lines them up, so that a phase time does not contain the other ranks' launch
+        # skew (the reference's test does the same before every sample: device-busy op + cross-rank barrier,
+        # `deep_ep/utils/testing.py:347-371` there). Both are inside `ms_per_step`.
         flusher()
+        buffer.barrier(wait_comm_stream=False)
         if events is not None:
             events[0].record()
         ev_d = buffer.dispatch(dispatch_input(), topk_idx=topk_idx, topk_weights=topk_w, fused_fp8_quant=fused, **common)
@@ -333,6 +338,7 @@ def main():
         if events is not None:
             events[2].record()
         flusher()
+        buffer.barrier(wait_comm_stream=False)
         if events is not None:
             events[3].record()
         ev_c = buffer.combine(y, h, topk_weights=w_out, num_sms=num_sms, async_with_compute_stream=True, defer_epilogue=True)
@@ -503,8 +509,8 @@ def main():
             'config': {'model': 'DeepSeek-V3-style MoE routing: hidden 7168, 256 experts, top-6, expert alignment 128',
                        'global_batch': T * world, 'seq_len': None, 'tokens_per_rank': T, 'parallelism': f'ep{world}',
                        'dispatch_input': args.dispatch_input, 'num_sms': num_sms,
-                       'l2': 'a 256 MiB buffer is overwritten before dispatch and before combine in every step (inside ms_per_step, '
-                             'outside the per-phase events)',
+                       'l2': 'a 256 MiB buffer is overwritten and the ranks meet in a device-side barrier before dispatch and before '
+                             'combine in every step (inside ms_per_step, outside the per-phase events)',
                        'timing': 'phase times: CUDA events around the issue kernel with the arrival wait inside it; max over ranks',
                        'vs_baseline_def': 'min per-rank dispatch GB/s / 375 GB/s (published EP8 per-rank figure); null on one GPU, '
                                           'where every message is a local copy'},
@@ -525,7 +531,7 @@ def main():
             'combine': {'value': round(combine_gbs_agg, 2), 'unit': 'GB/s'},
             'checks': checks,
             'clocks': clocks,
-            'gpu_launches': 4 * args.steps,
+            'gpu_launches': 6 * args.steps,        # dispatch, expand, combine, reduce + two rank-barrier kernels per step
         }
         if nccl is not None:
             line['nccl_baseline'] = nccl

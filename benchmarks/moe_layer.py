@@ -42,11 +42,8 @@ class BaselineMoELayer(nn.Module):
 
     def route(self, x):
         # library GEMM (cuBLAS) for the router of the baseline, same arithmetic as the layer's own kernel
-        gate = self.gate.to(torch.bfloat16)
-        try:
-            logits = torch.mm(x, gate.t(), out_dtype=torch.float32)           # bf16 operands, fp32 result, as the layer's kernel
-        except (TypeError, RuntimeError):
-            logits = F.linear(x.float(), gate.float())
+        # the operands of the layer's own kernel (bf16 activations, gate matrix rounded to bf16) in an fp32 library GEMM
+        logits = F.linear(x.float(), self.gate.to(torch.bfloat16).float())
         topk_weights, topk_idx = torch.softmax(logits, dim=-1).topk(self.config.num_topk, dim=-1)
         return topk_idx, topk_weights / topk_weights.sum(dim=-1, keepdim=True)
 
@@ -101,7 +98,7 @@ class BaselineMoELayer(nn.Module):
         return y
 
 
-def time_layer(layer, x, steps, warmup):
+def time_layer(layer, x, steps, warmup, accumulate_into=None):
     """Forward + backward per step. Gradients are dropped after every step (`zero_grad(set_to_none=True)` of a training
     loop), for both layers alike: otherwise every step after the first would also pay an elementwise accumulation pass
     over all expert weight gradients, which belongs to neither layer."""
@@ -110,6 +107,10 @@ def time_layer(layer, x, steps, warmup):
 
     def step():
         layer(x).backward(grad)
+        if accumulate_into is not None:
+            # a layer whose weight-gradient GEMMs cannot add into fp32 buffers themselves does it in a pass of its own
+            for p, main_grad in accumulate_into:
+                main_grad.add_(p.grad)
         for p in params:
             p.grad = None
         x.grad = None
@@ -173,6 +174,8 @@ def main():
     p.add_argument('--decode-graph', type=int, default=0, metavar='TOKENS',
                    help='also time a decode-sized inference forward (this many tokens per rank, FP8 with power-of-two scales, '
                         'no host synchronisation) launched eagerly and replayed as ONE CUDA graph of the whole layer')
+    p.add_argument('--kernel-breakdown', action='store_true',
+                   help='print the device time of every kernel of one forward + backward step of our layer (activity records)')
     p.add_argument('--forward-fp8', action='store_true',
                    help='also time the inference forward: BF16 path against the FP8 path (e4m3 dispatch + block-scaled FP8 GEMMs)')
     args = p.parse_args()
@@ -202,7 +205,12 @@ def main():
                 y_ours, y_base = ours(x), base(x)
             rel = ((y_ours.float() - y_base.float()).norm() / y_base.float().norm()).item()
             result['rel_diff_vs_baseline'] = round(rel, 5)
-            result[key] = round(time_layer(base, x, args.steps, args.warmup), 3)
+            accumulate = None
+            if args.main_grad:        # same work as our layer: expert weight gradients end up added into fp32 buffers
+                accumulate = [(w, torch.zeros(w.shape, dtype=torch.float32, device=dev)) for w in (base.w_gate_up, base.w_down)]
+                result['baseline_wgrad'] = 'bf16 gradients, then one fp32 accumulation pass per step (main_grad += grad)'
+            result[key] = round(time_layer(base, x, args.steps, args.warmup, accumulate), 3)
+            del accumulate
             result['baseline_gemm'], result['baseline_ms'] = name, result[key]       # the last (strongest) one
             del base
             torch.cuda.empty_cache()
@@ -231,6 +239,20 @@ def main():
         ours.config.fp8_training = False
         ours._fp8_cache = None
         torch.cuda.empty_cache()
+    if args.kernel_breakdown:
+        from deep_ep.utils.testing import bench_kineto
+        g = torch.randn_like(x)
+
+        def one_step():
+            ours(x).backward(g)
+            for p_ in ours.parameters():
+                p_.grad = None
+            x.grad = None
+        ours.config.fp8_training = args.fp8_training
+        profiles = bench_kineto(one_step, return_all_kernels=True, num_warmups=2, num_tests=3, flush_l2=False)
+        ours.config.fp8_training = False
+        top = sorted(profiles.values(), key=lambda k: -k.dur_ns * k.num_calls)[:24]
+        result['kernel_breakdown_us'] = [[k.name[:70], k.num_calls, round(k.dur_us, 1)] for k in top]
     if args.forward_fp8:
         ours.quantize_weights()
         with torch.no_grad():

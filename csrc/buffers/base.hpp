@@ -39,6 +39,17 @@ public:
     virtual ~BufferBase() = default;
     virtual void destroy() = 0;
 
+    // Teardown after a failure, in two steps and without the device-side barrier of `destroy()` (a peer may be gone, or
+    // the barrier's own state may be what broke): every rank first closes its mappings of the peers' memory, the caller
+    // then makes the ranks meet on the host, and only then each rank frees its own allocation with `abort()`.
+    void close_peer_mappings() {
+        if (main_context != nullptr) main_context->close_peer_mappings();
+    }
+    void abort() {
+        if (not destroyed) release_without_barrier();
+        destroyed = true;
+    }
+
     void print_memory_usage() const {
         EP_HOST_ASSERT(main_context != nullptr);
         const auto mib = [](int64_t b) { return static_cast<double>(b) / (1 << 20); };

@@ -26,7 +26,19 @@
 
 namespace deep_ep {
 
-class EPBuffer : public BufferBase {
+class EPBuffer : public BufferBase, public std::enable_shared_from_this<EPBuffer> {
+    // A deferred epilogue that has been handed out and neither run nor dropped yet. The epilogue kernels read the
+    // buffer's CURRENT epoch, the landing area and (with the host count handshake) the one shared block of host counts,
+    // so a second operation of the same kind must not be issued before the first one's epilogue has been enqueued.
+    struct EpilogueTicket {
+        int* pending;
+        bool released = false;
+        explicit EpilogueTicket(int* pending) : pending(pending) { ++*pending; }
+        void release() { if (not released) released = true, --*pending; }
+        ~EpilogueTicket() { release(); }
+    };
+    int pending_dispatch_epilogues = 0, pending_combine_epilogues = 0;
+
     layout::EPHostCounts* host_counts = nullptr;          // host view of the mapped pinned block
     layout::EPHostCounts* host_counts_device = nullptr;   // device view
 
@@ -151,6 +163,9 @@ public:
                              bool use_col_major_sf, bool defer_epilogue, int fused_fp8_quant) {
         EP_HOST_ASSERT(not destroyed and context->peers_ready);
         EP_HOST_ASSERT(do_expand and not do_handle_copy);
+        EP_HOST_ASSERT_MSG(pending_dispatch_epilogues == 0,
+                           "the deferred epilogue of the previous dispatch on this buffer has not been run yet: call its hook "
+                           "(`current_stream_wait()`) before the next dispatch");
         (void) allocate_on_comm_stream;
         const bool cached_mode = cached_recv_src_metadata.has_value();
         const int num_ranks = context->num_ranks;
@@ -264,7 +279,10 @@ public:
 
         // ---- epilogue (possibly deferred): sizes, outputs, expand kernel. The closure keeps the
         // inputs and the context alive until the expand kernel has been enqueued.
-        auto epilogue = [=, this, x = x, sf = sf, topk_idx = topk_idx, topk_weights = topk_weights, context = context]() -> pybind11::object {
+        // the closure keeps the buffer itself alive (a hook may outlive the Python object that created it)
+        auto epilogue = [=, this, self = shared_from_this(), ticket = std::make_shared<EpilogueTicket>(&pending_dispatch_epilogues),
+                         x = x, sf = sf, topk_idx = topk_idx, topk_weights = topk_weights, context = context]() -> pybind11::object {
+            EP_HOST_ASSERT_MSG(not ticket->released, "this dispatch epilogue has already been run");
             int num_recv_tokens = num_ranks * num_max_tokens_per_rank;
             int num_expanded_tokens = 0;
             std::vector<int> per_expert_list;
@@ -318,6 +336,7 @@ public:
             e.cached = cached_mode, e.do_zero_padding = do_zero_padding, e.wait_arrival = not barrier_in_prologue;
             e.timeout_ns = context->num_gpu_timeout_ns;
             launch::dispatch_expand(e, num_sms, out_stream);
+            ticket->release();
 
             return pybind11::make_tuple(recv_x, recv_sf, recv_topk_weights, num_recv_tokens, num_expanded_tokens, per_expert_list,
                                         psum_rank, psum_expert, num_unaligned, recv_src_metadata, dst_buffer_slot_idx, dst_gsge_idx);
@@ -343,6 +362,9 @@ public:
                             bool async_with_compute_stream, bool allocate_on_comm_stream, bool defer_epilogue,
                             bool skip_single_rows, bool apply_weights) {
         EP_HOST_ASSERT(not destroyed and context->peers_ready);
+        EP_HOST_ASSERT_MSG(pending_combine_epilogues == 0,
+                           "the deferred epilogue of the previous combine on this buffer has not been run yet: call its hook "
+                           "(`current_stream_wait()`) before the next combine");
         (void) allocate_on_comm_stream;
         const int num_ranks = context->num_ranks;
         const auto device = x.device();
@@ -388,8 +410,10 @@ public:
         launch::combine(args, num_sms, stream);
 
         const bool with_weights = topk_weights.has_value();
-        auto epilogue = [=, this, x = x, topk_weights = topk_weights, bias_0 = bias_0, bias_1 = bias_1, topk_idx = topk_idx,
+        auto epilogue = [=, this, self = shared_from_this(), ticket = std::make_shared<EpilogueTicket>(&pending_combine_epilogues),
+                         x = x, topk_weights = topk_weights, bias_0 = bias_0, bias_1 = bias_1, topk_idx = topk_idx,
                          context = context]() -> pybind11::object {
+            EP_HOST_ASSERT_MSG(not ticket->released, "this combine epilogue has already been run");
             auto combined_x = torch::empty({num_tokens, hidden}, x.options());
             std::optional<torch::Tensor> combined_topk_weights;
             if (with_weights)
@@ -407,6 +431,7 @@ public:
             r.rank = context->rank_idx, r.num_ranks = num_ranks;
             r.wait_arrival = not barrier_in_prologue, r.timeout_ns = context->num_gpu_timeout_ns;
             launch::combine_reduce(r, Runtime::get().get_num_device_sms(), c10::cuda::getCurrentCUDAStream());
+            ticket->release();
             return pybind11::make_tuple(combined_x, combined_topk_weights);
         };
 

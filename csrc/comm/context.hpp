@@ -206,6 +206,16 @@ public:
         throw EPException("Device status", __FILE__, __LINE__, os.str());
     }
 
+    // First half of a teardown without a device-side barrier (after a failure): this rank stops mapping its peers'
+    // memory. Once every rank has done so (the caller meets the others on the host), each may free its own allocation.
+    void close_peer_mappings() {
+        for (const auto& h : opened_handles) IpcMappingCache::get().close(h);
+        opened_handles.clear();
+        for (int r = 0; r < num_ranks; ++r)
+            if (r != rank_idx and memory != nullptr and memory->vmm == nullptr) peers.base[r] = nullptr;
+        peers_ready = num_ranks == 1;
+    }
+
     void finalize() {
         if (finalized) return;
         finalized = true;

@@ -126,17 +126,6 @@ void grouped_gemm_fp8(kernels::GroupedGemmFp8Args args, const void* a, int64_t a
     CUDA_CHECK(cudaGetLastError());
 }
 
-namespace {
-// EP_GEMM_L2_PREFETCH=<K blocks>: look-ahead of the producer's L2 prefetches in the bf16 kernel (0 switches them off)
-int l2_prefetch_distance() {
-    static const int distance = [] {
-        const char* text = std::getenv("EP_GEMM_L2_PREFETCH");
-        return text != nullptr ? std::max(0, std::atoi(text)) : 0;
-    }();
-    return distance;
-}
-}  // namespace
-
 void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, int64_t a_cols,
                   const void* b, int64_t b_rows, int64_t b_cols, int num_sms, cudaStream_t stream, bool use_pairs) {
     using namespace kernels;
@@ -180,7 +169,6 @@ void grouped_gemm(kernels::GroupedGemmArgs args, const void* a, int64_t a_rows, 
     // B: K-major weights (box 64 x 128) for forward, MN-major (box 64 x 64) otherwise
     const CUtensorMap map_b = args.mode == kModeForward ? make_map_2d(b, b_rows, b_cols, 64, 128) : make_map_2d(b, b_rows, b_cols, 64, 64);
     const auto smem = grouped_gemm_smem_bytes(args.block_n, args.num_stages);
-    args.l2_prefetch = l2_prefetch_distance();
     CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     grouped_gemm_kernel<<<grid, 192, smem, stream>>>(map_a, map_b, args);
     CUDA_CHECK(cudaGetLastError());

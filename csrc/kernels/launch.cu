@@ -144,8 +144,11 @@ void combine_route(const kernels::CombineRouteArgs& args, cudaStream_t stream) {
 
 void combine_reduce(kernels::CombineReduceArgs args, int num_sms, cudaStream_t stream) {
     // not cooperative: oversubscribe the SMs so that enough loads are in flight
-    launch_ep_kernel("reduce", {args.num_ranks, args.num_topk, args.hidden_bytes, args.num_experts}, kernels::ep_combine_reduce_kernel,
-                     args, clamp_sms(num_sms) * 4, 256, 0, false, stream);
+    const EPShape shape = {args.num_ranks, args.num_topk, args.hidden_bytes, args.num_experts};
+    if (std::min(args.num_topk, args.num_ranks) <= 2)
+        launch_ep_kernel("reduce", shape, kernels::ep_combine_reduce_few_rows_kernel, args, clamp_sms(num_sms) * 4, 256, 0, false, stream);
+    else
+        launch_ep_kernel("reduce", shape, kernels::ep_combine_reduce_kernel, args, clamp_sms(num_sms) * 6, 256, 0, false, stream);
 }
 
 namespace {

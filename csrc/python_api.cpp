@@ -369,6 +369,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     py::class_<BufferBase, std::shared_ptr<BufferBase>>(m, "BufferBase")
         .def_readonly("main_context", &BufferBase::main_context)
         .def("print_memory_usage", &BufferBase::print_memory_usage)
+        .def("close_peer_mappings", &BufferBase::close_peer_mappings)
+        .def("abort", &BufferBase::abort)
         .def("destroy", &BufferBase::destroy);
 
     py::class_<EPBuffer, BufferBase, std::shared_ptr<EPBuffer>>(m, "EPBuffer")

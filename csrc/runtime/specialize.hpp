@@ -7,6 +7,7 @@
 // Switch: `EP_JIT_SPECIALIZE=1` in the environment or `_C.set_jit_specialization(True)`.
 #pragma once
 
+#include <algorithm>
 #include <cstdio>
 #include <map>
 #include <mutex>
@@ -60,6 +61,8 @@ public:
             << "        const __grid_constant__ deep_ep::kernels::" << k->args_type << " a) {\n"
             << "    deep_ep::kernels::" << k->body << "<" << shape.num_ranks << ", " << shape.num_topk << ", " << shape.hidden_bytes;
         if (k->with_experts) out << ", " << shape.num_experts;
+        // the reduce body also takes "a token has at most two partials" (see ep_combine.cuh)
+        if (kernel == "reduce") out << ", " << (std::min(shape.num_topk, shape.num_ranks) <= 2 ? "true" : "false");
         out << ">(a);\n}\n";
         return out.str();
     }

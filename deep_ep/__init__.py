@@ -5,9 +5,11 @@ import os
 
 import torch
 
-# Environment defaults persisted at build time never override the caller's environment.
+# Written by setup.py at build time: the version with the source revision, and the values that the run-time compiler's
+# environment switches had during the build. Those become defaults; the caller's environment always wins.
+__version__ = '1.0.0'
 try:
-    from .envs import persistent_envs
+    from ._build_info import persistent_envs, version as __version__
     for _key, _value in persistent_envs.items():
         os.environ.setdefault(_key, _value)
 except ImportError:
@@ -44,5 +46,3 @@ get_num_rdma_alignment = _C.get_num_rdma_alignment
 get_num_tma_alignment = _C.get_num_tma_alignment
 topk_idx_t = _C.topk_idx_t
 EPException = _C.EPException
-
-__version__ = '1.0.0'

@@ -35,6 +35,25 @@ class BufferBase(ABC):
             self.runtime = None
 
 
+    def abort(self, group: dist.ProcessGroup = None) -> None:
+        """Teardown after a failure (a device-side wait that ran out, a peer that is gone): unlike `destroy()` it runs no
+        device-side barrier, whose own state may be what broke. This rank stops mapping its peers' memory, meets the other
+        ranks of `group` on the host (skip that with `group=None` when they cannot be reached any more) and frees its
+        allocation. The buffer is unusable afterwards; the CUDA context is not affected."""
+        if self.runtime is None:
+            return
+        if hasattr(self.runtime, 'close_peer_mappings'):
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            self.runtime.close_peer_mappings()
+            if group is not None and group.size() > 1:
+                dist.barrier(group)
+            self.runtime.abort()
+        elif hasattr(self.runtime, 'destroyed'):
+            self.runtime.destroyed = True          # CPU stand-in runtimes hold nothing that needs releasing
+        self.runtime = None
+
+
 def connect_peers(context, group: dist.ProcessGroup) -> None:
     """Exchange the CUDA-IPC handles of a context's symmetric allocation over `group` and map the peers.
 

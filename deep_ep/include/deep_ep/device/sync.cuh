@@ -87,15 +87,26 @@ EP_DEVICE bool rank_barrier_warp(layout::CommonSignals* cs, layout::HostStatus* 
     n = __shfl_sync(0xffffffffu, n, 0);
     const int phase = n & 1, sign = (n & 2) ? -1 : 1;
     __threadfence_system();
-    for (int r = lane; r < peers.num_ranks; r += 32)
-        ptx::red_add_release_sys(&peers.sym(cs, r)->barrier_signals[phase], sign);
+    for (int r = lane; r < peers.num_ranks; r += 32) {
+        layout::CommonSignals* peer = peers.sym(cs, r);
+        // who arrived (looked at only when the wait below runs out), then the arrival itself
+        ptx::red_xor_relaxed_sys(&peer->barrier_arrived[phase][peers.rank / 32], 1u << (peers.rank % 32));
+        ptx::red_add_release_sys(&peer->barrier_signals[phase], sign);
+    }
     const int target = sign > 0 ? peers.num_ranks : 0;
     bool ok = true;
     if (lane == 0) {
         const Deadline deadline(timeout_ns);
         ok = spin_until(deadline, [&]() { return ptx::ld_acquire_sys(&cs->barrier_signals[phase]) == target; });
-        if (not ok)
-            report_status(cs, hs, kStatusBarrierTimeout, peers.rank, -1, where, target, cs->barrier_signals[phase]);
+        if (not ok) {
+            // every rank has toggled its bit (n >> 1) + 1 times once it has arrived at this barrier of the phase: the
+            // first rank whose bit still has the old value is named in the report
+            const unsigned arrived_value = ((n >> 1) + 1) & 1;
+            int absent = -1;
+            for (int r = 0; r < peers.num_ranks and absent < 0; ++r)
+                if (((ptx::ld_acquire_sys(&cs->barrier_arrived[phase][r / 32]) >> (r % 32)) & 1u) != arrived_value) absent = r;
+            report_status(cs, hs, kStatusBarrierTimeout, peers.rank, absent, where, target, cs->barrier_signals[phase]);
+        }
         cs->barrier_counter = n + 1;
     }
     ok = __shfl_sync(0xffffffffu, ok, 0);

@@ -122,10 +122,6 @@ EP_DEVICE void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y,
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(ptx::smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(ptx::smem_addr(bar)) : "memory");
 }
-// Brings the same box into L2 only (no shared-memory destination, no completion to wait for).
-EP_DEVICE void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
-}
 EP_DEVICE void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

@@ -72,9 +72,13 @@ EP_DEVICE void reduce_rows(const uint8_t* x, int hidden_bytes, int c_begin, int 
                            uint8_t* stage, int lane) {
     if (count <= 4) {
         int sl[4];
+        unsigned left = valid;
         #pragma unroll
-        for (int u = 0; u < 4; ++u)
-            sl[u] = u < count ? __shfl_sync(0xffffffffu, my_slot, nth_set_bit(valid, min(u, count - 1))) : -1;
+        for (int u = 0; u < 4; ++u) {
+            const int v = __shfl_sync(0xffffffffu, my_slot, left != 0 ? __ffs(left) - 1 : 0);
+            sl[u] = left != 0 ? v : -1;
+            left &= left - 1;
+        }
         if (count == 2) {
             const int s2[2] = {sl[0], sl[1]};
             reduce_rows_impl<2, 4>(x, hidden_bytes, c_begin, chunks, s2, stage, lane);
@@ -83,9 +87,13 @@ EP_DEVICE void reduce_rows(const uint8_t* x, int hidden_bytes, int c_begin, int 
         }
     } else if (count <= 8) {
         int sl[8];
+        unsigned left = valid;
         #pragma unroll
-        for (int u = 0; u < 8; ++u)
-            sl[u] = u < count ? __shfl_sync(0xffffffffu, my_slot, nth_set_bit(valid, min(u, count - 1))) : -1;
+        for (int u = 0; u < 8; ++u) {
+            const int v = __shfl_sync(0xffffffffu, my_slot, left != 0 ? __ffs(left) - 1 : 0);
+            sl[u] = left != 0 ? v : -1;
+            left &= left - 1;
+        }
         reduce_rows_impl<8, 2>(x, hidden_bytes, c_begin, chunks, sl, stage, lane);
     } else {
         for (int base = c_begin; base < chunks; base += 32) {       // warp-uniform trip count: shuffles inside
@@ -141,19 +149,17 @@ EP_DEVICE void reduce_rows_weighted(const uint8_t* x, int hidden_bytes, int c_be
     }
 }
 
-// Owner-side reduction of one token: fp32 sum of bias_0, bias_1 and the partials in slot order, one rounding to
-// bf16. `kChunks` 16-byte chunks per lane are in flight before the first add.
+// Owner-side reduction of one token: fp32 sum of the rows `part[0..kParts)` (null entries skipped) in index order, one
+// rounding to bf16. The caller lists bias_0, bias_1 and then the partials in slot order. `kChunks` 16-byte chunks per lane
+// and row are in flight before the first add.
 template <int kParts, int kChunks>
-EP_DEVICE void reduce_token(const uint8_t* const (&part)[kParts], const uint8_t* b0, const uint8_t* b1, uint8_t* out,
-                            int c_begin, int chunks, int lane) {
+EP_DEVICE void reduce_token(const uint8_t* const (&part)[kParts], uint8_t* out, int c_begin, int chunks, int lane) {
     for (int c0 = c_begin + lane; c0 < chunks; c0 += 32 * kChunks) {
-        int4 v[kChunks][kParts], vb0[kChunks], vb1[kChunks];
+        int4 v[kChunks][kParts];
         #pragma unroll
         for (int i = 0; i < kChunks; ++i) {
             const int c = c0 + 32 * i;
             if (c >= chunks) continue;
-            if (b0 != nullptr) vb0[i] = ptx::ld_nc_v4(b0 + c * 16);
-            if (b1 != nullptr) vb1[i] = ptx::ld_nc_v4(b1 + c * 16);
             #pragma unroll
             for (int u = 0; u < kParts; ++u)
                 if (part[u] != nullptr) v[i][u] = ptx::ld_v4(part[u] + c * 16);
@@ -163,8 +169,6 @@ EP_DEVICE void reduce_token(const uint8_t* const (&part)[kParts], const uint8_t*
             const int c = c0 + 32 * i;
             if (c >= chunks) continue;
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (b0 != nullptr) accumulate(acc, vb0[i]);
-            if (b1 != nullptr) accumulate(acc, vb1[i]);
             #pragma unroll
             for (int u = 0; u < kParts; ++u)
                 if (part[u] != nullptr) accumulate(acc, v[i][u]);
@@ -421,7 +425,7 @@ __global__ void __launch_bounds__(32 * 8, 1) ep_combine_kernel(const __grid_cons
 
 // Kernel body; non-zero template arguments replace the corresponding run-time shape values by compile-time constants
 // (see `ep_dispatch_body`): zeros for the ahead-of-time kernel below, the shapes in use for run-time specialised kernels.
-template <int kNumRanks, int kNumTopk, int kHiddenBytes, int kNumExperts>
+template <int kNumRanks, int kNumTopk, int kHiddenBytes, int kNumExperts, bool kFewRows>
 EP_DEVICE void ep_combine_reduce_body(const CombineReduceArgs& a) {
     using namespace combine_detail;
     const int num_ranks = kNumRanks > 0 ? kNumRanks : a.num_ranks;
@@ -478,20 +482,33 @@ EP_DEVICE void ep_combine_reduce_body(const CombineReduceArgs& a) {
         const unsigned masters = __ballot_sync(0xffffffffu, is_master);
         const int count = __popc(masters);
 
-        const uint8_t* part[kUnroll];
-        #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const int g = __shfl_sync(0xffffffffu, group, u < count ? nth_set_bit(masters, u) : 0);
-            part[u] = u < count ? a.buffer + bl.offset(g, t) : nullptr;
-        }
         const uint8_t* b0 = a.bias_0 != nullptr ? a.bias_0 + int64_t(t) * hidden_bytes : nullptr;
         const uint8_t* b1 = a.bias_1 != nullptr ? a.bias_1 + int64_t(t) * hidden_bytes : nullptr;
         uint8_t* out = a.combined_x + int64_t(t) * hidden_bytes;
-        if (count <= 4) {
-            const uint8_t* p4[4] = {part[0], part[1], part[2], part[3]};
-            reduce_token<4, 4>(p4, b0, b1, out, c_begin, c_end, lane);
-        } else if (count <= kUnroll) {
-            reduce_token<kUnroll, 2>(part, b0, b1, out, c_begin, c_end, lane);
+        // rows to add, in the order of the sum: bias_0, bias_1, then the partials in slot order
+        const int num_bias = (b0 != nullptr) + (b1 != nullptr), total = num_bias + count;
+        const uint8_t* part[kUnroll];
+        unsigned left = masters;                // master positions not yet listed (the same in every lane)
+        #pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            if (u < num_bias) {
+                part[u] = (u == 0 and b0 != nullptr) ? b0 : b1;
+            } else {
+                const bool have = left != 0;
+                const int g = __shfl_sync(0xffffffffu, group, have ? __ffs(left) - 1 : 0);
+                left &= left - 1;
+                part[u] = have ? a.buffer + bl.offset(g, t) : nullptr;
+            }
+        }
+        // Register budget first: with one row per load round the kernel needs about 80 registers, so three CTAs (24 warps)
+        // fit on an SM and the rows of a token (3 to 6 at eight ranks) are in flight together in each of them. When a
+        // token can have at most two partials (`kFewRows`: one or two ranks, or top-1/top-2 routing) that would leave one or
+        // two loads per lane, so that variant fetches four chunks of each row per round instead (128 registers, 16 warps).
+        if (kFewRows and total <= 2) {
+            const uint8_t* p2[2] = {part[0], part[1]};
+            reduce_token<2, 4>(p2, out, c_begin, c_end, lane);
+        } else if (total <= kUnroll) {
+            reduce_token<kUnroll, 1>(part, out, c_begin, c_end, lane);
         } else {
             for (int base = c_begin; base < c_end; base += 32) {      // warp-uniform trip count: shuffles inside
                 const int c = base + lane;
@@ -526,8 +543,13 @@ EP_DEVICE void ep_combine_reduce_body(const CombineReduceArgs& a) {
     if (tracer) dev::trace_point(a.trace, kTrRedEnd);
 }
 
-__global__ void __launch_bounds__(32 * 8) ep_combine_reduce_kernel(const __grid_constant__ CombineReduceArgs a) {
-    ep_combine_reduce_body<0, 0, 0, 0>(a);
+__global__ void __launch_bounds__(32 * 8, 3) ep_combine_reduce_kernel(const __grid_constant__ CombineReduceArgs a) {
+    ep_combine_reduce_body<0, 0, 0, 0, false>(a);
+}
+
+// Variant for tokens with at most two partials (min(top-k, ranks) <= 2), see the note on the register budget above.
+__global__ void __launch_bounds__(32 * 8, 2) ep_combine_reduce_few_rows_kernel(const __grid_constant__ CombineReduceArgs a) {
+    ep_combine_reduce_body<0, 0, 0, 0, true>(a);
 }
 
 }  // namespace deep_ep::kernels

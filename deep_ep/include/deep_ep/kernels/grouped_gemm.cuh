@@ -57,15 +57,57 @@ EP_DEVICE Tile locate_tile(const GroupedGemmArgs& a, const int* prefix, int tile
     return t;
 }
 
-// TMA boxes of one K block of a tile: into the shared-memory stage (`sa`, `sb`, completion on `bar`) or, with
-// `kPrefetch`, into L2 only.
-template <bool kPrefetch>
+// fp32 weight-gradient row of a tile: `out[0, 32 * num_chunks)` = accumulator columns, plus the previous contents of `out`
+// with `accumulate`. Read-modify-write one 32-column chunk after the other would be a chain of dependent round trips to
+// memory (and with few rows per expert the tile's MMAs are far shorter than that chain), so the previous contents are
+// fetched ahead of their use: `WgradRow::prefetch` is called BEFORE the wait for the accumulator and requests the first
+// two chunks, `finish` requests chunk i + 2 while it adds and stores chunk i.
+struct WgradRow {
+    static constexpr int kMaxChunks = 8, kAhead = 2;
+    int4 old[kAhead + 1][8];
+
+    EP_DEVICE void fetch(const float* out, int chunk, int slot) {
+        #pragma unroll
+        for (int v = 0; v < 8; ++v) old[slot][v] = ptx::ld_v4(out + 32 * chunk + 4 * v);
+    }
+    EP_DEVICE void prefetch(const float* out, int num_chunks, bool accumulate) {
+        if (not accumulate) return;
+        #pragma unroll
+        for (int i = 0; i < kAhead; ++i)
+            if (i < num_chunks) fetch(out, i, i);
+    }
+    EP_DEVICE void finish(float* out, uint32_t taddr, int num_chunks, bool has_accumulator, bool accumulate) {
+        #pragma unroll
+        for (int i = 0; i < kMaxChunks; ++i) {
+            if (i >= num_chunks) break;
+            if (accumulate and i + kAhead < num_chunks) fetch(out, i + kAhead, (i + kAhead) % (kAhead + 1));
+            uint32_t r[32];
+            if (has_accumulator) {
+                tc::tmem_ld_32x32(taddr + 32 * i, r);
+                tc::wait_ld();
+            } else {
+                #pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0;
+            }
+            #pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                float4 val = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                         __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                if (accumulate) {
+                    const int4& before = old[i % (kAhead + 1)][v];
+                    val.x += __int_as_float(before.x), val.y += __int_as_float(before.y);
+                    val.z += __int_as_float(before.z), val.w += __int_as_float(before.w);
+                }
+                *reinterpret_cast<float4*>(out + 32 * i + 4 * v) = val;
+            }
+        }
+    }
+};
+
+// TMA boxes of one K block of a tile into the shared-memory stage (`sa`, `sb`, completion on `bar`).
 EP_DEVICE void load_k_block(const GroupedGemmArgs& a, const CUtensorMap& map_a, const CUtensorMap& map_b, const Tile& t, int kb,
                             int BN, uint8_t* sa, uint8_t* sb, uint64_t* bar) {
-    auto box = [&](uint8_t* dst, const CUtensorMap* map, int x, int y) {
-        if constexpr (kPrefetch) tc::tma_prefetch_2d(map, x, y);
-        else tc::tma_load_2d(dst, map, x, y, bar);
-    };
+    auto box = [&](uint8_t* dst, const CUtensorMap* map, int x, int y) { tc::tma_load_2d(dst, map, x, y, bar); };
     const int k0 = kb * kGemmBlockK;
     if (a.mode == kModeWgrad) {
         // A = dY^T: source rows are K, columns (contiguous) are M
@@ -154,20 +196,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t phase = 0;
             for (int tile = blockIdx.x; tile < num_tiles and not error_flag; tile += gridDim.x) {
                 const Tile t = locate_tile(a, tile_prefix, tile);
-                // optional look-ahead: K blocks that the ring will ask for `l2_prefetch` blocks from now (of this tile or
-                // of this CTA's next one) are pulled into L2 already, so that the ring's own loads do not wait for DRAM
-                const bool has_next = a.l2_prefetch > 0 and tile + int(gridDim.x) < num_tiles;
-                const Tile next = has_next ? locate_tile(a, tile_prefix, tile + gridDim.x) : t;
                 for (int kb = 0; kb < t.num_k_blocks; ++kb, s = (s + 1 == S ? 0 : s + 1), phase ^= (s == 0)) {
-                    if (a.l2_prefetch > 0) {
-                        const int ahead = kb + a.l2_prefetch;
-                        if (ahead < t.num_k_blocks) load_k_block<true>(a, map_a, map_b, t, ahead, BN, nullptr, nullptr, nullptr);
-                        else if (has_next and ahead - t.num_k_blocks < next.num_k_blocks)
-                            load_k_block<true>(a, map_a, map_b, next, ahead - t.num_k_blocks, BN, nullptr, nullptr, nullptr);
-                    }
                     if (not ptx::mbarrier_wait(&empty_bar[s], phase ^ 1)) { error_flag = 1; break; }
                     ptx::mbarrier_arrive_expect_tx(&full_bar[s], a_bytes + b_bytes);
-                    load_k_block<false>(a, map_a, map_b, t, kb, BN, smem_a + size_t(s) * a_bytes, smem_b + size_t(s) * b_bytes, &full_bar[s]);
+                    load_k_block(a, map_a, map_b, t, kb, BN, smem_a + size_t(s) * a_bytes, smem_b + size_t(s) * b_bytes, &full_bar[s]);
                 }
             }
         }
@@ -213,13 +245,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int tile = blockIdx.x; tile < num_tiles and not error_flag; tile += gridDim.x, ++local_tile) {
             const Tile t = locate_tile(a, tile_prefix, tile);
             const int acc = local_tile & 1, use = local_tile >> 1;
+            // fp32 weight gradients: the previous contents of this thread's output row are requested before the wait
+            const bool wgrad_fp32 = a.mode == kModeWgrad and not a.out_bf16;
+            const size_t wgrad_index = wgrad_fp32 ? (size_t(t.expert) * a.m + t.m0 + row) * a.n + t.n0 : 0;
+            WgradRow wgrad_row;
+            if (wgrad_fp32) wgrad_row.prefetch(reinterpret_cast<const float*>(a.d) + wgrad_index, BN / 32, a.accumulate);
             if (not ptx::mbarrier_wait(&tmem_full_bar[acc], use & 1)) { error_flag = 1; break; }
             tc::fence_after_thread_sync();
             const uint32_t taddr = tmem_base + acc * 256 + (uint32_t(quarter * 32) << 16);
             const bool valid = row < t.rows_valid;
-            if (a.mode == kModeWgrad) {
+            if (wgrad_fp32) {
+                wgrad_row.finish(reinterpret_cast<float*>(a.d) + wgrad_index, taddr, BN / 32, t.num_k_blocks > 0, a.accumulate);
+            } else if (a.mode == kModeWgrad) {
                 const size_t out_index = (size_t(t.expert) * a.m + t.m0 + row) * a.n + t.n0;
-                float* out = reinterpret_cast<float*>(a.d) + out_index;
                 __nv_bfloat16* out16 = reinterpret_cast<__nv_bfloat16*>(a.d) + out_index;
                 for (int c = 0; c < BN; c += 32) {
                     uint32_t r[32];
@@ -230,27 +268,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = 0;
                     }
-                    if (a.out_bf16) {
-                        #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            int4 packed;
-                            uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
-                            #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                w[i] = ptx::float2_to_bf16x2(__uint_as_float(r[8 * v + 2 * i]), __uint_as_float(r[8 * v + 2 * i + 1]));
-                            *reinterpret_cast<int4*>(out16 + c + 8 * v) = packed;
-                        }
-                        continue;
-                    }
                     #pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        float4 val = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                                 __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                        if (a.accumulate) {
-                            const float4 old = *reinterpret_cast<float4*>(out + c + 4 * v);
-                            val.x += old.x, val.y += old.y, val.z += old.z, val.w += old.w;
-                        }
-                        *reinterpret_cast<float4*>(out + c + 4 * v) = val;
+                    for (int v = 0; v < 4; ++v) {
+                        int4 packed;
+                        uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+                        #pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            w[i] = ptx::float2_to_bf16x2(__uint_as_float(r[8 * v + 2 * i]), __uint_as_float(r[8 * v + 2 * i + 1]));
+                        *reinterpret_cast<int4*>(out16 + c + 8 * v) = packed;
                     }
                 }
             } else if (a.epilogue != kEpilogueStore) {

@@ -192,14 +192,19 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         for (int tile = pair; tile < num_tiles and not error_flag; tile += num_pairs, ++local_tile) {
             const Tile t = locate_tile(a, tile_prefix, tile);
             const int acc = local_tile & 1, use = local_tile >> 1;
+            const int m = t.m0 + 128 * int(cta_rank) + row;        // row inside the expert's region (or of the per-expert output)
+            // fp32 weight gradients: the previous contents of this thread's output row are requested before the wait
+            const bool wgrad_fp32 = a.mode == kModeWgrad and not a.out_bf16;
+            const size_t wgrad_index = a.mode == kModeWgrad ? (size_t(t.expert) * a.m + m) * a.n + t.n0 : 0;
+            gemm_detail::WgradRow wgrad_row;
+            if (wgrad_fp32) wgrad_row.prefetch(reinterpret_cast<const float*>(a.d) + wgrad_index, kPairN / 32, a.accumulate);
             if (not ptx::mbarrier_wait(&tmem_full_bar[acc], use & 1)) { error_flag = 1; break; }
             tc::fence_after_thread_sync();
             const uint32_t taddr = tmem_base + acc * 256 + (uint32_t(quarter * 32) << 16);
-            const int m = t.m0 + 128 * int(cta_rank) + row;        // row inside the expert's region (or of the per-expert output)
-            if (a.mode == kModeWgrad) {
-                const size_t out_index = (size_t(t.expert) * a.m + m) * a.n + t.n0;
-                float* out = reinterpret_cast<float*>(a.d) + out_index;
-                __nv_bfloat16* out16 = reinterpret_cast<__nv_bfloat16*>(a.d) + out_index;
+            if (wgrad_fp32) {
+                wgrad_row.finish(reinterpret_cast<float*>(a.d) + wgrad_index, taddr, kPairN / 32, t.num_k_blocks > 0, a.accumulate);
+            } else if (a.mode == kModeWgrad) {
+                __nv_bfloat16* out16 = reinterpret_cast<__nv_bfloat16*>(a.d) + wgrad_index;
                 for (int c = 0; c < kPairN; c += 32) {
                     uint32_t r[32];
                     if (t.num_k_blocks > 0) {
@@ -209,27 +214,14 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = 0;
                     }
-                    if (a.out_bf16) {
-                        #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            int4 packed;
-                            uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
-                            #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                w[i] = ptx::float2_to_bf16x2(__uint_as_float(r[8 * v + 2 * i]), __uint_as_float(r[8 * v + 2 * i + 1]));
-                            *reinterpret_cast<int4*>(out16 + c + 8 * v) = packed;
-                        }
-                        continue;
-                    }
                     #pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        float4 val = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                                 __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                        if (a.accumulate) {
-                            const float4 old = *reinterpret_cast<float4*>(out + c + 4 * v);
-                            val.x += old.x, val.y += old.y, val.z += old.z, val.w += old.w;
-                        }
-                        *reinterpret_cast<float4*>(out + c + 4 * v) = val;
+                    for (int v = 0; v < 4; ++v) {
+                        int4 packed;
+                        uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+                        #pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            w[i] = ptx::float2_to_bf16x2(__uint_as_float(r[8 * v + 2 * i]), __uint_as_float(r[8 * v + 2 * i + 1]));
+                        *reinterpret_cast<int4*>(out16 + c + 8 * v) = packed;
                     }
                 }
             } else {

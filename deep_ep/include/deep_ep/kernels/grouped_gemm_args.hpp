@@ -26,7 +26,6 @@ struct GroupedGemmArgs {
     int block_n;              // accumulator columns per tile (128 or 256)
     int block_n_out;          // output columns per tile
     int num_stages;
-    int l2_prefetch;          // K blocks of look-ahead that the producer prefetches into L2 (0 = none; single-CTA kernel)
     int out_bf16;             // wgrad: 1 = d is bf16 (overwrite only), 0 = d is fp32
     int out_fp32;             // forward / dgrad with the plain-store epilogue: 1 = d is fp32 [rows, n_out] (single-CTA kernel only)
     int accumulate;           // wgrad: 1 = add to the existing contents of d, 0 = overwrite (experts without rows get zeros)

@@ -13,13 +13,14 @@
 // 128-row tile side by side in one 16-byte line, the arrangement `tcgen05.cp.32x128b.warpx4` copies into tensor
 // memory), and the MMA thread copies them next to the accumulator: 4 columns for A, 8 for the 256 columns of B.
 //
-// 384 threads per CTA, registers re-split with `setmaxnreg` (40 / 232):
+// 384 threads per CTA, registers re-split with `setmaxnreg` (72 / 216; with 40 the scale producer spilled):
 //   warp 0      TMA producer of the operand tiles (128-byte swizzle, CTA-local loads)
 //   warp 1      MMA issuer: `tcgen05.cp` of the scales, four block-scaled MMAs per K block, commits
 //   warp 2      scale producer: global scale bytes -> shared-memory atoms
 //   warp 3      idle
-//   warps 4-11  epilogue: each thread takes 128 accumulator values into registers (so that tensor memory is handed
-//               back to the next tile after one round of loads), then SwiGLU / re-quantisation / stores
+//   warps 4-11  epilogue: each thread takes its 128 accumulator values into registers in two rounds of 64, reducing the
+//               first round to its results before the second arrives; tensor memory is handed back to the next tile
+//               right after the second round's loads, before the re-quantisation and the stores
 // K must be a multiple of 512 (whole scale groups), N a multiple of 256.
 // The reference contains no matrix math; this kernel exists for the fused MoE layer the library is benchmarked in.
 #pragma once
@@ -87,8 +88,8 @@ grouped_gemm_fp8_hw_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     const int num_tiles = tile_prefix[a.num_groups];
 
     if (warp < 4) {
-    // The CTA's register pool is 384 threads x 168 registers = 64512 = 128 x 40 + 256 x 232.
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    // The CTA's register pool is 384 threads x 168 registers = 64512 = 128 x 72 + 256 x 216.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -196,7 +197,7 @@ grouped_gemm_fp8_hw_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     }
     } else {
         // ------------------------------------------------------------------ epilogue (eight warps)
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         const int quarter = warp & 3;                    // tensor-memory lane quarter this warp may access
         const int half = (warp - 4) >> 2;                // which two 64-column segments
         const int row = quarter * 32 + lane;
@@ -210,19 +211,31 @@ grouped_gemm_fp8_hw_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             if (not ptx::mbarrier_wait(&tmem_full_bar, local_tile & 1)) { error_flag = 1; break; }
             tc::fence_after_thread_sync();
             const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
-            uint32_t acc[128];
-            #pragma unroll
-            for (int seg = 0; seg < 4; ++seg) {
-                uint32_t (&r)[32] = *reinterpret_cast<uint32_t (*)[32]>(&acc[32 * seg]);
-                tc::tmem_ld_32x32(taddr + (seg < 2 ? col_a + 32 * seg : col_b + 32 * (seg - 2)), r);
-            }
-            tc::wait_ld();
-            // the accumulator is in registers: the next tile may overwrite tensor memory
-            tc::fence_before_thread_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbarrier_arrive(&tmem_empty_bar);
-
+            // The warp's 128 accumulator columns are taken out of tensor memory in two rounds of 64 (two 32-column loads
+            // each): the values of the first round are already reduced to their results (32 SwiGLU outputs, or stored) when
+            // the second round arrives, so at most about a hundred registers are live instead of two hundred. Tensor
+            // memory is handed back to the MMA warp right after the second round's loads.
             const bool valid = row < t.rows_valid, written = row < t.rows_written;
+            uint32_t acc[64];
+            auto load_round = [&](int round) {
+                // SwiGLU: 32 gate + 32 up columns of output columns [32 * round, 32 * round + 32); plain: 64 columns
+                uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&acc[0]);
+                uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&acc[32]);
+                if (swiglu) {
+                    tc::tmem_ld_32x32(taddr + col_a + 32 * round, lo);
+                    tc::tmem_ld_32x32(taddr + col_b + 32 * round, hi);
+                } else {
+                    tc::tmem_ld_32x32(taddr + (round == 0 ? col_a : col_b), lo);
+                    tc::tmem_ld_32x32(taddr + (round == 0 ? col_a : col_b) + 32, hi);
+                }
+                tc::wait_ld();
+                if (round == 1) {
+                    // everything is in registers: the next tile may overwrite tensor memory
+                    tc::fence_before_thread_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbarrier_arrive(&tmem_empty_bar);
+                }
+            };
             if (not swiglu) {
                 __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + size_t(grow) * a.n_out + t.n0 + half * 128;
                 if (a.route != nullptr and valid) {
@@ -230,26 +243,35 @@ grouped_gemm_fp8_hw_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
                     const unsigned long long target = __ldg(a.route + grow);
                     if (target != 0) out = reinterpret_cast<__nv_bfloat16*>(target) + t.n0 + half * 128, stored_remotely = true;
                 }
-                if (written) {
-                    #pragma unroll
-                    for (int v = 0; v < 16; ++v) {
-                        int4 packed;
-                        uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+                #pragma unroll
+                for (int round = 0; round < 2; ++round) {
+                    load_round(round);
+                    if (written) {
                         #pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            w[i] = valid ? ptx::float2_to_bf16x2(__uint_as_float(acc[8 * v + 2 * i]), __uint_as_float(acc[8 * v + 2 * i + 1])) : 0u;
-                        *reinterpret_cast<int4*>(out + 8 * v) = packed;
+                        for (int v = 0; v < 8; ++v) {
+                            int4 packed;
+                            uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+                            #pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                w[i] = valid ? ptx::float2_to_bf16x2(__uint_as_float(acc[8 * v + 2 * i]), __uint_as_float(acc[8 * v + 2 * i + 1])) : 0u;
+                            *reinterpret_cast<int4*>(out + 64 * round + 8 * v) = packed;
+                        }
                     }
                 }
             } else {
-                // acc[0..64) = gate, acc[64..128) = up of output columns n0 + half * 64 ..
+                // output columns n0 + half * 64 .. + 64 of this warp: h = silu(gate) * up * row scale
                 const float scale = (valid and a.row_scale != nullptr) ? a.row_scale[grow] : 1.0f;
                 float amax = 0.f;
                 float h[64];
                 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    h[i] = valid ? silu(__uint_as_float(acc[i])) * __uint_as_float(acc[64 + i]) * scale : 0.f;
-                    amax = fmaxf(amax, fabsf(h[i]));
+                for (int round = 0; round < 2; ++round) {
+                    load_round(round);
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float value = valid ? silu(__uint_as_float(acc[i])) * __uint_as_float(acc[32 + i]) * scale : 0.f;
+                        h[32 * round + i] = value;
+                        amax = fmaxf(amax, fabsf(value));
+                    }
                 }
                 if (not a.out_fp8) {
                     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + size_t(grow) * a.n_out + t.n0 + half * 64;

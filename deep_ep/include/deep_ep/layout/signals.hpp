@@ -49,7 +49,10 @@ struct alignas(128) CommonSignals {
     unsigned int reserved[27];
     // ---- written by peers ----
     alignas(128) int barrier_signals[2];   // +-1 per rank per phase, never reset
-    int reserved2[30];
+    // One bit per rank and phase, toggled by that rank at every barrier of the phase (never reset either). Only read when a
+    // barrier runs out of time: the ranks whose bit has not flipped are the ones that did not arrive.
+    unsigned int barrier_arrived[2][kMaxRanks / 32];
+    int reserved2[30 - 2 * (kMaxRanks / 32)];
 };
 static_assert(sizeof(CommonSignals) == 256, "CommonSignals must stay two cache lines");
 

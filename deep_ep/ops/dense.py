@@ -66,8 +66,8 @@ class DenseLinear(torch.autograd.Function):
 def dense_linear(x: torch.Tensor, w: torch.Tensor, out_fp32: bool = False) -> torch.Tensor:
     """`x @ w.T` for 2-D `x`; on a GPU with bf16 operands and 128-aligned `w` it runs on the tcgen05 kernel."""
     if not _supported(x, w):
-        y = F.linear(x, w)
-        return y.float() if out_fp32 else y
+        # library fallback; an fp32 result is computed in fp32 from the same operands, not rounded to bf16 on the way
+        return F.linear(x.float(), w.float()) if out_fp32 else F.linear(x, w)
     return DenseLinear.apply(x.contiguous(), w.contiguous(), out_fp32)
 
 

@@ -163,6 +163,23 @@ def expand(layout: DispatchLayout, inputs: List[RankInput], num_expanded_rows: i
     return recv_x, recv_sf, recv_w
 
 
+class _EpilogueTicket:
+    """Marks a deferred epilogue as outstanding until it is run or dropped; the CUDA runtime refuses a second dispatch
+    (or combine) while one is outstanding (`csrc/buffers/ep.hpp`), and so does this one."""
+
+    def __init__(self, owner, kind: str):
+        self.owner, self.kind, self.released = owner, kind, False
+        owner._pending[kind] += 1
+
+    def release(self) -> None:
+        if not self.released:
+            self.released = True
+            self.owner._pending[self.kind] -= 1
+
+    def __del__(self):
+        self.release()
+
+
 def combine_partials(x: torch.Tensor, topk_weights: Optional[torch.Tensor], metadata: torch.Tensor, num_topk: int,
                      apply_weights: bool = False):
     """Per received row: fp32 sum of its expanded rows in top-k order -> bf16, and the routed weights. With
@@ -239,6 +256,7 @@ class SimEPRuntime:
         self.context = self.main_context = SimEPRuntime._Context(self.rank_idx, self.num_ranks)
         self.lb_storage = torch.zeros(num_lb_bytes, dtype=torch.uint8)
         self.destroyed = False
+        self._pending = {'dispatch': 0, 'combine': 0}      # deferred epilogues handed out and not yet run
 
     def destroy(self):
         dist.barrier(self.group)
@@ -297,6 +315,8 @@ class SimEPRuntime:
         from ..utils.event import EventHandle
         from ..utils.math import per_token_cast_to_fp8
         assert do_expand and not do_handle_copy and not self.destroyed
+        assert self._pending['dispatch'] == 0, \
+            'the deferred epilogue of the previous dispatch on this buffer has not been run yet'
         cached = cached_recv_src_metadata is not None
         num_tokens, num_topk = topk_idx.shape
         assert num_tokens <= num_max_tokens_per_rank and num_experts % self.num_ranks == 0
@@ -334,7 +354,11 @@ class SimEPRuntime:
                 metadata = torch.full((num_recv_tokens, num_topk + 2), -1, dtype=torch.int32)
                 metadata[:exact_recv] = layout.recv_src_metadata
 
+        ticket = _EpilogueTicket(self, 'dispatch')
+
         def epilogue():
+            assert not ticket.released, 'this dispatch epilogue has already been run'
+            ticket.release()
             recv_x, recv_sf, recv_w = expand(layout, inputs, num_expanded, do_zero_padding, use_col_major_sf)
             if x.dtype == torch.float8_e4m3fn:
                 recv_x = recv_x.view(torch.float8_e4m3fn)
@@ -353,6 +377,8 @@ class SimEPRuntime:
         from ..utils.event import EventHandle
         assert not skip_single_rows, 'GEMM epilogues that store into landing slots exist on CUDA only'
         assert not apply_weights or topk_weights is not None, 'a weighted combine needs `topk_weights`'
+        assert self._pending['combine'] == 0, \
+            'the deferred epilogue of the previous combine on this buffer has not been run yet'
         num_tokens, num_topk = topk_idx.shape
         num_recv = int(psum_rank[-1])
         metadata = recv_src_metadata[:num_recv]
@@ -360,7 +386,11 @@ class SimEPRuntime:
         src_global = metadata[:, num_topk].long()
         gathered = self._gather((partials, weights, src_global))
 
+        ticket = _EpilogueTicket(self, 'combine')
+
         def epilogue():
+            assert not ticket.released, 'this combine epilogue has already been run'
+            ticket.release()
             partials_by_rank, weights_by_rank = [], []
             for d, (p, w, g) in enumerate(gathered):
                 mine = (g // num_max_tokens_per_rank) == self.rank_idx

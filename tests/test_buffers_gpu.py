@@ -56,6 +56,46 @@ def test_bounded_wait_reports_status(master_port):
     run_distributed(_timeout_worker, 1, master_port, 'nccl')
 
 
+def _absent_peer_worker(rank, world):
+    """One rank never enters a barrier: the other one's wait gives up after its one-second budget, the exception names
+    the absent rank and the site, and both ranks then release their buffers without a device-side barrier. Nothing
+    faults, traps or spins past its budget; the failure is a rank that stays away, made on the host."""
+    import time
+    import torch.distributed as dist
+    import deep_ep
+    buf = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=64, hidden=256, num_topk=2, explicitly_destroy=True,
+                           num_gpu_timeout_secs=1, num_cpu_timeout_secs=5)
+    assert not buf.is_simulated
+    buf.barrier(with_cpu_sync=True)                 # a healthy barrier first
+    if rank == 0:
+        t0 = time.time()
+        with pytest.raises(deep_ep.EPException) as info:
+            buf.barrier(with_cpu_sync=True)         # rank `world - 1` does not come
+        took = time.time() - t0
+        text = str(info.value)
+        assert f'waiting for rank {world - 1}' in text and 'site 1' in text and 'rank barrier timeout' in text, text
+        assert 0.5 < took < 5, took
+    elif rank != world - 1:
+        with pytest.raises(deep_ep.EPException):
+            buf.barrier(with_cpu_sync=True)
+    # the absent rank learns on the host that the others are done; no kernel of this buffer is in flight anywhere now
+    torch.cuda.synchronize()
+    dist.barrier()
+    buf.abort(dist.group.WORLD)
+    # the process and its CUDA context are still healthy: a new buffer over the same group works
+    buf2 = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=64, hidden=256, num_topk=2, explicitly_destroy=True,
+                            num_gpu_timeout_secs=10)
+    buf2.barrier(with_cpu_sync=True)
+    buf2.destroy()
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_barrier_names_the_absent_rank_and_buffers_are_released_without_a_barrier(master_port, monkeypatch):
+    monkeypatch.setenv('NCCL_NVLS_ENABLE', '0')     # plain peer loads and stores everywhere in a failure test
+    run_distributed(_absent_peer_worker, 2, master_port, 'nccl', timeout_s=60)
+
+
 # ---------------------------------------------------------------------------------------------------- events / streams
 def _stream_worker(rank, world):
     import torch.distributed as dist
@@ -307,9 +347,19 @@ def _reduce_worker(rank, world):
         odd = session.allocate((world * 4 + 1,), torch.float32)
         with pytest.raises(deep_ep.EPException):
             bucket.all_reduce(odd)
-        outside = torch.zeros(world * 16, device='cuda')
-        with pytest.raises(deep_ep.EPException):
-            bucket.reduce_scatter(outside)
+        # tensors outside the storage are staged by the session: all-reduce stays in place for the caller,
+        # reduce-scatter hands back the reduced shard
+        n, dt = specs[0]
+        user = data(rank, n, dt)
+        out = bucket.all_reduce(user, scale=0.5).wait()
+        assert out is user and torch.equal(user, expected(n, dt, 0.5))
+        user2 = data(rank, n, dt)
+        shard = bucket.reduce_scatter(user2).wait()
+        assert torch.equal(shard, expected(n, dt, 1.0)[rank * (n // world):(rank + 1) * (n // world)])
+        assert torch.equal(user2, data(rank, n, dt))
+    outside = torch.zeros(world * 16, device='cuda')
+    with pytest.raises(deep_ep.EPException):
+        bucket.reduce_scatter(outside)                       # outside a session only registered tensors are accepted
     torch.cuda.synchronize()
     bucket.destroy()
 

@@ -145,3 +145,33 @@ def _lb_worker(rank, world):
 
 def test_lb_two_cpu_ranks(master_port):
     run_distributed(_lb_worker, 2, master_port, 'gloo')
+
+
+def _pending_epilogue_worker(rank, world):
+    import torch.distributed as dist
+    import deep_ep
+    buffer = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=16, hidden=32, num_topk=2, explicitly_destroy=True)
+    x = torch.randn(16, 32).to(torch.bfloat16)
+    idx = torch.rand(16, 4 * world).topk(2, dim=-1).indices
+    common = dict(topk_idx=idx, num_experts=4 * world, expert_alignment=1, do_expand=True, async_with_compute_stream=True)
+    first = buffer.dispatch(x, defer_epilogue=True, **common)
+    # the first dispatch's epilogue is still outstanding: a second dispatch would read the landing area, the epoch and the
+    # host counts of the wrong call, so it is refused
+    with pytest.raises((AssertionError, deep_ep.EPException)):
+        buffer.dispatch(x, defer_epilogue=True, **common)
+    recv_x, _, _, handle = first.current_stream_wait()
+    second = buffer.dispatch(x, defer_epilogue=True, **common)            # fine once the hook has run
+    second.current_stream_wait()
+    dropped = buffer.dispatch(x, defer_epilogue=True, **common)           # a hook that is dropped releases its claim
+    del dropped
+    import gc
+    gc.collect()
+    combine_a = buffer.combine(recv_x, handle, async_with_compute_stream=True, defer_epilogue=True)
+    with pytest.raises((AssertionError, deep_ep.EPException)):
+        buffer.combine(recv_x, handle, async_with_compute_stream=True, defer_epilogue=True)
+    combine_a.current_stream_wait()
+    buffer.destroy()
+
+
+def test_second_operation_is_refused_while_a_deferred_epilogue_is_pending(master_port):
+    run_distributed(_pending_epilogue_worker, 2, master_port, 'gloo', timeout_s=120)

@@ -77,6 +77,22 @@ def _recreate_worker(rank, world_size):
     assert torch.cuda.mem_get_info()[0] >= free_before - (64 << 20), 'device memory leaked across buffer lifetimes'
 
 
+def _pending_worker(rank, world_size):
+    from test_ep_gloo import _pending_epilogue_worker
+    with torch.cuda.device(rank):
+        torch.set_default_device('cuda')
+        try:
+            _pending_epilogue_worker(rank, world_size)
+        finally:
+            torch.set_default_device('cpu')
+    torch.cuda.synchronize()
+
+
+@pytest.mark.gpu
+def test_second_operation_is_refused_while_a_deferred_epilogue_is_pending_gpu(master_port):
+    run_distributed(_pending_worker, min(torch.cuda.device_count(), 2), master_port, 'nccl')
+
+
 @pytest.mark.gpu
 def test_ep_buffer_recreation(master_port):
     world = min(torch.cuda.device_count(), 2)

@@ -152,7 +152,11 @@ def _new_paths_worker(rank, world_size):
         ys.backward(torch.ones_like(ys))
         torch.cuda.synchronize()
         results.append((ys.detach().clone(), xs.grad.clone()))
-    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    # same output bit for bit; the input gradient is a sum of three contributions (dispatch, router, shared expert) whose
+    # order of accumulation depends on the streams, so it may differ in the last bf16 digit
+    assert torch.equal(results[0][0], results[1][0])
+    ga, gb = results[0][1].float(), results[1][1].float()
+    assert torch.allclose(ga, gb, atol=2e-2 * ga.abs().max().item(), rtol=2e-2)
     layer_s.destroy()
 
     # the same through the FP8 inference path with power-of-two scales (GEMM2 = the hardware-scaled kernel)

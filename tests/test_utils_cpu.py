@@ -171,3 +171,29 @@ def test_nvtx_range_decorator_is_transparent(monkeypatch):
         raise ValueError('boom')
     with pytest.raises(ValueError):
         nvtx_range('y')(boom)()
+
+
+def test_build_time_environment_defaults_and_version(tmp_path, monkeypatch):
+    """`setup.py` records the source revision and the build-time values of the JIT switches; importing the package turns
+    them into defaults that the caller's environment overrides."""
+    import importlib.util
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location('deep_ep_setup_probe', os.path.join(root, 'setup.py'))
+    code = open(os.path.join(root, 'setup.py')).read().split('sources = [')[0]      # the helpers, without running setup()
+    namespace = {'__file__': os.path.join(root, 'setup.py')}
+    monkeypatch.setenv('EP_JIT_CACHE_DIR', '/baked/in/cache')
+    monkeypatch.delenv('EP_JIT_DEBUG', raising=False)
+    exec(compile(code, spec.origin, 'exec'), namespace)
+    namespace['write_build_info'](str(tmp_path))
+    info = {}
+    exec(open(tmp_path / '_build_info.py').read(), info)
+    assert info['persistent_envs'] == {'EP_JIT_CACHE_DIR': '/baked/in/cache'}
+    assert info['version'].startswith('1.0.0+') and len(info['version']) > len('1.0.0+')
+    # the installed defaults never override what the caller has set
+    probe = ('import os, sys; sys.path.insert(0, %r); os.environ["EP_JIT_CACHE_DIR"] = "/mine"; import deep_ep; '
+             'print(os.environ["EP_JIT_CACHE_DIR"], deep_ep.__version__)' % root)
+    out = subprocess.check_output([sys.executable, '-c', probe]).decode().split()
+    assert out[0] == '/mine' and out[1].startswith('1.0.0')
