@@ -272,7 +272,7 @@ public:
         args.psum_rank = psum_rank.data_ptr<int>(), args.psum_expert = psum_expert.data_ptr<int>();
         args.num_unaligned = num_unaligned.data_ptr<int>();
         args.cumulative_stats = cumulative_local_expert_recv_stats.has_value() ? cumulative_local_expert_recv_stats->data_ptr<int>() : nullptr;
-        args.ws = signals(), args.buffer_offset = context->num_workspace_bytes, args.peers = context->peers;
+        args.ws = signals(), args.buffer_offset = context->num_workspace_bytes, args.buffer_bytes = num_bytes, args.peers = context->peers;
         args.host = host_counts_device, args.timeout_ns = context->num_gpu_timeout_ns;
         args.trace = trace_of(0);
         launch::dispatch(args, num_sms, stream);
@@ -400,7 +400,7 @@ public:
         args.num_metadata_rows = static_cast<int>(recv_src_metadata.size(0));
         args.num_topk = num_topk, args.num_max_tokens = num_max_tokens_per_rank, args.hidden_bytes = hidden * 2;
         args.wait_arrival = barrier_in_prologue;
-        args.ws = signals(), args.buffer_offset = context->num_workspace_bytes, args.peers = context->peers;
+        args.ws = signals(), args.buffer_offset = context->num_workspace_bytes, args.buffer_bytes = num_bytes, args.peers = context->peers;
         args.host = host_counts_device, args.timeout_ns = context->num_gpu_timeout_ns;
         args.trace = trace_of(2);
         const bool coop = Runtime::get().get_warp_cooperation();

@@ -288,6 +288,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("get_npu_arch", [] { return Runtime::get().get_arch(); });
     m.def("set_npu_arch", [](const std::string& a) { Runtime::get().set_arch(a); });
     jit::register_python_api(m);
+    m.def("landing_range_ok", &layout::landing_range_ok, py::arg("offset"), py::arg("bytes"), py::arg("area_bytes"),
+          "the predicate the bounds-checked kernels (EP_DEBUG) apply to every remote message store");
     jit::register_specialization_api(m);
     // Host-only self-test of the descriptor exchange used by the virtual-memory-management route: a pipe's two ends travel
     // through `FdServer` / `receive_fds` inside this process and must still be connected to each other afterwards.

@@ -120,6 +120,8 @@ public:
         EP_HOST_ASSERT_MSG(not package_dir.empty(), "init_jit(package_dir) has not been called");
         std::string flags = "-std=c++20 -O3 --expt-relaxed-constexpr -cubin";
         if (get_env_flag("KERNEL_DEBUG_INFO")) flags += " -lineinfo";
+        // EP_DEBUG=1: bounds-checked build of the kernels (every remote message store is checked against its landing area)
+        if (const char* debug = std::getenv("EP_DEBUG"); debug != nullptr and std::string(debug) == "1") flags += " -DEP_DEBUG";
         const std::string arch_num = arch.substr(3);
         flags += " -gencode arch=compute_" + arch_num + ",code=" + arch;
         std::ostringstream key;

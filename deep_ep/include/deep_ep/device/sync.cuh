@@ -4,6 +4,7 @@
 // returns false; nothing traps.
 #pragma once
 
+#include "../layout/ep.hpp"
 #include "../layout/signals.hpp"
 #include "ptx.cuh"
 
@@ -41,6 +42,24 @@ EP_DEVICE void report_status(layout::CommonSignals* cs, layout::HostStatus* hs, 
         __threadfence_system();
         hs->code = code;
     }
+}
+
+// Bulk store of a message into the landing area of `peer` at `area_offset` bytes from the area's start. Kernels compiled
+// with `-DEP_DEBUG` (the bounds-checked build: `EP_DEBUG=1` for `setup.py`, or for the run-time specialiser) first check
+// that the destination lies inside the area and is 16-byte aligned; a store that fails the check is NOT issued, and the
+// offending offset is recorded in the status word (`kStatusBadArgument`, `expected` = area size, `observed` = offset).
+EP_DEVICE void store_message(layout::CommonSignals* cs, layout::HostStatus* hs, const layout::PeerTable& peers, int peer,
+                             int64_t area_start, int64_t area_bytes, int64_t area_offset, const void* smem_src, uint32_t bytes,
+                             int where) {
+#ifdef EP_DEBUG
+    if (peer < 0 or peer >= peers.num_ranks or not layout::landing_range_ok(area_offset, bytes, area_bytes)) {
+        report_status(cs, hs, kStatusBadArgument, peers.rank, peer, where, area_bytes, area_offset);
+        return;
+    }
+#else
+    (void) cs, (void) hs, (void) area_bytes, (void) where;
+#endif
+    ptx::bulk_store(peers.base[peer] + area_start + area_offset, smem_src, bytes);
 }
 
 EP_DEVICE bool healthy(const layout::CommonSignals* cs) {

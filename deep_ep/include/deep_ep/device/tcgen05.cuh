@@ -122,6 +122,17 @@ EP_DEVICE void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y,
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(ptx::smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(ptx::smem_addr(bar)) : "memory");
 }
+// Tiled 2-D store of a shared-memory box to global memory, and the same as an element-wise add into global memory
+// (the element type comes from the tensor map). Tracked by the issuing thread's bulk async-group. `x * element size`
+// must be a multiple of 16 bytes and no coordinate may be negative.
+EP_DEVICE void tma_store_2d(const CUtensorMap* map, int x, int y, const void* smem_src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(ptx::smem_addr(smem_src)) : "memory");
+}
+EP_DEVICE void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, const void* smem_src) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(ptx::smem_addr(smem_src)) : "memory");
+}
 EP_DEVICE void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

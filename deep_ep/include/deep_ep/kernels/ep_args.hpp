@@ -34,6 +34,7 @@ struct DispatchArgs {
     // communication
     layout::EPSignals* ws;
     int64_t buffer_offset;          // receive buffer offset inside the symmetric allocation
+    int64_t buffer_bytes;           // size of the receive buffer (bounds-checked build)
     layout::PeerTable peers;
     layout::EPHostCounts* host;
     long long timeout_ns;
@@ -72,6 +73,7 @@ struct CombineArgs {
     int wait_arrival;
     layout::EPSignals* ws;
     int64_t buffer_offset;
+    int64_t buffer_bytes;             // size of the landing buffer (bounds-checked build)
     layout::PeerTable peers;
     layout::EPHostCounts* host;
     long long timeout_ns;

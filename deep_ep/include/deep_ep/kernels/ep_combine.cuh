@@ -19,7 +19,7 @@ namespace deep_ep::kernels {
 
 namespace combine_detail {
 
-constexpr int kSiteEntryBarrier = 30, kSiteGridSync = 31, kSiteLoad = 32, kSiteArrival = 33;
+constexpr int kSiteEntryBarrier = 30, kSiteGridSync = 31, kSiteLoad = 32, kSiteArrival = 33, kSitePush = 34;
 constexpr int kUnroll = 8;
 
 
@@ -275,8 +275,8 @@ EP_DEVICE void ep_combine_body(const CombineArgs& a) {
                             __syncwarp();
                             if (lane == 0) {
                                 const int dst_group = num_ranks >= k ? master : rank;
-                                ptx::bulk_store(a.peers.base[s] + a.buffer_offset + bl.offset(dst_group, token) + tl.weight_offset(),
-                                                stage + tl.weight_offset(), token_bytes - tl.weight_offset());
+                                dev::store_message(cs, hs, a.peers, s, a.buffer_offset, a.buffer_bytes, bl.offset(dst_group, token) + tl.weight_offset(),
+                                                   stage + tl.weight_offset(), token_bytes - tl.weight_offset(), kSitePush);
                             }
                         }
                         ptx::bulk_commit();
@@ -298,7 +298,7 @@ EP_DEVICE void ep_combine_body(const CombineArgs& a) {
                 if (part == 0) {
                     if (lane == 0) {
                         const int dst_group = num_ranks >= k ? master : rank;
-                        ptx::bulk_store(a.peers.base[s] + a.buffer_offset + bl.offset(dst_group, token), stage, token_bytes);
+                        dev::store_message(cs, hs, a.peers, s, a.buffer_offset, a.buffer_bytes, bl.offset(dst_group, token), stage, token_bytes, kSitePush);
                     }
                     ptx::bulk_commit();
                 }
@@ -342,8 +342,8 @@ EP_DEVICE void ep_combine_body(const CombineArgs& a) {
                     __syncwarp();
                     if (lane == 0) {
                         const int group = num_ranks >= k ? master : rank;
-                        ptx::bulk_store(a.peers.base[s] + a.buffer_offset + bl.offset(group, token) + tl.weight_offset(),
-                                        stage + tl.weight_offset(), token_bytes - tl.weight_offset());
+                        dev::store_message(cs, hs, a.peers, s, a.buffer_offset, a.buffer_bytes, bl.offset(group, token) + tl.weight_offset(),
+                                           stage + tl.weight_offset(), token_bytes - tl.weight_offset(), kSitePush);
                     }
                 }
                 ptx::bulk_commit();
@@ -380,7 +380,7 @@ EP_DEVICE void ep_combine_body(const CombineArgs& a) {
             }
             if (lane == 0) {
                 const int group = num_ranks >= k ? master : rank;
-                ptx::bulk_store(a.peers.base[s] + a.buffer_offset + bl.offset(group, token), stage, token_bytes);
+                dev::store_message(cs, hs, a.peers, s, a.buffer_offset, a.buffer_bytes, bl.offset(group, token), stage, token_bytes, kSitePush);
             }
             ptx::bulk_commit();
         }

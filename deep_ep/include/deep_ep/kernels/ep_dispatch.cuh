@@ -18,7 +18,7 @@ namespace deep_ep::kernels {
 namespace dispatch_detail {
 
 constexpr int kSiteEntryBarrier = 10, kSiteGridSync1 = 11, kSiteRankCount = 12, kSiteExpertCount = 13,
-              kSiteLoad = 14, kSiteArrival = 15;
+              kSiteLoad = 14, kSiteArrival = 15, kSitePush = 16;
 
 struct Smem {
     uint64_t* mbar;          // [W][S + 2]  (S message stages + 2 quantiser source stages)
@@ -423,11 +423,10 @@ EP_DEVICE void ep_dispatch_body(const DispatchArgs& a) {
         }
 
         // ---- one bulk store per destination rank, issued by the lane that owns the slot
-        if (my_slot >= 0 and my_slot < a.num_max_tokens) {
-            uint8_t* dst = a.peers.base[my_rank] + a.buffer_offset +
-                           layout::BufferLayout(token_bytes, num_ranks, a.num_max_tokens).offset(rank, my_slot);
-            ptx::bulk_store(dst, stage, token_bytes);
-        }
+        if (my_slot >= 0 and my_slot < a.num_max_tokens)
+            dev::store_message(cs, hs, a.peers, my_rank, a.buffer_offset, a.buffer_bytes,
+                               layout::BufferLayout(token_bytes, num_ranks, a.num_max_tokens).offset(rank, my_slot), stage,
+                               token_bytes, kSitePush);
         ptx::bulk_commit();
     }
 

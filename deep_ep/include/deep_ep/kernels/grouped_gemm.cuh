@@ -57,30 +57,70 @@ EP_DEVICE Tile locate_tile(const GroupedGemmArgs& a, const int* prefix, int tile
     return t;
 }
 
-// fp32 weight-gradient row of a tile: `out[0, 32 * num_chunks)` = accumulator columns, plus the previous contents of `out`
-// with `accumulate`. Read-modify-write one 32-column chunk after the other would be a chain of dependent round trips to
-// memory (and with few rows per expert the tile's MMAs are far shorter than that chain), so the previous contents are
-// fetched ahead of their use: `WgradRow::prefetch` is called BEFORE the wait for the accumulator and requests the first
-// two chunks, `finish` requests chunk i + 2 while it adds and stores chunk i.
-struct WgradRow {
-    static constexpr int kMaxChunks = 8, kAhead = 2;
-    int4 old[kAhead + 1][8];
+// fp32 weight-gradient tiles leave the CTA through shared memory and the TMA. An epilogue thread holds one accumulator row
+// (`tcgen05.ld` 32x32b), so a warp-wide store from registers would touch 32 different rows, 16 bytes each, per instruction,
+// and with `accumulate` every 16 bytes would also be a round trip for the previous contents. Instead each warp writes its
+// 32 rows x 32 columns chunk (4 KB) into a staging buffer, laid out in the 128-byte swizzle the tensor map expects (which
+// also makes the writes bank-conflict free), and one lane hands it to the TMA: a plain tiled store, or a tiled
+// reduce-add (`cp.reduce.async.bulk.tensor ... .add`) that performs the fp32 accumulation at the memory side with no
+// load in the SM at all. Two buffers per warp alternate; a buffer is reused once the copy that read it has done so.
+struct WgradStaging {
+    static constexpr int kChunkBytes = 32 * 128;          // 32 rows x 32 fp32 (or x 64 bf16)
+    uint8_t* buffers;                                     // this warp's chunk buffers (1024-byte aligned)
+    int num_buffers = 2;                                  // 1 or 2
+    unsigned issued = 0;
 
-    EP_DEVICE void fetch(const float* out, int chunk, int slot) {
+    // one chunk: wait until the buffer is free, write `units[8]` (the row's 128 bytes) swizzled, hand it to the TMA
+    EP_DEVICE void push(const CUtensorMap* map_d, const uint4 (&units)[8], int x, int y, bool accumulate, int lane) {
+        uint8_t* buffer = buffers + (num_buffers == 2 ? (issued & 1) : 0) * kChunkBytes;
+        // the copy that last read this buffer has done so (lane 0 owns the bulk groups)
+        if (lane == 0) {
+            if (num_buffers == 2) ptx::bulk_wait_read<1>();
+            else ptx::bulk_wait_read<0>();
+        }
+        __syncwarp();
         #pragma unroll
-        for (int v = 0; v < 8; ++v) old[slot][v] = ptx::ld_v4(out + 32 * chunk + 4 * v);
+        for (int v = 0; v < 8; ++v)             // 16-byte unit v of row `lane` sits at unit v ^ (row % 8) of its 128-byte line
+            *reinterpret_cast<uint4*>(buffer + lane * 128 + ((v ^ (lane & 7)) << 4)) = units[v];
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            if (accumulate) tc::tma_reduce_add_2d(map_d, x, y, buffer);
+            else tc::tma_store_2d(map_d, x, y, buffer);
+            ptx::bulk_commit();
+        }
+        ++issued;
     }
-    EP_DEVICE void prefetch(const float* out, int num_chunks, bool accumulate) {
-        if (not accumulate) return;
-        #pragma unroll
-        for (int i = 0; i < kAhead; ++i)
-            if (i < num_chunks) fetch(out, i, i);
+
+    // bf16 rows: `num_chunks` chunks of 64 columns; rows whose `valid` is false are written as zeros
+    EP_DEVICE void store_rows_bf16(const CUtensorMap* map_d, uint32_t taddr, int num_chunks, int x0, int y0, bool has_accumulator,
+                                   bool valid, int lane) {
+        for (int i = 0; i < num_chunks; ++i) {
+            uint32_t lo[32], hi[32];
+            if (has_accumulator) {
+                tc::tmem_ld_32x32(taddr + 64 * i, lo);
+                tc::tmem_ld_32x32(taddr + 64 * i + 32, hi);
+                tc::wait_ld();
+            }
+            uint4 units[8];
+            #pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                uint32_t* w = reinterpret_cast<uint32_t*>(&units[v]);
+                uint32_t* w2 = reinterpret_cast<uint32_t*>(&units[4 + v]);
+                #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const bool keep = valid and has_accumulator;
+                    w[j] = keep ? ptx::float2_to_bf16x2(__uint_as_float(lo[8 * v + 2 * j]), __uint_as_float(lo[8 * v + 2 * j + 1])) : 0u;
+                    w2[j] = keep ? ptx::float2_to_bf16x2(__uint_as_float(hi[8 * v + 2 * j]), __uint_as_float(hi[8 * v + 2 * j + 1])) : 0u;
+                }
+            }
+            push(map_d, units, x0 + 64 * i, y0, false, lane);
+        }
     }
-    EP_DEVICE void finish(float* out, uint32_t taddr, int num_chunks, bool has_accumulator, bool accumulate) {
-        #pragma unroll
-        for (int i = 0; i < kMaxChunks; ++i) {
-            if (i >= num_chunks) break;
-            if (accumulate and i + kAhead < num_chunks) fetch(out, i + kAhead, (i + kAhead) % (kAhead + 1));
+
+    EP_DEVICE void store_rows(const CUtensorMap* map_d, uint32_t taddr, int num_chunks, int x0, int y0, bool has_accumulator,
+                              bool accumulate, int lane) {
+        for (int i = 0; i < num_chunks; ++i) {
             uint32_t r[32];
             if (has_accumulator) {
                 tc::tmem_ld_32x32(taddr + 32 * i, r);
@@ -89,18 +129,16 @@ struct WgradRow {
                 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = 0;
             }
+            uint4 units[8];
             #pragma unroll
-            for (int v = 0; v < 8; ++v) {
-                float4 val = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                         __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                if (accumulate) {
-                    const int4& before = old[i % (kAhead + 1)][v];
-                    val.x += __int_as_float(before.x), val.y += __int_as_float(before.y);
-                    val.z += __int_as_float(before.z), val.w += __int_as_float(before.w);
-                }
-                *reinterpret_cast<float4*>(out + 32 * i + 4 * v) = val;
-            }
+            for (int v = 0; v < 8; ++v) units[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            push(map_d, units, x0 + 32 * i, y0, accumulate, lane);
         }
+    }
+    // every copy has been performed (call before the kernel ends)
+    EP_DEVICE void drain(int lane) {
+        if (lane == 0) ptx::bulk_wait<0>();
+        __syncwarp();
     }
 };
 
@@ -135,7 +173,7 @@ EP_DEVICE void load_k_block(const GroupedGemmArgs& a, const CUtensorMap& map_a, 
 
 __global__ void __launch_bounds__(192, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ GroupedGemmArgs a) {
+                    const __grid_constant__ CUtensorMap map_d, const __grid_constant__ GroupedGemmArgs a) {
     using namespace gemm_detail;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[kGemmMaxStages], empty_bar[kGemmMaxStages], tmem_full_bar[2], tmem_empty_bar[2];
@@ -242,20 +280,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int row = quarter * 32 + lane;
         int local_tile = 0;
         bool stored_remotely = false;
+        // results that leave through the TMA: staging buffers of this warp behind the operand ring (see WgradStaging)
+        WgradStaging staging;
+        staging.num_buffers = max(a.staging_buffers, 1);
+        staging.buffers = smem_b + size_t(S) * b_bytes + size_t(quarter) * staging.num_buffers * WgradStaging::kChunkBytes;
+        const bool use_tma = a.staging_buffers > 0;
         for (int tile = blockIdx.x; tile < num_tiles and not error_flag; tile += gridDim.x, ++local_tile) {
             const Tile t = locate_tile(a, tile_prefix, tile);
             const int acc = local_tile & 1, use = local_tile >> 1;
-            // fp32 weight gradients: the previous contents of this thread's output row are requested before the wait
             const bool wgrad_fp32 = a.mode == kModeWgrad and not a.out_bf16;
-            const size_t wgrad_index = wgrad_fp32 ? (size_t(t.expert) * a.m + t.m0 + row) * a.n + t.n0 : 0;
-            WgradRow wgrad_row;
-            if (wgrad_fp32) wgrad_row.prefetch(reinterpret_cast<const float*>(a.d) + wgrad_index, BN / 32, a.accumulate);
             if (not ptx::mbarrier_wait(&tmem_full_bar[acc], use & 1)) { error_flag = 1; break; }
             tc::fence_after_thread_sync();
             const uint32_t taddr = tmem_base + acc * 256 + (uint32_t(quarter * 32) << 16);
             const bool valid = row < t.rows_valid;
             if (wgrad_fp32) {
-                wgrad_row.finish(reinterpret_cast<float*>(a.d) + wgrad_index, taddr, BN / 32, t.num_k_blocks > 0, a.accumulate);
+                staging.store_rows(&map_d, taddr, BN / 32, t.n0, t.expert * a.m + t.m0 + quarter * 32, t.num_k_blocks > 0,
+                                   a.accumulate, lane);
+            } else if (a.mode == kModeWgrad and use_tma) {
+                staging.store_rows_bf16(&map_d, taddr, BN / 64, t.n0, t.expert * a.m + t.m0 + quarter * 32, t.num_k_blocks > 0, true, lane);
             } else if (a.mode == kModeWgrad) {
                 const size_t out_index = (size_t(t.expert) * a.m + t.m0 + row) * a.n + t.n0;
                 __nv_bfloat16* out16 = reinterpret_cast<__nv_bfloat16*>(a.d) + out_index;
@@ -311,6 +353,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
                 }
+            } else if (use_tma and a.route == nullptr and not a.out_fp32 and quarter * 32 + 32 <= t.rows_written) {
+                // all 32 rows of this warp are written (values, or zeros for padding rows): whole chunks through the TMA
+                staging.store_rows_bf16(&map_d, taddr, BN / 64, t.n0, t.row_base + t.m0 + quarter * 32, true, valid, lane);
             } else {
                 __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + size_t(t.row_base + t.m0 + row) * a.n_out + t.n0;
                 if (a.route != nullptr and valid) {
@@ -349,6 +394,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (lane == 0) ptx::mbarrier_arrive(&tmem_empty_bar[acc]);
         }
         if (stored_remotely) __threadfence_system();     // peer stores are performed before the kernel completes
+        staging.drain(lane);
     }
 
     // ---- teardown: every thread arrives here, then the allocating warp frees tensor memory

@@ -53,7 +53,7 @@ EP_DEVICE Tile locate_tile(const GroupedGemmArgs& a, const int* prefix, int tile
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         const __grid_constant__ GroupedGemmArgs a) {
+                         const __grid_constant__ CUtensorMap map_d, const __grid_constant__ GroupedGemmArgs a) {
     using namespace gemm2_detail;
     using gemm_detail::silu;
     extern __shared__ uint8_t smem_raw[];
@@ -189,20 +189,26 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int row = quarter * 32 + lane;                       // row inside this CTA's 128-row half
         int local_tile = 0;
         bool stored_remotely = false;
+        // fp32 weight gradients: two staging buffers per warp behind the operand ring (see gemm_detail::WgradStaging)
+        gemm_detail::WgradStaging staging;
+        staging.num_buffers = max(a.staging_buffers, 1);
+        staging.buffers = smem_b + size_t(S) * kHalfBytes + size_t(quarter) * staging.num_buffers * gemm_detail::WgradStaging::kChunkBytes;
+        const bool use_tma = a.staging_buffers > 0;
         for (int tile = pair; tile < num_tiles and not error_flag; tile += num_pairs, ++local_tile) {
             const Tile t = locate_tile(a, tile_prefix, tile);
             const int acc = local_tile & 1, use = local_tile >> 1;
             const int m = t.m0 + 128 * int(cta_rank) + row;        // row inside the expert's region (or of the per-expert output)
-            // fp32 weight gradients: the previous contents of this thread's output row are requested before the wait
             const bool wgrad_fp32 = a.mode == kModeWgrad and not a.out_bf16;
             const size_t wgrad_index = a.mode == kModeWgrad ? (size_t(t.expert) * a.m + m) * a.n + t.n0 : 0;
-            gemm_detail::WgradRow wgrad_row;
-            if (wgrad_fp32) wgrad_row.prefetch(reinterpret_cast<const float*>(a.d) + wgrad_index, kPairN / 32, a.accumulate);
             if (not ptx::mbarrier_wait(&tmem_full_bar[acc], use & 1)) { error_flag = 1; break; }
             tc::fence_after_thread_sync();
             const uint32_t taddr = tmem_base + acc * 256 + (uint32_t(quarter * 32) << 16);
             if (wgrad_fp32) {
-                wgrad_row.finish(reinterpret_cast<float*>(a.d) + wgrad_index, taddr, kPairN / 32, t.num_k_blocks > 0, a.accumulate);
+                staging.store_rows(&map_d, taddr, kPairN / 32, t.n0, t.expert * a.m + t.m0 + 128 * int(cta_rank) + quarter * 32,
+                                   t.num_k_blocks > 0, a.accumulate, lane);
+            } else if (a.mode == kModeWgrad and use_tma) {
+                staging.store_rows_bf16(&map_d, taddr, kPairN / 64, t.n0, t.expert * a.m + t.m0 + 128 * int(cta_rank) + quarter * 32,
+                                        t.num_k_blocks > 0, true, lane);
             } else if (a.mode == kModeWgrad) {
                 __nv_bfloat16* out16 = reinterpret_cast<__nv_bfloat16*>(a.d) + wgrad_index;
                 for (int c = 0; c < kPairN; c += 32) {
@@ -258,6 +264,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                             }
                         }
                     }
+                } else if (use_tma and a.route == nullptr and t.m0 + 128 * int(cta_rank) + quarter * 32 + 32 <= t.aligned_count) {
+                    // all 32 rows of this warp are written (values, or zeros for padding rows): whole chunks through the TMA
+                    staging.store_rows_bf16(&map_d, taddr, kPairN / 64, t.n0, t.row_base + t.m0 + 128 * int(cta_rank) + quarter * 32,
+                                            true, valid, lane);
                 } else {
                     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.d) + grow * a.n_out + t.n0;
                     if (a.route != nullptr and valid) {
@@ -287,6 +297,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             if (lane == 0) tc::mbarrier_arrive_cluster(tc::map_to_cta(&tmem_empty_bar[acc], 0));
         }
         if (stored_remotely) __threadfence_system();     // peer stores are performed before the kernel completes
+        staging.drain(lane);
     }
 
     // ---- teardown: no CTA leaves while its partner may still signal its barriers or read its shared memory

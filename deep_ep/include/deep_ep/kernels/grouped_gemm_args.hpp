@@ -27,6 +27,7 @@ struct GroupedGemmArgs {
     int block_n_out;          // output columns per tile
     int num_stages;
     int out_bf16;             // wgrad: 1 = d is bf16 (overwrite only), 0 = d is fp32
+    int staging_buffers;      // chunk buffers per epilogue warp for results that leave through the TMA (0 = none: register stores)
     int out_fp32;             // forward / dgrad with the plain-store epilogue: 1 = d is fp32 [rows, n_out] (single-CTA kernel only)
     int accumulate;           // wgrad: 1 = add to the existing contents of d, 0 = overwrite (experts without rows get zeros)
     void* d;                  // bf16 [rows, n_out] (forward/dgrad) or fp32 [G, m, n] accumulated into (wgrad)

@@ -45,6 +45,13 @@ struct BufferLayout {
     EP_HOST_DEVICE int64_t num_bytes() const { return offset(num_groups, 0); }
 };
 
+// `[offset, offset + bytes)` lies inside the landing area `[0, area_bytes)` and obeys the bulk-copy rule (16-byte aligned
+// start and size). Used by the bounds-checked build of the kernels (`EP_DEBUG`) and testable on the host.
+EP_HOST_DEVICE bool landing_range_ok(int64_t offset, int64_t bytes, int64_t area_bytes) {
+    return offset >= 0 and bytes > 0 and offset + bytes <= area_bytes and offset % kBulkAlignmentBytes == 0 and
+           bytes % kBulkAlignmentBytes == 0;
+}
+
 // Count words that cross ranks carry the call's epoch in the high half so that nothing has to be
 // cleared between calls: `[epoch:32 | value:32]`.
 EP_HOST_DEVICE uint64_t pack_tagged(uint32_t epoch, uint32_t value) {

@@ -116,3 +116,19 @@ def test_specialised_ep_kernels_match_generic_bitwise(master_port, tmp_path):
     from dist_utils import run_distributed
     world = min(torch.cuda.device_count(), 2)
     run_distributed(_specialised_worker, world, master_port, 'nccl', (str(tmp_path),))
+
+
+def test_bounds_checked_build_compiles_and_its_predicate(tmp_path, monkeypatch):
+    """`EP_DEBUG=1` makes the run-time compiler build the kernels with their bounds checks (a different cubin from the
+    plain build), and the predicate those checks apply accepts exactly the aligned ranges inside the landing area."""
+    import deep_ep
+    monkeypatch.setenv('EP_JIT_CACHE_DIR', str(tmp_path))
+    source = deep_ep._C.jit_specialized_source('dispatch', 2, 4, 1024, 16)
+    plain = deep_ep._C.jit_compile('ep_dispatch_dbg_test', source)
+    monkeypatch.setenv('EP_DEBUG', '1')
+    checked = deep_ep._C.jit_compile('ep_dispatch_dbg_test', source)
+    assert plain != checked and os.path.getsize(checked) > os.path.getsize(plain)
+    ok = deep_ep._C.landing_range_ok
+    assert ok(0, 7456, 7456 * 4) and ok(7456 * 3, 7456, 7456 * 4)
+    assert not ok(7456 * 3 + 16, 7456, 7456 * 4)          # runs past the end
+    assert not ok(-16, 32, 1024) and not ok(8, 32, 1024) and not ok(0, 24, 1024) and not ok(0, 0, 1024)

@@ -14,7 +14,7 @@ def test_public_constants():
     assert deep_ep.get_num_allocation_alignment() == 2 << 20
     assert deep_ep.get_num_rdma_alignment() == 32 and deep_ep.get_num_tma_alignment() == 32
     assert deep_ep.topk_idx_t == torch.int64
-    assert deep_ep.__version__ == '1.0.0'
+    assert deep_ep.__version__.split('+')[0] == '1.0.0'      # the build appends '+<source revision>'
 
 
 def test_math_helpers():
