@@ -61,7 +61,13 @@ def engram(args, group, rank, world, out):
         tables = [torch.randn(n, hidden, device='cuda', dtype=torch.bfloat16) for n in entries]
         if use_fp8:
             quant = [per_token_cast_to_fp8(t) for t in tables]
-            buf.write([q for q, _ in quant], [s.view(torch.int16) for _, s in quant])
+            # the tables are sharded over the ranks, their scale factors are replicated: every rank passes all of them
+            def everyone(t):              # as bytes: the collective library has no 16-bit integer type
+                raw = t.contiguous().view(torch.uint8)
+                parts = [torch.empty_like(raw) for _ in range(world)]
+                dist.all_gather(parts, raw)
+                return torch.cat(parts).view(t.dtype)
+            buf.write([q for q, _ in quant], [everyone(s.view(torch.int16)) for _, s in quant])
         else:
             buf.write(tables)
         del tables
@@ -103,9 +109,21 @@ def barrier_latency(args, group, rank, world, out):
     per_call_us = max_over_ranks(a.elapsed_time(b) * 1e3 / n)
     profile = bench_kineto(lambda: [buffer.barrier() for _ in range(100)], kernel_names='rank_barrier', num_warmups=1, num_tests=5,
                            flush_l2=False, barrier=buffer.barrier)
-    out.append({'bench': 'barrier', 'n_gpus': world, 'barriers': n, 'us_per_barrier_back_to_back': round(per_call_us, 3),
+    # the barrier's own latency: n barriers inside ONE kernel launch (every rank passes the same count)
+    def in_kernel():
+        deep_ep._C.barrier(buffer.context, False, True, False, n)
+    in_kernel()
+    torch.cuda.synchronize()
+    dist.barrier()
+    a.record()
+    in_kernel()
+    b.record()
+    torch.cuda.synchronize()
+    in_kernel_us = max_over_ranks(a.elapsed_time(b) * 1e3 / n)
+    out.append({'bench': 'barrier', 'n_gpus': world, 'barriers': n, 'us_per_barrier_in_one_kernel': round(in_kernel_us, 3),
+                'us_per_barrier_back_to_back': round(per_call_us, 3),
                 'kernel_us': round(max_over_ranks(profile.us), 3),
-                'what': 'back-to-back: events around 1000 launches / 1000 (launch-bound on the host when the kernel is shorter '
+                'what': 'in_one_kernel: 1000 barriers executed by one launch / 1000 (the device-side latency of a barrier); back-to-back: events around 1000 launches / 1000 (launch-bound on the host when the kernel is shorter '
                         'than a launch); kernel_us: device time of one barrier kernel from the activity records'})
     buffer.destroy()
 

@@ -11,12 +11,14 @@
 
 namespace deep_ep::comm {
 
-inline void barrier(Context& context, bool with_cpu_sync = false, bool sequential = true, bool wait_comm_stream = true) {
+inline void barrier(Context& context, bool with_cpu_sync = false, bool sequential = true, bool wait_comm_stream = true,
+                    int repeats = 1) {
     (void) sequential;   // accepted for API parity; the kernel is always a single ordered barrier
     EP_HOST_ASSERT(context.peers_ready and context.common_signals != nullptr);
     const auto stream = c10::cuda::getCurrentCUDAStream();
     if (wait_comm_stream) stream_wait(stream, get_comm_stream());
-    kernels::BarrierArgs args = {context.common_signals, context.host_status_device, context.peers, context.num_gpu_timeout_ns};
+    EP_HOST_ASSERT(repeats >= 1);
+    kernels::BarrierArgs args = {context.common_signals, context.host_status_device, context.peers, context.num_gpu_timeout_ns, repeats};
     launch::barrier(args, stream);
     if (wait_comm_stream) stream_wait(get_comm_stream(), stream);
     if (with_cpu_sync) {

@@ -338,9 +338,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("clear_status", &clear_status)
         .def("bounded_wait_probe", &run_bounded_wait_probe);
 
-    m.def("barrier", [](comm::Context& context, bool with_cpu_sync, bool sequential, bool wait_comm_stream) {
-        comm::barrier(context, with_cpu_sync, sequential, wait_comm_stream);
-    }, py::arg("context"), py::arg("with_cpu_sync") = false, py::arg("sequential") = true, py::arg("wait_comm_stream") = true);
+    m.def("barrier", [](comm::Context& context, bool with_cpu_sync, bool sequential, bool wait_comm_stream, int repeats) {
+        comm::barrier(context, with_cpu_sync, sequential, wait_comm_stream, repeats);
+    }, py::arg("context"), py::arg("with_cpu_sync") = false, py::arg("sequential") = true, py::arg("wait_comm_stream") = true,
+       py::arg("repeats") = 1);
     m.def("get_comm_stream", [] {
         const auto s = comm::get_comm_stream();
         return py::make_tuple(s.id(), static_cast<int>(s.device_index()), static_cast<int>(s.device_type()));

@@ -56,13 +56,16 @@ public:
         const auto* k = info(kernel);
         EP_HOST_ASSERT_MSG(k != nullptr, "unknown kernel " + kernel);
         std::ostringstream out;
+        // the reduce epilogue has two register budgets (see ep_combine.cuh): three CTAs per SM, or two for its few-rows variant
+        const bool few_rows = std::min(shape.num_topk, shape.num_ranks) <= 2;
+        const std::string bounds = kernel == "reduce" ? (few_rows ? "32 * 8, 2" : "32 * 8, 3") : k->launch_bounds;
         out << "#include <deep_ep/kernels/" << k->header << ">\n"
-            << "extern \"C\" __global__ void __launch_bounds__(" << k->launch_bounds << ") ep_specialized(\n"
+            << "extern \"C\" __global__ void __launch_bounds__(" << bounds << ") ep_specialized(\n"
             << "        const __grid_constant__ deep_ep::kernels::" << k->args_type << " a) {\n"
             << "    deep_ep::kernels::" << k->body << "<" << shape.num_ranks << ", " << shape.num_topk << ", " << shape.hidden_bytes;
         if (k->with_experts) out << ", " << shape.num_experts;
         // the reduce body also takes "a token has at most two partials" (see ep_combine.cuh)
-        if (kernel == "reduce") out << ", " << (std::min(shape.num_topk, shape.num_ranks) <= 2 ? "true" : "false");
+        if (kernel == "reduce") out << ", " << (few_rows ? "true" : "false");
         out << ">(a);\n}\n";
         return out.str();
     }

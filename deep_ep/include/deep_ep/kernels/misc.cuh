@@ -15,7 +15,10 @@ namespace deep_ep::kernels {
 // ---------------------------------------------------------------------------------------- barrier
 __global__ void __launch_bounds__(32) rank_barrier_kernel(const __grid_constant__ BarrierArgs a) {
     if (not dev::healthy(a.cs)) return;
-    dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, /*where=*/1);
+    // `repeats` > 1: that many barriers back to back inside one launch, which is how the barrier's own latency is timed
+    // (a loop of launches measures the host's launch rate instead); every rank must pass the same count
+    for (int i = 0; i < max(a.repeats, 1); ++i)
+        if (not dev::rank_barrier_warp(a.cs, a.host_status, a.peers, a.timeout_ns, /*where=*/1)) return;
 }
 
 // ---------------------------------------------------------------------------------------- engram

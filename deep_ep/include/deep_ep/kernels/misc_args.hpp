@@ -13,6 +13,7 @@ struct BarrierArgs {
     layout::HostStatus* host_status;
     layout::PeerTable peers;
     long long timeout_ns;
+    int repeats;              // barriers executed by this launch (1 = a barrier; more = latency measurement)
 };
 
 struct EngramFetchArgs {
