@@ -60,6 +60,9 @@ EP_DEVICE void red_add_release_sys(int* p, int v) {
 EP_DEVICE void red_add_release_sys(unsigned long long* p, unsigned long long v) {
     asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+EP_DEVICE void red_add_relaxed_sys(int* p, int v) {
+    asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 EP_DEVICE void red_xor_relaxed_sys(unsigned int* p, unsigned int v) {
     asm volatile("red.relaxed.sys.global.xor.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

@@ -105,12 +105,15 @@ EP_DEVICE bool rank_barrier_warp(layout::CommonSignals* cs, layout::HostStatus* 
     if (lane == 0) n = cs->barrier_counter;
     n = __shfl_sync(0xffffffffu, n, 0);
     const int phase = n & 1, sign = (n & 2) ? -1 : 1;
+    // One system-scope fence releases everything ordered before this call; the arrivals that follow it can then be relaxed
+    // (fence + relaxed atomic is a release). A `red.release` per peer would repeat that fence once per lane, and each
+    // system-scope fence waits for the acknowledgements of earlier remote writes, a round trip over the links.
     __threadfence_system();
     for (int r = lane; r < peers.num_ranks; r += 32) {
         layout::CommonSignals* peer = peers.sym(cs, r);
         // who arrived (looked at only when the wait below runs out), then the arrival itself
         ptx::red_xor_relaxed_sys(&peer->barrier_arrived[phase][peers.rank / 32], 1u << (peers.rank % 32));
-        ptx::red_add_release_sys(&peer->barrier_signals[phase], sign);
+        ptx::red_add_relaxed_sys(&peer->barrier_signals[phase], sign);
     }
     const int target = sign > 0 ? peers.num_ranks : 0;
     bool ok = true;
@@ -128,8 +131,10 @@ EP_DEVICE bool rank_barrier_warp(layout::CommonSignals* cs, layout::HostStatus* 
         }
         cs->barrier_counter = n + 1;
     }
+    // lane 0's acquire load of the completed count orders the peers' released writes before everything after the barrier;
+    // the shuffle hands that order to the other lanes, the caller's block-wide sync to the other warps
     ok = __shfl_sync(0xffffffffu, ok, 0);
-    __threadfence_system();
+    ptx::fence_acq_rel_gpu();
     return ok;
 }
 

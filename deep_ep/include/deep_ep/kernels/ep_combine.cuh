@@ -230,9 +230,13 @@ EP_DEVICE void ep_combine_body(const CombineArgs& a) {
     // Decode-sized calls leave most warps without a row while the few busy ones walk through a row in a dozen
     // dependent round trips. With `coop`, P warps of a CTA (a power of two, the same in the whole CTA) share every
     // row: each reduces 1/P of the 16-byte chunks into the group's stage and the group's first warp sends it.
+    // all received rows, and the first row of the source after this rank (where this rank starts, so that the ranks of a
+    // node begin with different destinations)
+    const int total_rows = min(psum_rank_smem[num_ranks - 1], a.num_metadata_rows);
+    const int next_rank = (rank + 1) % num_ranks;
+    const int first_row = total_rows > 0 ? (next_rank == 0 ? 0 : min(psum_rank_smem[next_rank - 1], total_rows)) % total_rows : 0;
     int P = 1;
     if (a.coop) {
-        const int total_rows = min(psum_rank_smem[num_ranks - 1], a.num_metadata_rows);
         while (2 * P <= W and W % (2 * P) == 0 and int64_t(total_rows) * (2 * P) <= num_gw) P *= 2;
     }
     if (P > 1) {
@@ -241,11 +245,12 @@ EP_DEVICE void ep_combine_body(const CombineArgs& a) {
         uint8_t* group_stages = base + math::align<int64_t>(int64_t(W) * S * 8, 128) + int64_t(group * P) * S * token_bytes;
         const int c_begin = chunks * part / P, c_end = chunks * (part + 1) / P;
         const int bar_id = 1 + group, bar_threads = 32 * P;
-        for (int q = 0; q < num_ranks; ++q) {
-            const int s = (rank + 1 + gg + q) % num_ranks;
-            const int begin = s == 0 ? 0 : psum_rank_smem[s - 1];
-            const int end = min(psum_rank_smem[s], a.num_metadata_rows);
-            for (int row = begin + gg; row < end; row += num_gg, ++n) {
+        // rows are scarce here: one flat walk over all received rows (see the note at the loop of the other path)
+        for (int i = gg; i < total_rows; i += num_gg, ++n) {
+            const int row = (i + first_row) % total_rows;
+            int s = 0;
+            while (s < num_ranks - 1 and row >= psum_rank_smem[s]) ++s;
+            {
                 // every warp of the group reads the same metadata and therefore takes the same branches
                 uint8_t* stage = group_stages + (n % S) * token_bytes;
                 const int my_slot = lane < k ? a.recv_src_metadata[int64_t(row) * meta_cols + lane] : -1;
@@ -306,13 +311,24 @@ EP_DEVICE void ep_combine_body(const CombineArgs& a) {
         }
     }
 
-    for (int q = 0; q < num_ranks and not failed and P == 1; ++q) {
-        // visit sources in an order rotated by rank and warp so that, at any moment, the ranks of
-        // the node spread their pushes over all destinations instead of converging on one
-        const int s = (rank + 1 + gw + q) % num_ranks;
-        const int begin = s == 0 ? 0 : psum_rank_smem[s - 1];
-        const int end = min(psum_rank_smem[s], a.num_metadata_rows);
-        for (int row = begin + gw; row < end; row += num_gw, ++n) {
+    // Two ways to hand rows to warps. Plenty of rows (bandwidth-bound calls): every warp visits the sources in an order
+    // rotated by rank and warp and takes every `num_gw`-th row of each, so that at any moment the ranks of the node spread
+    // their pushes over all destinations. Few rows (decode-sized calls): that scheme gives the first warps one row PER
+    // SOURCE, eight rows one after the other, while most warps have none; a flat walk over all rows gives every warp at
+    // most a few.
+    const bool flat_walk = total_rows <= 4 * num_gw;
+    const int num_outer = flat_walk ? 1 : num_ranks;
+    for (int q = 0; q < num_outer and not failed and P == 1; ++q) {
+        const int source = (rank + 1 + gw + q) % num_ranks;
+        const int begin = flat_walk ? 0 : (source == 0 ? 0 : psum_rank_smem[source - 1]);
+        const int end = flat_walk ? total_rows : min(psum_rank_smem[source], a.num_metadata_rows);
+        for (int walk = begin + gw; walk < end; walk += num_gw, ++n) {
+            int row = walk, s = source;
+            if (flat_walk) {
+                row = (walk + first_row) % total_rows;
+                s = 0;
+                while (s < num_ranks - 1 and row >= psum_rank_smem[s]) ++s;
+            }
             const int stage_idx = n % S;
             uint8_t* stage = stages + stage_idx * token_bytes;
             const int my_slot = lane < k ? a.recv_src_metadata[int64_t(row) * meta_cols + lane] : -1;

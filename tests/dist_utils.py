@@ -45,4 +45,15 @@ def _worker(rank, world_size, port, backend, fn, args, timeout_s=None):
 
 def run_distributed(fn, world_size, port, backend='gloo', args=(), timeout_s=None):
     """Run `fn(rank, world_size, *args)` in `world_size` processes; raises if any of them fails."""
-    mp.spawn(_worker, args=(world_size, port, backend, fn, args, timeout_s), nprocs=world_size, join=True)
+    for attempt in range(3):
+        try:
+            mp.spawn(_worker, args=(world_size, port, backend, fn, args, timeout_s), nprocs=world_size, join=True)
+            return
+        except Exception as exc:
+            # the port was free when it was chosen and taken when rank 0 tried to listen on it: take another one
+            if 'EADDRINUSE' not in str(exc) or attempt == 2:
+                raise
+            import socket
+            with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as probe:
+                probe.bind(('127.0.0.1', 0))
+                port = probe.getsockname()[1]
