@@ -293,3 +293,82 @@ def test_grouped_fp8_hardware_scaled_swiglu_chain():
         assert err <= 0.07 * scale, f'quantised swiglu expert {e}: {err} vs {scale}'
         ref_y = act_deq[s:s + c] @ w2_deq[e].t()
         assert torch.allclose(y[s:s + c].float(), ref_y, atol=1e-2 * ref_y.abs().max().item(), rtol=1e-2), f'ffn expert {e}'
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('rows', [64, 300, 1024])
+def test_dense_linear_and_dense_ffn_match_torch(rows):
+    """The one-group kernels behind the router and the shared expert: fp32 logits, data and weight gradients of
+    `dense_linear`, and the fused dense SwiGLU FFN, against fp32 PyTorch."""
+    from deep_ep.ops.dense import dense_linear, dense_swiglu_ffn
+    torch.manual_seed(rows)
+    dev = torch.device('cuda')
+    k, n = 512, 256
+    x = (torch.randn(rows, k, device=dev) * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(n, k, device=dev) * 0.1).to(torch.bfloat16).requires_grad_()
+    y = dense_linear(x, w, out_fp32=True)
+    assert y.dtype == torch.float32 and y.shape == (rows, n)
+    ref = x.detach().float() @ w.detach().float().t()
+    assert torch.allclose(y, ref, atol=1e-3 * ref.abs().max().item(), rtol=1e-3)        # fp32 accumulator, not rounded to bf16
+    dy = torch.randn(rows, n, device=dev)
+    y.backward(dy)
+    dyb = dy.to(torch.bfloat16).float()
+    ref_dx, ref_dw = dyb @ w.detach().float(), dyb.t() @ x.detach().float()
+    assert torch.allclose(x.grad.float(), ref_dx, atol=2e-2 * ref_dx.abs().max().item(), rtol=2e-2)
+    assert torch.allclose(w.grad.float(), ref_dw, atol=2e-2 * ref_dw.abs().max().item(), rtol=2e-2)
+    # dense SwiGLU FFN (rows that are no multiple of 128 are padded inside)
+    inter = 256
+    w1 = (torch.randn(2 * inter, k, device=dev) * 0.1).to(torch.bfloat16).requires_grad_()
+    w2 = (torch.randn(k, inter, device=dev) * 0.1).to(torch.bfloat16).requires_grad_()
+    x2 = x.detach().clone().requires_grad_()
+    out = dense_swiglu_ffn(x2, w1, w2)
+    g, u = (x2.detach().float() @ w1.detach().float().t()).chunk(2, dim=-1)
+    ref_out = (torch.nn.functional.silu(g) * u) @ w2.detach().float().t()
+    assert out.shape == (rows, k)
+    assert torch.allclose(out.float(), ref_out, atol=3e-2 * ref_out.abs().max().item(), rtol=3e-2)
+    out.backward(torch.ones_like(out))
+    assert torch.isfinite(x2.grad.float()).all() and torch.isfinite(w1.grad.float()).all() and torch.isfinite(w2.grad.float()).all()
+
+
+@pytest.mark.gpu
+def test_unfused_ffn_with_alignment_64_survives_poisoned_padding():
+    """Expert alignment 64 takes the un-fused autograd path (two `GroupedLinear` nodes). Its intermediate tensors come from
+    `torch.empty`; the tensor-core weight gradient reads whole 64-row blocks, padding included, so the padding rows of every
+    intermediate must have been written as zeros. The allocator is seeded with NaN blocks first, so that a row that was
+    left unwritten shows up as a NaN in a weight gradient."""
+    from deep_ep.ops import grouped_gemm as gg
+    torch.manual_seed(3)
+    dev = torch.device('cuda')
+    counts, alignment, hidden, inter = [70, 1, 0, 130, 64], 64, 256, 128
+    psum, count, rows, starts = make_layout(counts, alignment, dev)
+    g = len(counts)
+    x = torch.zeros(rows, hidden, device=dev, dtype=torch.bfloat16)
+    for s, c in zip(starts, counts):
+        x[s:s + c] = torch.randn(c, hidden, device=dev).to(torch.bfloat16)
+    w1 = (torch.randn(g, 2 * inter, hidden, device=dev) * 0.05).to(torch.bfloat16).requires_grad_()
+    w2 = (torch.randn(g, hidden, inter, device=dev) * 0.05).to(torch.bfloat16).requires_grad_()
+    # blocks of the sizes the layer is about to ask for, filled with NaN and handed back to the caching allocator
+    for cols in (2 * inter, inter, hidden, 2 * inter, inter, hidden):
+        poison = torch.full((rows, cols), float('nan'), device=dev, dtype=torch.bfloat16)
+        del poison
+    xg = x.clone().requires_grad_()
+    y = gg.grouped_swiglu_ffn(xg, w1, w2, psum, count, None, alignment)
+    dy = torch.zeros_like(y)
+    for s, c in zip(starts, counts):
+        dy[s:s + c] = torch.randn(c, hidden, device=dev).to(torch.bfloat16)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    for name, t in (('y', y), ('dx', xg.grad), ('dw_gate_up', w1.grad), ('dw_down', w2.grad)):
+        assert torch.isfinite(t.float()).all(), f'{name} holds a value that came from an unwritten padding row'
+    # against the per-expert fp32 computation
+    w1r, w2r = w1.detach().float().requires_grad_(), w2.detach().float().requires_grad_()
+    xr = x.float().requires_grad_()
+    ref = torch.zeros(rows, hidden, device=dev)
+    for e, (s, c) in enumerate(zip(starts, counts)):
+        if c:
+            gate, up = (xr[s:s + c] @ w1r[e].t()).chunk(2, dim=-1)
+            ref[s:s + c] = (torch.nn.functional.silu(gate) * up) @ w2r[e].t()
+    ref.backward(dy.float())
+    for name, got, want in (('y', y, ref), ('dx', xg.grad, xr.grad), ('dw_gate_up', w1.grad, w1r.grad), ('dw_down', w2.grad, w2r.grad)):
+        scale = want.abs().max().item()
+        assert torch.allclose(got.float(), want.detach(), atol=4e-2 * scale, rtol=4e-2), name
