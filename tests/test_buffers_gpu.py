@@ -426,8 +426,6 @@ def test_pp_send_recv(master_port):
 
 
 @pytest.mark.gpu
-@pytest.mark.skipif(__import__('os').environ.get('EP_TEST_NEW_PATHS', '0') != '1',
-                    reason='path that has not run on a GPU yet; set EP_TEST_NEW_PATHS=1 to try it')
 def test_pp_send_recv_over_nccl_point_to_point(master_port):
     """The same schedule through `PPBuffer(transport='nccl')`."""
     run_distributed(_pp_worker, _world(), master_port, 'nccl', ('nccl',), timeout_s=120)

@@ -50,6 +50,8 @@ def test_allocator_plan_and_materialize():
     a.fill_(1.0)
     assert storage[:60].view(torch.float32).sum() == 15
     assert b.data_ptr() - storage.data_ptr() == 2 << 20
+    assert [offset for _, offset in plan.allocations] == [0, 2 << 20] and plan.allocations[1][0] is b
+    assert 'materialized' in plan.describe() and '(3, 5)' in plan.describe()
     with pytest.raises(AssertionError):
         plan.materialize(storage)
     with pytest.raises(AssertionError):
