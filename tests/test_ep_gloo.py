@@ -175,3 +175,18 @@ def _pending_epilogue_worker(rank, world):
 
 def test_second_operation_is_refused_while_a_deferred_epilogue_is_pending(master_port):
     run_distributed(_pending_epilogue_worker, 2, master_port, 'gloo', timeout_s=120)
+
+
+def _abort_worker(rank, world):
+    import torch.distributed as dist
+    import deep_ep
+    buffer = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=8, hidden=32, num_topk=2, explicitly_destroy=True)
+    buffer.abort(dist.group.WORLD)               # teardown without the collective barrier of destroy()
+    assert buffer.runtime is None
+    buffer.abort()                               # idempotent
+    again = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=8, hidden=32, num_topk=2, explicitly_destroy=True)
+    again.destroy()
+
+
+def test_abort_releases_a_buffer_without_destroy(master_port):
+    run_distributed(_abort_worker, 2, master_port, 'gloo', timeout_s=120)
