@@ -67,6 +67,13 @@ class EPHandle:
         self._topk_idx = topk_idx
         self._topk_idx_version = None if topk_idx.is_inference() else topk_idx._version
 
+    def __setstate__(self, state: dict) -> None:
+        # A handle is plain data and may be pickled (for instance into a checkpoint). The tensor version counter is not
+        # part of a tensor's value: a restored `topk_idx` starts counting again, so the guard is re-armed on it.
+        self.__dict__.update(state)
+        restored = self._topk_idx
+        self._topk_idx_version = None if restored.is_inference() else restored._version
+
     @property
     def topk_idx(self) -> torch.Tensor:
         assert self._topk_idx_version is None or self._topk_idx._version == self._topk_idx_version, \

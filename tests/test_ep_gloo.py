@@ -190,3 +190,29 @@ def _abort_worker(rank, world):
 
 def test_abort_releases_a_buffer_without_destroy(master_port):
     run_distributed(_abort_worker, 2, master_port, 'gloo', timeout_s=120)
+
+
+def _handle_pickle_worker(rank, world):
+    """A routing handle is plain data (integers, lists, tensors): it survives a pickle round trip and still drives a
+    cached dispatch and a combine, which is all a checkpoint of this library's state would have to hold."""
+    import pickle
+    import torch.distributed as dist
+    import deep_ep
+    buffer = deep_ep.EPBuffer(dist.group.WORLD, num_max_tokens_per_rank=16, hidden=32, num_topk=2, explicitly_destroy=True)
+    torch.manual_seed(rank)
+    x = torch.randn(16, 32).to(torch.bfloat16)
+    idx = torch.rand(16, 4 * world).topk(2, dim=-1).indices
+    common = dict(num_experts=4 * world, expert_alignment=1, do_expand=True)
+    recv_x, _, _, handle, _ = buffer.dispatch(x, topk_idx=idx, **common)
+    restored = pickle.loads(pickle.dumps(handle))
+    assert torch.equal(restored.recv_src_metadata, handle.recv_src_metadata) and restored.num_sms == handle.num_sms
+    assert torch.equal(restored.topk_idx, idx)
+    again, _, _, same, _ = buffer.dispatch(x, handle=restored, do_expand=True)
+    assert same is restored and torch.equal(again, recv_x)
+    combined, _, _ = buffer.combine(again, restored)
+    assert torch.allclose(combined.float(), 2 * x.float(), atol=2e-2, rtol=2e-2)
+    buffer.destroy()
+
+
+def test_handles_survive_a_pickle_round_trip(master_port):
+    run_distributed(_handle_pickle_worker, 2, master_port, 'gloo', timeout_s=120)
