@@ -32,9 +32,16 @@ class ParallelMesh:
 
     AXES = ('pp', 'dp', 'ep')
 
-    def __init__(self, ep_size: int = 1, pp_size: int = 1, dp_size: Optional[int] = None, backend: Optional[str] = None):
-        assert dist.is_initialized(), 'initialise torch.distributed first'
-        self.world_size, self.rank = dist.get_world_size(), dist.get_rank()
+    def __init__(self, ep_size: int = 1, pp_size: int = 1, dp_size: Optional[int] = None, backend: Optional[str] = None,
+                 *, world_size: Optional[int] = None, rank: Optional[int] = None):
+        """`world_size` and `rank` are taken from `torch.distributed`; passing both instead gives a layout-only mesh
+        (coordinates and group membership, no process groups), which is what planning tools and tests need."""
+        layout_only = world_size is not None and rank is not None
+        if layout_only:
+            self.world_size, self.rank = world_size, rank
+        else:
+            assert dist.is_initialized(), 'initialise torch.distributed first'
+            self.world_size, self.rank = dist.get_world_size(), dist.get_rank()
         assert ep_size >= 1 and pp_size >= 1 and self.world_size % (ep_size * pp_size) == 0, \
             f'{self.world_size} ranks cannot be split into pp={pp_size} x ep={ep_size}'
         dp_size = self.world_size // (ep_size * pp_size) if dp_size is None else dp_size
@@ -44,7 +51,7 @@ class ParallelMesh:
         for name in self.AXES:
             for ranks in self.groups_of(name):
                 # one-rank groups are created too: the buffers run on them as loop-back groups
-                group = dist.new_group(list(ranks), backend=backend)
+                group = None if layout_only else dist.new_group(list(ranks), backend=backend)
                 if self.rank in ranks:
                     self.axes[name].group, self.axes[name].ranks = group, ranks
 

@@ -199,3 +199,30 @@ def test_build_time_environment_defaults_and_version(tmp_path, monkeypatch):
              'print(os.environ["EP_JIT_CACHE_DIR"], deep_ep.__version__)' % root)
     out = subprocess.check_output([sys.executable, '-c', probe]).decode().split()
     assert out[0] == '/mine' and out[1].startswith('1.0.0')
+
+
+def test_parallel_mesh_layout_partitions_the_world():
+    """For every factorisation of the world, each axis partitions the ranks into equal groups, a rank's three groups meet
+    in that rank alone, EP groups are runs of neighbouring ranks, and coordinates and ranks convert both ways."""
+    from hypothesis import given, settings, strategies as st
+    from deep_ep.parallel import ParallelMesh
+
+    @settings(max_examples=60, deadline=None)
+    @given(st.integers(1, 4), st.integers(1, 4), st.integers(1, 4), st.data())
+    def check(pp, dp, ep, data):
+        world = pp * dp * ep
+        rank = data.draw(st.integers(0, world - 1))
+        mesh = ParallelMesh(ep_size=ep, pp_size=pp, dp_size=dp, world_size=world, rank=rank)
+        mine = {}
+        for axis, size in (('pp', pp), ('dp', dp), ('ep', ep)):
+            groups = mesh.groups_of(axis)
+            assert sorted(r for g in groups for r in g) == list(range(world)) and all(len(g) == size for g in groups)
+            mine[axis] = set(mesh.axes[axis].ranks)
+            assert rank in mine[axis]
+        assert mine['pp'] & mine['dp'] & mine['ep'] == {rank}
+        ep_ranks = sorted(mine['ep'])
+        assert ep_ranks == list(range(ep_ranks[0], ep_ranks[0] + ep))            # neighbours: one NVSwitch domain
+        assert mesh.rank_of(**mesh.coords) == rank and mesh.coords_of(rank) == mesh.coords
+        assert mesh.coords_of(mesh.pp_next())['pp'] == (mesh.coords['pp'] + 1) % pp
+
+    check()
