@@ -226,3 +226,19 @@ def test_parallel_mesh_layout_partitions_the_world():
         assert mesh.coords_of(mesh.pp_next())['pp'] == (mesh.coords['pp'] + 1) % pp
 
     check()
+
+
+def test_type_stubs_match_the_built_extension():
+    """`deep_ep/_C.pyi` is what the stub generator makes of the built extension: a binding that is added or changed
+    without regenerating the stubs fails here. The stubs must also be valid Python."""
+    import ast
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location('generate_pyi', os.path.join(root, 'csrc', 'generate_pyi.py'))
+    generator = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(generator)
+    committed = open(os.path.join(root, 'deep_ep', '_C.pyi')).read()
+    assert generator.generate() == committed, 'run `python csrc/generate_pyi.py`'
+    declared = {node.name for node in ast.parse(committed).body if isinstance(node, (ast.FunctionDef, ast.ClassDef))}
+    assert {'EPBuffer', 'PPBuffer', 'BucketBuffer', 'EngramBuffer', 'Context', 'barrier', 'calculate_ep_buffer_size'} <= declared
