@@ -55,7 +55,7 @@ inline uint64_t fnv1a(const std::string& s, uint64_t h = 1469598103934665603ull)
 
 // Runs `argv` (argv[0] = program path, looked up in PATH when it has no slash) as a child process, standard output and
 // error appended to `log_path`; returns the exit code, or -1 when the process could not be started or was killed.
-inline int run_process(const std::vector<std::string>& argv_text, const std::string& log_path) {
+inline int run_process(const std::vector<std::string>& argv_text, const std::string& log_path, const std::string& working_dir = "") {
     std::vector<char*> argv;
     for (const auto& word : argv_text) argv.push_back(const_cast<char*>(word.c_str()));
     argv.push_back(nullptr);
@@ -63,6 +63,7 @@ inline int run_process(const std::vector<std::string>& argv_text, const std::str
     posix_spawn_file_actions_init(&actions);
     posix_spawn_file_actions_addopen(&actions, 1, log_path.c_str(), O_WRONLY | O_CREAT | O_TRUNC, 0644);
     posix_spawn_file_actions_adddup2(&actions, 1, 2);
+    if (not working_dir.empty()) posix_spawn_file_actions_addchdir_np(&actions, working_dir.c_str());
     pid_t pid = 0;
     const int err = posix_spawnp(&pid, argv[0], &actions, nullptr, argv.data(), environ);
     posix_spawn_file_actions_destroy(&actions);
@@ -142,22 +143,23 @@ public:
         }
         const auto tmp = cubin + ".tmp." + std::to_string(::getpid());
         // the compiler runs as a child process with an argument vector (no shell: paths from the environment may hold
-        // spaces or shell metacharacters), its output goes to `nvcc.log`
+        // spaces or shell metacharacters), its output goes to `nvcc.log`. It runs INSIDE the entry's directory and is given
+        // file names only, because nvcc passes the paths it receives on to its own sub-commands through a shell.
         std::vector<std::string> argv_text = {nvcc_path()};
         {
             std::stringstream words(flags);
             for (std::string word; words >> word;) argv_text.push_back(word);
         }
         argv_text.push_back("-I" + include_dir());
-        argv_text.push_back(dir + "/kernel.cu");
+        argv_text.push_back("kernel.cu");
         argv_text.push_back("-o");
-        argv_text.push_back(tmp);
+        argv_text.push_back(std::filesystem::path(tmp).filename().string());
         if (get_env_flag("PRINT_COMPILER_COMMAND") or get_env_flag("DEBUG")) {
             std::string line;
             for (const auto& word : argv_text) line += word + " ";
             std::fprintf(stderr, "[deep_ep jit] %s\n", line.c_str());
         }
-        const int rc = run_process(argv_text, dir + "/nvcc.log");
+        const int rc = run_process(argv_text, dir + "/nvcc.log", dir);
         if (rc != 0) {
             std::ifstream log(dir + "/nvcc.log");
             std::stringstream text;

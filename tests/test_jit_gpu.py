@@ -60,6 +60,24 @@ def test_jit_cache_searches_every_root_and_writes_the_first(tmp_path):
             os.environ['EP_JIT_CACHE_DIR'] = saved
 
 
+def test_jit_paths_with_spaces_and_shell_characters(tmp_path):
+    """The compiler is started as a process with an argument vector, not through a shell: a cache directory whose name
+    has spaces, quotes and a `;` compiles, and nothing from the name is executed."""
+    import deep_ep
+    root = tmp_path / "cache dir; touch 'owned' $(echo x)"
+    saved = os.environ.get('EP_JIT_CACHE_DIR')
+    try:
+        os.environ['EP_JIT_CACHE_DIR'] = str(root)
+        cubin = deep_ep._C.jit_compile('spaces', 'extern "C" __global__ void k3(int* p) { if (p) p[0] = 3; }\n')
+        assert cubin.startswith(str(root)) and os.path.getsize(cubin) > 0
+        assert not (tmp_path / 'owned').exists() and not os.path.exists('owned')
+    finally:
+        if saved is None:
+            os.environ.pop('EP_JIT_CACHE_DIR', None)
+        else:
+            os.environ['EP_JIT_CACHE_DIR'] = saved
+
+
 @pytest.mark.parametrize('kernel', ['dispatch', 'expand', 'combine', 'reduce'])
 def test_specialised_ep_kernels_cross_compile(kernel, tmp_path):
     """Every shape-specialised EP kernel compiles for sm_100a (no GPU needed) from the three-line translation unit
