@@ -60,6 +60,43 @@ def _bucket_worker(rank, world):
             raise RuntimeError('boom')
     assert bucket.all_gather == original and bucket._active_session is None
 
+    # randomised schedule (reference: `tests/bucket/test_session.py:65-185`): 64 gathers with at most 4 in flight, sizes
+    # and forms mixed (outside destination, no destination, in place inside a session allocation, batches of two);
+    # when the arena runs low the ranks meet at a barrier and the session starts again at offset 0
+    import random
+    rng = random.Random(5)
+    with bucket.session() as session:
+        inflight = []
+
+        def drain():
+            for tag, count, handle in inflight:
+                outs = handle.wait()
+                outs = [outs] if isinstance(outs, torch.Tensor) else outs
+                assert len(outs) == count
+                for k, out in enumerate(outs):
+                    assert torch.equal(out.view(world, -1)[:, -1].float(), torch.arange(world).float() + tag + k)
+            inflight.clear()
+        for i in range(64):
+            n, form = rng.choice([7, 256, 4099]), rng.randrange(4)
+            src = torch.full((n,), float(rank + i), dtype=torch.bfloat16)
+            if form == 0:
+                inflight.append((i, 1, bucket.all_gather(src, torch.empty(world * n, dtype=torch.bfloat16), group=group)))
+            elif form == 1:
+                inflight.append((i, 1, bucket.all_gather(src, group=group)))
+            elif form == 2:
+                full = session.allocate((world, n), torch.bfloat16, group=group)
+                full[rank] = src
+                inflight.append((i, 1, bucket.all_gather(full[rank], group=group)))
+            else:
+                pair = [src, torch.full((n + 3,), float(rank + i + 1), dtype=torch.bfloat16)]
+                inflight.append((i, 2, bucket.all_gather(pair, [torch.empty(world * t.numel(), dtype=torch.bfloat16) for t in pair], group=group)))
+            if len(inflight) >= 4 or session.offset > (3 << 20):
+                drain()
+                if session.offset > (3 << 20):
+                    bucket.barrier(group=group)
+                    session.offset = 0
+        drain()
+
     # reduce-scatter and all-reduce: fp32 sum in rank order, scaled, one rounding
     with bucket.session() as session:
         t = session.allocate((world * 8 * 25,), torch.bfloat16, group=group)
@@ -114,6 +151,28 @@ def _pp_worker(rank, world, transport='nvlink'):
         got = torch.empty(33, dtype=torch.int32)
         pp.recv(got, nxt)
         assert torch.equal(got, torch.arange(33, dtype=torch.int32) + nxt)
+    # both directions at once, random schedule honouring the in-flight limit (same seed on every rank), as the
+    # reference's `tests/pp/test_pp.py:16-47,96-111` does with timestamps
+    import random
+    rng = random.Random(11)
+    sent, received = {0: 0, 1: 0}, {0: 0, 1: 0}
+
+    def receive(d):
+        src = prv if d == 0 else nxt
+        got = torch.empty(64 + 5 * (received[d] % 7), dtype=torch.bfloat16)
+        pp.recv(got, src)
+        assert torch.all(got == float(100 * d + received[d] % 50 + src))
+        received[d] += 1
+    for _ in range(80):
+        d = rng.randrange(2) if world > 2 else 0                     # with two ranks both directions are one channel
+        if sent[d] - received[d] < 3 and rng.random() < 0.6:
+            pp.send(torch.full((64 + 5 * (sent[d] % 7),), float(100 * d + sent[d] % 50 + rank), dtype=torch.bfloat16), nxt if d == 0 else prv)
+            sent[d] += 1
+        elif received[d] < sent[d]:
+            receive(d)
+    for d in (0, 1):
+        while received[d] < sent[d]:
+            receive(d)
     with pytest.raises(AssertionError):
         pp.send(torch.zeros(1 << 20), nxt)                           # larger than the slot
     if world > 3:
