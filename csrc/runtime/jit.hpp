@@ -137,11 +137,17 @@ public:
         const auto dir = roots.front() + "/" + entry;
         const auto cubin = dir + "/kernel.cubin";
         std::filesystem::create_directories(dir);
-        {
-            std::ofstream out(dir + "/kernel.cu");
-            out << source;
-        }
         const auto tmp = cubin + ".tmp." + std::to_string(::getpid());
+        {
+            // several ranks may compile the same entry at once: the source is published with a rename, so a compiler that
+            // another rank has already started never reads a half-written file
+            const auto source_tmp = dir + "/kernel.cu.tmp." + std::to_string(::getpid());
+            {
+                std::ofstream out(source_tmp);
+                out << source;
+            }
+            std::filesystem::rename(source_tmp, dir + "/kernel.cu");
+        }
         // the compiler runs as a child process with an argument vector (no shell: paths from the environment may hold
         // spaces or shell metacharacters), its output goes to `nvcc.log`. It runs INSIDE the entry's directory and is given
         // file names only, because nvcc passes the paths it receives on to its own sub-commands through a shell.

@@ -78,6 +78,25 @@ def test_jit_paths_with_spaces_and_shell_characters(tmp_path):
             os.environ['EP_JIT_CACHE_DIR'] = saved
 
 
+def test_jit_concurrent_compilation_of_one_entry(tmp_path):
+    """Ranks of a job compile the same kernel at the same moment into one cache: every process gets the same complete
+    cubin (source and result are published with renames), and no temporary file stays behind."""
+    import subprocess
+    import sys
+    program = (
+        "import os, sys, deep_ep\n"
+        "src = 'extern \"C\" __global__ void k4(float* p) { if (p) p[threadIdx.x] *= 2.f; }\\n'\n"
+        "path = deep_ep._C.jit_compile('racing', src)\n"
+        "print(path, os.path.getsize(path))\n")
+    env = dict(os.environ, EP_JIT_CACHE_DIR=str(tmp_path))
+    children = [subprocess.Popen([sys.executable, '-c', program], env=env, stdout=subprocess.PIPE, text=True) for _ in range(4)]
+    answers = [child.communicate(timeout=600)[0].split() for child in children]
+    assert all(child.returncode == 0 for child in children)
+    assert len({tuple(answer) for answer in answers}) == 1 and int(answers[0][1]) > 0
+    leftovers = [f for _, _, files in os.walk(tmp_path) for f in files if '.tmp.' in f]
+    assert not leftovers
+
+
 @pytest.mark.parametrize('kernel', ['dispatch', 'expand', 'combine', 'reduce'])
 def test_specialised_ep_kernels_cross_compile(kernel, tmp_path):
     """Every shape-specialised EP kernel compiles for sm_100a (no GPU needed) from the three-line translation unit
