@@ -242,3 +242,38 @@ def test_type_stubs_match_the_built_extension():
     assert generator.generate() == committed, 'run `python csrc/generate_pyi.py`'
     declared = {node.name for node in ast.parse(committed).body if isinstance(node, (ast.FunctionDef, ast.ClassDef))}
     assert {'EPBuffer', 'PPBuffer', 'BucketBuffer', 'EngramBuffer', 'Context', 'barrier', 'calculate_ep_buffer_size'} <= declared
+
+
+def test_ep_buffer_size_follows_the_wire_format():
+    """`_C.calculate_ep_buffer_size` against a restatement of the wire format: a dispatch message is
+    [payload][scale factors ^16][top-k indices i32][top-k weights f32][source index i32] ^16, one landing slot per source
+    rank and token; a combine message is [bf16 payload][weights f32] ^16, one slot per master position (at most
+    min(top-k, ranks)) and token; the buffer is the larger of the two areas, 2 MiB aligned. Every slot of the area passes
+    the bounds predicate of the checked build and the first byte behind it does not."""
+    from hypothesis import given, settings, strategies as st
+    import deep_ep
+    _C = deep_ep._C
+
+    def up(x, a):
+        return (x + a - 1) // a * a
+
+    @settings(max_examples=80, deadline=None)
+    @given(st.sampled_from([1, 2, 4, 8]), st.integers(1, 4096), st.sampled_from([128, 512, 2048, 7168]),
+           st.integers(1, 8), st.booleans())
+    def check(num_ranks, num_tokens, hidden, num_topk, fp8):
+        payload = hidden if fp8 else 2 * hidden
+        scale_bytes = (hidden + 31) // 32 * 2 if fp8 else 0            # room for the densest scale format (1 x 32, 2 bytes)
+        dispatch_message = up(payload + up(scale_bytes, 16) + 8 * num_topk + 4, 16)
+        combine_message = up(2 * hidden + 4 * num_topk, 16)
+        dispatch_area = num_ranks * num_tokens * dispatch_message
+        combine_area = min(num_topk, num_ranks) * num_tokens * combine_message
+        expect = up(max(dispatch_area, combine_area), _C.get_num_allocation_alignment())
+        assert _C.calculate_ep_buffer_size(num_ranks, num_tokens, hidden, num_topk, fp8) == expect
+        last = (num_ranks * num_tokens - 1) * dispatch_message
+        assert _C.landing_range_ok(last, dispatch_message, dispatch_area)
+        assert not _C.landing_range_ok(last + dispatch_message, dispatch_message, dispatch_area)
+        assert not _C.landing_range_ok(last + 8, dispatch_message, dispatch_area + 64)      # a bulk store starts on 16 bytes
+
+    check()
+    # top-k 0 reserves room for the largest top-k a buffer may be used with
+    assert _C.calculate_ep_buffer_size(8, 4096, 7168, 0, True) >= _C.calculate_ep_buffer_size(8, 4096, 7168, 8, True)
